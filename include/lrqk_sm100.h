@@ -1,0 +1,255 @@
+/*
+ * lrqk_sm100.h -- C ABI of liblrqk_sm100.so: the LRQK prefill-factorisation and
+ * decode-time selection / attention path as CUDA kernels for NVIDIA B200 (sm_100a).
+ *
+ * Conventions
+ *   - Plain C: pointers, sizes, POD structs.  No C++ or torch types cross this line.
+ *   - Every compute entry point enqueues work on the CUDA stream it is given and
+ *     returns at once: 0 (LRQK_OK) or a negative LRQK_E* code (see lrqk_strerror).
+ *     Nothing here synchronises the stream, and -- unless an entry says otherwise --
+ *     nothing allocates: the caller owns every buffer, including scratch space whose
+ *     size the matching *_workspace_bytes() function reports.
+ *   - "device pointer" means an address a kernel on the current device can
+ *     dereference.  The host K|V store is page-locked host memory; its
+ *     device-visible address (lrqk_host_device_ptr) is what the structs carry.
+ *   - All tensors are dense and row-major in the shapes written beside them.
+ *     Shapes use: B batch, Hq query heads, Hkv key/value heads, G = Hq/Hkv,
+ *     N = B*Hq, d head dim, r rank, k resident (selected) rows, m recent-token
+ *     ("lite") rows.  Query head h reads KV head h / G.
+ *   - There is no CPU fallback: on a machine without an sm_100 device every compute
+ *     entry returns LRQK_ENODEVICE.
+ *
+ * Each entry cites the interface of the reference project (tenghuilee/LRQK, paths
+ * relative to its checkout) that it stands in for.
+ */
+#ifndef LRQK_SM100_H_
+#define LRQK_SM100_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void *lrqk_stream_t; /* a cudaStream_t */
+
+enum {
+  LRQK_OK = 0,
+  LRQK_EINVAL = -1,       /* null pointer, non-positive size, inconsistent shapes */
+  LRQK_ECAPACITY = -2,    /* an index or length exceeds the capacity given        */
+  LRQK_EUNSUPPORTED = -3, /* shape or dtype outside what the kernels are built for */
+  LRQK_ELAUNCH = -4,      /* the CUDA runtime refused a launch or an API call     */
+  LRQK_ETIMEOUT = -5,     /* a bounded device-side wait ran out                   */
+  LRQK_ENODEVICE = -6,    /* no sm_100 device is current                          */
+  LRQK_ENOMEM = -7        /* host allocation failed                               */
+};
+
+enum { LRQK_F32 = 0, LRQK_BF16 = 1 };
+
+const char *lrqk_version(void);
+const char *lrqk_strerror(int code);
+/* 1 when the current CUDA device is compute capability 10.x, else 0. */
+int lrqk_device_supported(void);
+/* Text of the last CUDA runtime error seen by this library on the calling thread. */
+const char *lrqk_last_cuda_error(void);
+
+/* ------------------------------------------------------------------------------------
+ * Page-locked, device-mapped host memory for the K|V store.
+ * Stands in for torch.empty(..., pin_memory=True) of AutoIncreaseTensorSharedKV
+ * (lrqk_attention.py:883-888, :1088-1094).  The only entries that allocate.
+ * ---------------------------------------------------------------------------------- */
+int lrqk_host_alloc(void **host_ptr, size_t bytes);
+int lrqk_host_free(void *host_ptr);
+int lrqk_host_device_ptr(void *host_ptr, void **device_ptr);
+
+/* ------------------------------------------------------------------------------------
+ * State of one layer (one LightAttentionIndicesFactory, lrqk_attention.py:1052-1111).
+ * All pointers are device pointers owned by the caller.
+ * ---------------------------------------------------------------------------------- */
+typedef struct lrqk_layer {
+  int32_t dtype;          /* LRQK_F32 / LRQK_BF16: element type of every tensor below   */
+  int32_t bsz, q_heads, kv_heads, head_dim;
+  int32_t r, k, m;        /* rank, attn_topk, num_lite_tokens                            */
+  int64_t a_capacity;     /* rows allocated per head in A_K (zero-initialised, :888)      */
+  int64_t host_capacity;  /* rows allocated per (b, kv head) in the host store (:113)     */
+  void *A_K;              /* [B,Hq,a_capacity,r]   rank-r key factors, all tokens         */
+  void *B_Q;              /* [B,Hq,r,d]                                                   */
+  void *B_K;              /* [B,Hq,r,d]                                                   */
+  void *K_res;            /* [B,Hq,k+m,d]  resident keys: k selected slots, then m lite   */
+  void *V_res;            /* [B,Hq,k+m,d]                                                 */
+  int32_t *table;         /* [B,Hq,k]   token position held by each selected slot         */
+  int32_t *lite_pos;      /* [m]        token position held by each lite slot             */
+  void *host_kv;          /* device-visible address of host [B,Hkv,host_capacity,2d], K|V */
+} lrqk_layer;
+
+/* One missed row: resident slot `slot` of head `head` (= b*Hq + h) must be refilled with
+ * token position `pos` from the host store. */
+typedef struct lrqk_miss {
+  int32_t head, slot, pos;
+} lrqk_miss;
+
+/* ------------------------------------------------------------------------------------
+ * Lite-ring write (+ optional flush of the ring to the host store).
+ * Replaces LightAttentionIndicesFactory._append / __set_lite (lrqk_attention.py:1133-1135,
+ * :1174-1196) and AutoIncreaseTensorSharedKV.append of the ring (:959-963, :1124-1131).
+ *   k_new, v_new : [B,Hkv,d]   the step's key / value
+ *   lite_slot    : ring slot written (K_res/V_res row k + lite_slot of all G heads of a group)
+ *   position     : token position stored into lite_pos[lite_slot]
+ *   flush_rows   : 0, or m when this write filled the ring: the ring of every KV head is then
+ *                  copied, in slot order, to host rows [host_row, host_row + m) as K|V
+ * ---------------------------------------------------------------------------------- */
+int lrqk_lite_append(const lrqk_layer *L, const void *k_new, const void *v_new, int32_t lite_slot,
+                     int32_t position, int32_t flush_rows, int64_t host_row, lrqk_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * Rank-r projection of the step's q, k and update of B_Q, B_K.
+ * Replaces _get_A_K_hitted_with_lite (lrqk_attention.py:1156-1171), cast_lrqk_decode /
+ * _lrqk_decode_inv_w1 / _lrqk_decode_gd_B_lr (:522-628, :651-665, :803-839) and the
+ * sync_cache append of k_hat (:1208-1233).  Unit weights (lambda = 1) only, like every
+ * caller in the reference (:1435-1436 defaults).
+ *   q        : [B,Hq,d], k_new: [B,Hkv,d]
+ *   append_row : row of A_K that receives k_hat (the new token's position)
+ *   q_hat    : out [B,Hq,r] in L->dtype
+ *   iters_out: optional device int32[1], number of alternations actually applied
+ * The active set is the k table entries followed by the m lite positions; A_K rows are
+ * read from the capacity buffer, so the row of the token being appended reads as zero.
+ * The early exit "mse(k_hat, k_hat') < tol" is a mean over ALL heads, as in the
+ * reference (:603-609); it is evaluated on the device, without a host round trip.
+ * ---------------------------------------------------------------------------------- */
+size_t lrqk_decode_project_update_workspace_bytes(const lrqk_layer *L, int32_t max_iter);
+int lrqk_decode_project_update(const lrqk_layer *L, const void *q, const void *k_new, int32_t max_iter,
+                               float tol, int64_t append_row, void *q_hat, int32_t *iters_out,
+                               void *workspace, lrqk_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * Proxy scores over the first `candidates` rows of A_K and top-k, fused.
+ * Replaces compute_hit_indices (lrqk_attention.py:1235-1273: matmul, torch.topk, torch.sort).
+ *   q_hat      : [B,Hq,r] in L->dtype
+ *   candidates : c, k < c <= a_capacity
+ *   wanted     : out [B,Hq,k] int32, ascending.  Scores are fp32 dot products of the stored
+ *                operands; of equal scores the lower position wins (-0 equals +0).
+ *   scores_out : optional [B,Hq,scores_stride] fp32 copy of the scores (testing)
+ * ---------------------------------------------------------------------------------- */
+int lrqk_score_topk(const lrqk_layer *L, const void *q_hat, int64_t candidates, int32_t *wanted,
+                    float *scores_out, int64_t scores_stride, lrqk_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * Hit/miss difference of `wanted` against the slot table, in place.
+ * Replaces only_indices_in_cpu (lrqk_attention.py:1275-1315) and the index builder
+ * _take_along_dim_with_mask_python_indices (:71-98).
+ *   wanted     : [B,Hq,k] ascending, duplicate-free
+ *   mask       : out [B,Hq,k] uint8, 1 = slot refilled
+ *   miss_count : out [B,Hq] int32
+ *   list       : out, room for B*Hq*k entries; *list_len (device int32, must be 0 on entry)
+ *                receives the number of entries.  Entry order across heads is unspecified.
+ *   status     : device int32[1]; set non-zero if a head's evicted and missing counts differ
+ * ---------------------------------------------------------------------------------- */
+int lrqk_slot_diff(const lrqk_layer *L, const int32_t *wanted, uint8_t *mask, int32_t *miss_count,
+                   lrqk_miss *list, int32_t *list_len, int32_t *status, lrqk_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * Fetch of the missed rows from the host store straight into their slots.
+ * Replaces take_along_dim_with_mask_python -> cpp_kernel.d0_index_select -> .to(cuda)
+ * (lrqk_attention.py:101-117, cpp_kernel/__init__.py:7-16,
+ * cpp_kernel/take_along_dim_grouped.cpp:133-183) and the masked scatter (:1603-1608).
+ * Reads *list_len on the device; no host synchronisation.
+ * ---------------------------------------------------------------------------------- */
+int lrqk_miss_gather(const lrqk_layer *L, const lrqk_miss *list, const int32_t *list_len,
+                     lrqk_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * Exact attention of one query per head over the first `rows` resident rows.
+ * Replaces flash_attn_with_kvcache(q, k, v, causal=True) with one query
+ * (lrqk_attention.py:2326-2327; Qwen2/Mistral :2205-2216, :2438-2449).
+ *   q   : [B,Hq,d];  out : [B,Hq,d] in L->dtype;  scale: 1/sqrt(d) in the reference
+ *   workspace must be zero-filled before its first use; the kernel leaves it reusable.
+ * ---------------------------------------------------------------------------------- */
+size_t lrqk_flash_decode_workspace_bytes(const lrqk_layer *L, int32_t rows);
+int lrqk_flash_decode(const lrqk_layer *L, const void *q, void *out, int32_t rows, float scale,
+                      void *workspace, lrqk_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * One whole decode step of a layer: the six calls above in the reference's order
+ * (LightAttentionIndicesFactory.decode, lrqk_attention.py:1506-1613, followed by the
+ * attention call).  Host-side counters (ring slot, positions, candidate count) are the
+ * caller's, exactly as they are Python attributes in the reference.
+ * ---------------------------------------------------------------------------------- */
+typedef struct lrqk_step_args {
+  const void *q;          /* [B,Hq,d]  */
+  const void *k_new;      /* [B,Hkv,d] */
+  const void *v_new;      /* [B,Hkv,d] */
+  void *attn_out;         /* [B,Hq,d], may be NULL to skip attention */
+  int32_t lite_slot;      /* ring slot this step writes                          */
+  int32_t position;       /* token position of the new token (= current length)  */
+  int32_t flush_rows;     /* m when this step fills the ring, else 0             */
+  int64_t host_row;       /* first host row of a flush                           */
+  int64_t candidates;     /* c = oldest lite position - 1 after the ring write   */
+  int32_t max_iter;       /* decode alternations                                 */
+  float tol;
+  float scale;            /* softmax scale                                       */
+  void *q_hat;            /* out [B,Hq,r]                                        */
+  int32_t *wanted;        /* out [B,Hq,k]                                        */
+  uint8_t *mask;          /* out [B,Hq,k]                                        */
+  int32_t *miss_count;    /* out [B,Hq]                                          */
+  lrqk_miss *miss_list;   /* scratch, B*Hq*k entries                             */
+  int32_t *counters;      /* device int32[4]: [0] list length, [1] status, [2] iterations, [3] spare */
+  void *project_workspace;
+  void *attn_workspace;
+} lrqk_step_args;
+
+int lrqk_layer_step(const lrqk_layer *L, const lrqk_step_args *a, lrqk_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * The reference's native gather interface (pybind11 module take_along_dim_grouped,
+ * cpp_kernel/take_along_dim_grouped.cpp:185-208), as device kernels that read the
+ * page-locked host source directly.
+ * ---------------------------------------------------------------------------------- */
+/* dst[i,:] = src[rows[i],:]  -- d0_indices_select (:133-183).  dst, rows: device; src: device-
+ * visible (host-mapped or device) memory; row_bytes a multiple of 16. */
+int lrqk_d0_indices_select(void *dst, const void *src, const int64_t *rows, int64_t n_rows,
+                           int64_t row_bytes, int64_t src_rows, lrqk_stream_t stream);
+/* take_along_dim_with_mask (:13-124): src [B,Hkv,S,row_bytes], indices int64 and mask uint8
+ * [B,Hkv,G,k]; dst receives the masked rows in row-major mask order; *n_out (device int64)
+ * their number.  workspace: lrqk_take_along_dim_with_mask_workspace_bytes(). */
+size_t lrqk_take_along_dim_with_mask_workspace_bytes(int64_t bsz, int64_t kv_heads, int64_t groups,
+                                                     int64_t k);
+int lrqk_take_along_dim_with_mask(void *dst, const void *src, const int64_t *indices,
+                                  const uint8_t *mask, int64_t bsz, int64_t kv_heads, int64_t seq_len,
+                                  int64_t groups, int64_t k, int64_t row_bytes, int64_t *n_out,
+                                  void *workspace, lrqk_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * Prompt-time helpers of LightAttentionIndicesFactory.prefill (lrqk_attention.py:1385-1504).
+ * ---------------------------------------------------------------------------------- */
+/* K|V rows of the prompt into the host store (KVcpu.append, :1469, :959-963):
+ * keys, values [B,Hkv,S,d] -> host rows [host_row, host_row+S) of every (b, kv head). */
+int lrqk_kv_pack_host(const lrqk_layer *L, const void *keys, const void *values, int64_t seq_len,
+                      int64_t host_row, lrqk_stream_t stream);
+/* Selected prompt rows into the resident slots, on the device (fetch_by_hit same-device
+ * branch, :1339-1351) and the last m prompt tokens into the lite slots (:1493-1504):
+ * K_res/V_res[n, s] = keys/values[b, kvh, table[n, s]] for s < k; slots k..k+m-1 receive
+ * positions S-m..S-1, which are also written to lite_pos. */
+int lrqk_prefill_fill_resident(const lrqk_layer *L, const void *keys, const void *values,
+                               int64_t seq_len, lrqk_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * Prompt factorisation  Q ~ A_Q B_Q, K ~ A_K B_K with A_Q A_K^T ~ Q K^T.
+ * Replaces cast_lrqk_prefill / _lrqk_prefill_inv_w1 (lrqk_attention.py:312-423, :772-800).
+ *   Q [B,Hq,S,d], K [B,Hkv,S,d] in L->dtype (K is NOT expanded to the query heads)
+ *   A_Q, A_K_init : fp32 [B,Hq,S,r] initial factors (see _init_AQ_AK, :187-209); overwritten
+ *   sweeps, tol : max_iter[0], tol[0]; the stop test after a sweep is evaluated on the device
+ * Outputs: L->A_K rows [0,S), L->B_Q, L->B_K in L->dtype; a_q_last [B,Hq,r] in L->dtype
+ * (the last row of A_Q, the query of the prompt-time selection, :1471-1474);
+ * sweeps_out optional device int32[1].
+ * ---------------------------------------------------------------------------------- */
+size_t lrqk_prefill_factorize_workspace_bytes(const lrqk_layer *L, int64_t seq_len);
+int lrqk_prefill_factorize(const lrqk_layer *L, const void *Q, const void *K, float *A_Q,
+                           float *A_K_init, int64_t seq_len, int32_t sweeps, float tol,
+                           void *a_q_last, int32_t *sweeps_out, void *workspace,
+                           lrqk_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LRQK_SM100_H_ */

@@ -1,0 +1,95 @@
+// Library-level entry points: version, error text, device check, page-locked host memory.
+#include <stdio.h>
+#include <string.h>
+
+#include "common.cuh"
+
+namespace lrqk {
+
+static thread_local char g_last_cuda_error[256] = "";
+
+void note_cuda_error(cudaError_t e) {
+  const char *name = cudaGetErrorName(e);
+  const char *text = cudaGetErrorString(e);
+  snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "%s: %s", name ? name : "?", text ? text : "?");
+  cudaGetLastError();  // clear the sticky-free error so later launches are judged on their own
+}
+
+int check_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return LRQK_ENODEVICE; }
+  static int cached_dev = -2, cached_ok = 0;
+  if (dev != cached_dev) {
+    int major = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) {
+      cudaGetLastError();
+      return LRQK_ENODEVICE;
+    }
+    cached_ok = (major == 10);
+    cached_dev = dev;
+  }
+  return cached_ok ? LRQK_OK : LRQK_ENODEVICE;
+}
+
+int check_layer(const lrqk_layer *L) {
+  if (!L) return LRQK_EINVAL;
+  if (L->dtype != LRQK_F32 && L->dtype != LRQK_BF16) return LRQK_EUNSUPPORTED;
+  if (L->bsz <= 0 || L->q_heads <= 0 || L->kv_heads <= 0 || L->head_dim <= 0) return LRQK_EINVAL;
+  if (L->q_heads % L->kv_heads != 0) return LRQK_EINVAL;
+  if (L->r <= 0 || L->k <= 0 || L->m <= 0) return LRQK_EINVAL;
+  if (L->a_capacity <= 0 || L->host_capacity < 0) return LRQK_EINVAL;
+  if (L->head_dim != 64 && L->head_dim != 128) return LRQK_EUNSUPPORTED;
+  if (L->r != 8 && L->r != 16 && L->r != 32 && L->r != 64) return LRQK_EUNSUPPORTED;
+  if ((int64_t)L->bsz * L->q_heads * (int64_t)L->k >= (1ll << 31)) return LRQK_EUNSUPPORTED;
+  if (L->a_capacity >= (1ll << 31)) return LRQK_EUNSUPPORTED;
+  return LRQK_OK;
+}
+
+}  // namespace lrqk
+
+extern "C" {
+
+const char *lrqk_version(void) { return "lrqk_sm100 0.1.0 (sm_100a)"; }
+
+const char *lrqk_strerror(int code) {
+  switch (code) {
+    case LRQK_OK: return "ok";
+    case LRQK_EINVAL: return "invalid argument";
+    case LRQK_ECAPACITY: return "index or length exceeds the given capacity";
+    case LRQK_EUNSUPPORTED: return "shape or dtype not supported by the sm_100a kernels";
+    case LRQK_ELAUNCH: return "CUDA runtime error (see lrqk_last_cuda_error)";
+    case LRQK_ETIMEOUT: return "bounded device-side wait ran out";
+    case LRQK_ENODEVICE: return "no sm_100 CUDA device is current (there is no CPU fallback)";
+    case LRQK_ENOMEM: return "host allocation failed";
+    default: return "unknown lrqk error code";
+  }
+}
+
+const char *lrqk_last_cuda_error(void) { return lrqk::g_last_cuda_error; }
+
+int lrqk_device_supported(void) { return lrqk::check_device() == LRQK_OK ? 1 : 0; }
+
+int lrqk_host_alloc(void **host_ptr, size_t bytes) {
+  if (!host_ptr || bytes == 0) return LRQK_EINVAL;
+  *host_ptr = nullptr;
+  cudaError_t e = cudaHostAlloc(host_ptr, bytes, cudaHostAllocMapped | cudaHostAllocPortable);
+  if (e != cudaSuccess) {
+    lrqk::note_cuda_error(e);
+    return e == cudaErrorMemoryAllocation ? LRQK_ENOMEM : LRQK_ELAUNCH;
+  }
+  return LRQK_OK;
+}
+
+int lrqk_host_free(void *host_ptr) {
+  if (!host_ptr) return LRQK_OK;
+  LRQK_CUDA_TRY(cudaFreeHost(host_ptr));
+  return LRQK_OK;
+}
+
+int lrqk_host_device_ptr(void *host_ptr, void **device_ptr) {
+  if (!host_ptr || !device_ptr) return LRQK_EINVAL;
+  LRQK_CUDA_TRY(cudaHostGetDevicePointer(device_ptr, host_ptr, 0));
+  return LRQK_OK;
+}
+
+}  // extern "C"

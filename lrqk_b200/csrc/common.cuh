@@ -1,0 +1,92 @@
+// Shared device/host helpers of liblrqk_sm100.so (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "lrqk_sm100.h"
+
+namespace lrqk {
+
+constexpr int kNumSMs = 148;  // B200: two dies of 74 SMs
+
+// ---- host side -------------------------------------------------------------------------
+void note_cuda_error(cudaError_t e);
+
+#define LRQK_CUDA_TRY(expr)                      \
+  do {                                           \
+    cudaError_t _e = (expr);                     \
+    if (_e != cudaSuccess) {                     \
+      ::lrqk::note_cuda_error(_e);               \
+      return LRQK_ELAUNCH;                       \
+    }                                            \
+  } while (0)
+
+#define LRQK_LAUNCH_CHECK() LRQK_CUDA_TRY(cudaGetLastError())
+
+int check_device();              // LRQK_OK or LRQK_ENODEVICE
+int check_layer(const lrqk_layer *L);
+
+inline cudaStream_t as_stream(lrqk_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+inline size_t elt_size(int dtype) { return dtype == LRQK_BF16 ? 2 : 4; }
+inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// ---- device side -----------------------------------------------------------------------
+// Order-preserving map float -> uint32 (larger float <=> larger key); -0 folds onto +0.
+__device__ __forceinline__ uint32_t order_key(float f) {
+  if (f == 0.0f) f = 0.0f;
+  uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+template <typename T> struct Elt;
+template <> struct Elt<float> {
+  static constexpr int kPerVec = 4;  // elements per 16-byte vector
+  __device__ static __forceinline__ void unpack(const uint4 &v, float (&f)[4]) {
+    f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y);
+    f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+  }
+  __device__ static __forceinline__ float to_float(float x) { return x; }
+  __device__ static __forceinline__ float from_float(float x) { return x; }
+};
+template <> struct Elt<__nv_bfloat16> {
+  static constexpr int kPerVec = 8;
+  __device__ static __forceinline__ void unpack(const uint4 &v, float (&f)[8]) {
+    // bf16 -> fp32 is a 16-bit shift
+    f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xFFFF0000u);
+    f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xFFFF0000u);
+    f[4] = __uint_as_float(v.z << 16); f[5] = __uint_as_float(v.z & 0xFFFF0000u);
+    f[6] = __uint_as_float(v.w << 16); f[7] = __uint_as_float(v.w & 0xFFFF0000u);
+  }
+  __device__ static __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+  __device__ static __forceinline__ __nv_bfloat16 from_float(float x) { return __float2bfloat16_rn(x); }
+};
+
+// Streaming 16-byte load that bypasses L1 allocation.  (The L2 evict-first qualifier exists
+// only for 32-byte loads on sm_100; the scoring kernel uses those where a row allows.)
+__device__ __forceinline__ uint4 ld_stream16(const void *p) {
+  uint4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint4 ld16(const void *p) { return *reinterpret_cast<const uint4 *>(p); }
+__device__ __forceinline__ void st16(void *p, const uint4 &v) { *reinterpret_cast<uint4 *>(p) = v; }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+  return v;
+}
+
+// Dispatch on the element type of a layer.
+#define LRQK_DISPATCH_DTYPE(dtype, T, ...)                       \
+  do {                                                           \
+    if ((dtype) == LRQK_BF16) { using T = __nv_bfloat16; __VA_ARGS__; } \
+    else if ((dtype) == LRQK_F32) { using T = float; __VA_ARGS__; }     \
+    else return LRQK_EUNSUPPORTED;                               \
+  } while (0)
+
+}  // namespace lrqk

@@ -1,0 +1,30 @@
+// One decode step of a layer as a single host call: the kernels of the step are enqueued
+// back to back on the caller's stream, with no host synchronisation in between (the miss
+// count, the early-exit decision and the slot-table update all stay on the device).
+#include "common.cuh"
+
+extern "C" int lrqk_layer_step(const lrqk_layer *L, const lrqk_step_args *a, lrqk_stream_t stream) {
+  using namespace lrqk;
+  if (!L || !a) return LRQK_EINVAL;
+  if (!a->q || !a->k_new || !a->v_new || !a->q_hat || !a->wanted || !a->mask || !a->miss_count || !a->miss_list ||
+      !a->counters || !a->project_workspace)
+    return LRQK_EINVAL;
+  if (a->attn_out && !a->attn_workspace) return LRQK_EINVAL;
+  int rc = lrqk_lite_append(L, a->k_new, a->v_new, a->lite_slot, a->position, a->flush_rows, a->host_row, stream);
+  if (rc != LRQK_OK) return rc;
+  rc = lrqk_decode_project_update(L, a->q, a->k_new, a->max_iter, a->tol, a->position, a->q_hat, a->counters + 2,
+                                  a->project_workspace, stream);
+  if (rc != LRQK_OK) return rc;
+  rc = lrqk_score_topk(L, a->q_hat, a->candidates, a->wanted, nullptr, 0, stream);
+  if (rc != LRQK_OK) return rc;
+  LRQK_CUDA_TRY(cudaMemsetAsync(a->counters, 0, sizeof(int32_t), as_stream(stream)));
+  rc = lrqk_slot_diff(L, a->wanted, a->mask, a->miss_count, a->miss_list, a->counters, a->counters + 1, stream);
+  if (rc != LRQK_OK) return rc;
+  rc = lrqk_miss_gather(L, a->miss_list, a->counters, stream);
+  if (rc != LRQK_OK) return rc;
+  if (a->attn_out) {
+    rc = lrqk_flash_decode(L, a->q, a->attn_out, L->k + L->m, a->scale, a->attn_workspace, stream);
+    if (rc != LRQK_OK) return rc;
+  }
+  return LRQK_OK;
+}

@@ -1,0 +1,208 @@
+"""Device-side state of one layer and thin wrappers over the C-ABI operators.
+
+``LayerState`` owns the tensors a ``LightAttentionIndicesFactory`` keeps in the
+reference (lrqk_attention.py:1052-1111) -- the rank-r key factors ``A_K``, the
+right factors ``B_Q``/``B_K``, the resident keys/values, the slot table and the
+page-locked host K|V store -- and the ``lrqk_layer`` struct that points at them.
+torch is used for device memory and streams only; every computation is a call
+into ``liblrqk_sm100.so``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import numpy as np
+import torch
+
+from . import _lib
+
+_DTYPES = {torch.float32: _lib.LRQK_F32, torch.bfloat16: _lib.LRQK_BF16}
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class HostStore:
+    """Page-locked, device-mapped host buffer [B, Hkv, capacity, 2d] holding K|V rows
+    (the reference's pinned AutoIncreaseTensorSharedKV, lrqk_attention.py:959-963, :1088-1094)."""
+
+    def __init__(self, bsz: int, kv_heads: int, capacity: int, head_dim: int, dtype: torch.dtype):
+        self.shape = (bsz, kv_heads, capacity, 2 * head_dim)
+        self.dtype = dtype
+        self.nbytes = int(np.prod(self.shape)) * torch.empty((), dtype=dtype).element_size()
+        hp = C.c_void_p()
+        _lib.check(_lib.lib().lrqk_host_alloc(C.byref(hp), self.nbytes), "lrqk_host_alloc")
+        self.host_ptr = hp.value
+        dp = C.c_void_p()
+        _lib.check(_lib.lib().lrqk_host_device_ptr(hp, C.byref(dp)), "lrqk_host_device_ptr")
+        self.device_ptr = dp.value
+        raw = (C.c_uint8 * self.nbytes).from_address(self.host_ptr)
+        self._raw = raw
+        self.data = torch.frombuffer(raw, dtype=torch.uint8).view(dtype).view(self.shape)
+        self.data.zero_()  # the reference's store is zero-initialised (:888); cudaHostAlloc memory is not
+        self.current_len = 0
+
+    @property
+    def capacity(self) -> int:
+        return self.shape[2]
+
+    def close(self):
+        if getattr(self, "host_ptr", None):
+            self.data = None
+            self._raw = None
+            _lib.lib().lrqk_host_free(C.c_void_p(self.host_ptr))
+            self.host_ptr = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class LayerState:
+    def __init__(self, bsz: int, q_heads: int, kv_heads: int, head_dim: int, r: int, k: int, m: int,
+                 a_capacity: int, host_capacity: int, dtype: torch.dtype, device="cuda", max_iter: int = 2,
+                 with_host: bool = True):
+        if dtype not in _DTYPES:
+            raise ValueError(f"unsupported dtype {dtype}: the kernels take float32 or bfloat16")
+        if not torch.cuda.is_available():
+            raise RuntimeError("lrqk_b200 needs a CUDA device (sm_100); there is no CPU path")
+        self.lib = _lib.lib()
+        self.bsz, self.q_heads, self.kv_heads, self.head_dim = bsz, q_heads, kv_heads, head_dim
+        self.r, self.k, self.m = r, k, m
+        self.dtype, self.device = dtype, torch.device(device)
+        n = bsz * q_heads
+        z = dict(dtype=dtype, device=self.device)
+        self.A_K = torch.zeros((bsz, q_heads, a_capacity, r), **z)          # zero-initialised (:888)
+        self.B_Q = torch.zeros((bsz, q_heads, r, head_dim), **z)
+        self.B_K = torch.zeros((bsz, q_heads, r, head_dim), **z)
+        self.K_res = torch.zeros((bsz, q_heads, k + m, head_dim), **z)      # (:1417-1426)
+        self.V_res = torch.zeros((bsz, q_heads, k + m, head_dim), **z)
+        self.table = torch.zeros((bsz, q_heads, k), dtype=torch.int32, device=self.device)
+        self.lite_pos = torch.full((m,), -1, dtype=torch.int32, device=self.device)
+        self.host = HostStore(bsz, kv_heads, host_capacity, head_dim, dtype) if with_host else None
+        # per-step outputs and scratch
+        self.q_hat = torch.zeros((bsz, q_heads, r), **z)
+        self.wanted = torch.zeros((bsz, q_heads, k), dtype=torch.int32, device=self.device)
+        self.mask = torch.zeros((bsz, q_heads, k), dtype=torch.uint8, device=self.device)
+        self.miss_count = torch.zeros((bsz, q_heads), dtype=torch.int32, device=self.device)
+        self.miss_list = torch.zeros((n * k, 3), dtype=torch.int32, device=self.device)
+        self.counters = torch.zeros((4,), dtype=torch.int32, device=self.device)
+        self.attn_out = torch.zeros((bsz, q_heads, head_dim), **z)
+        self._rebuild_struct()
+        self.max_iter_ws = max(1, max_iter)
+        nb = self.lib.lrqk_decode_project_update_workspace_bytes(C.byref(self.c), self.max_iter_ws)
+        self.project_ws = torch.zeros((max(nb, 16),), dtype=torch.uint8, device=self.device)
+        nb = self.lib.lrqk_flash_decode_workspace_bytes(C.byref(self.c), k + m)
+        self.attn_ws = torch.zeros((max(nb, 16),), dtype=torch.uint8, device=self.device)
+
+    def _rebuild_struct(self):
+        c = _lib.Layer()
+        c.dtype = _DTYPES[self.dtype]
+        c.bsz, c.q_heads, c.kv_heads, c.head_dim = self.bsz, self.q_heads, self.kv_heads, self.head_dim
+        c.r, c.k, c.m = self.r, self.k, self.m
+        c.a_capacity = self.A_K.shape[2]
+        c.host_capacity = self.host.capacity if self.host is not None else 0
+        c.A_K, c.B_Q, c.B_K = self.A_K.data_ptr(), self.B_Q.data_ptr(), self.B_K.data_ptr()
+        c.K_res, c.V_res = self.K_res.data_ptr(), self.V_res.data_ptr()
+        c.table, c.lite_pos = self.table.data_ptr(), self.lite_pos.data_ptr()
+        c.host_kv = self.host.device_ptr if self.host is not None else None
+        self.c = c
+
+    # ---- operators -------------------------------------------------------------------------
+    def _chk(self, t: torch.Tensor, shape, name: str):
+        if t.dtype != self.dtype or not t.is_cuda or not t.is_contiguous() or tuple(t.shape) != tuple(shape):
+            raise ValueError(f"{name}: expected contiguous {self.dtype} CUDA tensor of shape {tuple(shape)}, "
+                             f"got {t.dtype} {tuple(t.shape)} on {t.device}")
+
+    def lite_append(self, k_new, v_new, lite_slot: int, position: int, flush_rows: int = 0, host_row: int = 0):
+        self._chk(k_new, (self.bsz, self.kv_heads, self.head_dim), "k_new")
+        self._chk(v_new, (self.bsz, self.kv_heads, self.head_dim), "v_new")
+        _lib.check(self.lib.lrqk_lite_append(C.byref(self.c), _ptr(k_new), _ptr(v_new), lite_slot, position,
+                                             flush_rows, host_row, _stream()), "lrqk_lite_append")
+
+    def project_update(self, q, k_new, max_iter: int, tol: float, append_row: int):
+        self._chk(q, (self.bsz, self.q_heads, self.head_dim), "q")
+        self._chk(k_new, (self.bsz, self.kv_heads, self.head_dim), "k_new")
+        if max(1, max_iter) > self.max_iter_ws:
+            raise ValueError("max_iter exceeds the workspace this state was sized for")
+        _lib.check(self.lib.lrqk_decode_project_update(
+            C.byref(self.c), _ptr(q), _ptr(k_new), max_iter, tol, append_row, _ptr(self.q_hat),
+            C.c_void_p(self.counters.data_ptr() + 8), _ptr(self.project_ws), _stream()),
+            "lrqk_decode_project_update")
+        return self.q_hat
+
+    def score_topk(self, q_hat, candidates: int, scores_out: Optional[torch.Tensor] = None):
+        self._chk(q_hat, (self.bsz, self.q_heads, self.r), "q_hat")
+        stride = 0
+        if scores_out is not None:
+            assert scores_out.dtype == torch.float32 and scores_out.is_contiguous()
+            stride = scores_out.shape[-1]
+        _lib.check(self.lib.lrqk_score_topk(C.byref(self.c), _ptr(q_hat), candidates, _ptr(self.wanted),
+                                            _ptr(scores_out), stride, _stream()), "lrqk_score_topk")
+        return self.wanted
+
+    def slot_diff(self, wanted: Optional[torch.Tensor] = None):
+        wanted = self.wanted if wanted is None else wanted
+        self.counters[:2].zero_()
+        _lib.check(self.lib.lrqk_slot_diff(C.byref(self.c), _ptr(wanted), _ptr(self.mask), _ptr(self.miss_count),
+                                           _ptr(self.miss_list), _ptr(self.counters),
+                                           C.c_void_p(self.counters.data_ptr() + 4), _stream()), "lrqk_slot_diff")
+        return self.mask
+
+    def miss_gather(self):
+        _lib.check(self.lib.lrqk_miss_gather(C.byref(self.c), _ptr(self.miss_list), _ptr(self.counters), _stream()),
+                   "lrqk_miss_gather")
+
+    def flash_decode(self, q, rows: Optional[int] = None, scale: Optional[float] = None):
+        self._chk(q, (self.bsz, self.q_heads, self.head_dim), "q")
+        rows = self.k + self.m if rows is None else rows
+        scale = self.head_dim ** -0.5 if scale is None else scale
+        _lib.check(self.lib.lrqk_flash_decode(C.byref(self.c), _ptr(q), _ptr(self.attn_out), rows, scale,
+                                              _ptr(self.attn_ws), _stream()), "lrqk_flash_decode")
+        return self.attn_out
+
+    def make_step_args(self, q, k_new, v_new, lite_slot: int, position: int, flush_rows: int, host_row: int,
+                       candidates: int, max_iter: int, tol: float, scale: Optional[float] = None,
+                       attention: bool = True) -> _lib.StepArgs:
+        a = _lib.StepArgs()
+        a.q, a.k_new, a.v_new = q.data_ptr(), k_new.data_ptr(), v_new.data_ptr()
+        a.attn_out = self.attn_out.data_ptr() if attention else None
+        a.lite_slot, a.position, a.flush_rows, a.host_row = lite_slot, position, flush_rows, host_row
+        a.candidates, a.max_iter, a.tol = candidates, max_iter, tol
+        a.scale = self.head_dim ** -0.5 if scale is None else scale
+        a.q_hat, a.wanted, a.mask = self.q_hat.data_ptr(), self.wanted.data_ptr(), self.mask.data_ptr()
+        a.miss_count, a.miss_list = self.miss_count.data_ptr(), self.miss_list.data_ptr()
+        a.counters = self.counters.data_ptr()
+        a.project_workspace, a.attn_workspace = self.project_ws.data_ptr(), self.attn_ws.data_ptr()
+        return a
+
+    def layer_step(self, args: _lib.StepArgs):
+        _lib.check(self.lib.lrqk_layer_step(C.byref(self.c), C.byref(args), _stream()), "lrqk_layer_step")
+
+    def kv_pack_host(self, keys, values, host_row: int = 0):
+        s = keys.shape[2]
+        self._chk(keys, (self.bsz, self.kv_heads, s, self.head_dim), "keys")
+        self._chk(values, (self.bsz, self.kv_heads, s, self.head_dim), "values")
+        _lib.check(self.lib.lrqk_kv_pack_host(C.byref(self.c), _ptr(keys), _ptr(values), s, host_row, _stream()),
+                   "lrqk_kv_pack_host")
+
+    def fill_resident(self, keys, values):
+        s = keys.shape[2]
+        self._chk(keys, (self.bsz, self.kv_heads, s, self.head_dim), "keys")
+        self._chk(values, (self.bsz, self.kv_heads, s, self.head_dim), "values")
+        _lib.check(self.lib.lrqk_prefill_fill_resident(C.byref(self.c), _ptr(keys), _ptr(values), s, _stream()),
+                   "lrqk_prefill_fill_resident")
+
+    def close(self):
+        if self.host is not None:
+            torch.cuda.synchronize()
+            self.host.close()
+            self.host = None
