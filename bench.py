@@ -1,0 +1,506 @@
+#!/usr/bin/env python
+"""Benchmark of the LRQK per-layer decode step on B200.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--layers L] [--rho R]
+
+Workload ("cfg2-layer"): the attention layer of a Llama-3-8B-shaped model at 128K context --
+batch 1, 32 query / 8 KV heads, head_dim 128, prompt 131072 tokens, r=32, num_active_tokens=2048,
+lite_tokens=64, max_iter=(2,2), bf16 -- with `--layers` independent layer states that a decode
+"step" (one token) walks through in order, as a model would.  Metric: microseconds per layer per
+decode step (lite-ring write + rank-r projection/update + proxy score + top-k + hit/miss + miss
+fetch from pinned host memory + exact attention).  Inputs are seeded synthetic tensors of the
+config's distributions; nothing is read from disk.
+
+N > 1 (torchrun, one rank per GPU): KV heads are sharded across ranks (strong scaling), each rank
+owns its heads' factors, slot tables, resident rows and host store; one all-gather of the
+attention outputs per layer-step.
+
+`--impl reference` times the CPU restatement of the reference's decode step (oracle/) on the host
+cores for the same workload; the default arm also times it on a bounded sample (`cpu_baseline`).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch
+
+WORKLOADS = {
+    # name: bsz, q heads, kv heads, head dim, prompt length, r, k, m, max_iter, tol
+    "cfg2-layer": dict(bsz=1, hq=32, hkv=8, d=128, seq=131072, r=32, k=2048, m=64, max_iter=(2, 2), tol=1e-2),
+    "cfg1-layer": dict(bsz=4, hq=32, hkv=8, d=128, seq=32768, r=32, k=2048, m=64, max_iter=(2, 2), tol=1e-2),
+    "cfg0": dict(bsz=1, hq=8, hkv=2, d=128, seq=4096, r=16, k=256, m=16, max_iter=(2, 2), tol=1e-2),
+}
+FALLBACK_HBM_GBS = 6650.0
+
+
+# ------------------------------------------------------------------------------------------------
+# synthetic inputs
+# ------------------------------------------------------------------------------------------------
+def make_prompt(seed: int, w: dict, hq: int, hkv: int, device, dtype):
+    """K = U W + 0.1 E per KV head (U~N(0,1) [S,32], W~N(0,1/32), E~N(0,1)); V, Q ~ N(0,1)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    b, s, d = w["bsz"], w["seq"], w["d"]
+    U = torch.randn(b, hkv, s, 32, generator=g, device=device)
+    W = torch.randn(b, hkv, 32, d, generator=g, device=device) / math.sqrt(32)
+    K = (U @ W + 0.1 * torch.randn(b, hkv, s, d, generator=g, device=device)).to(dtype)
+    V = torch.randn(b, hkv, s, d, generator=g, device=device).to(dtype)
+    Q = torch.randn(b, hq, s, d, generator=g, device=device).to(dtype)
+    return Q, K, V
+
+
+def factor_state(Q, K, r: int, groups: int, sweeps: int, seed: int):
+    """Rank-r factors for a synthetic prompt, from a random start, by the reference's alternating
+    least squares written on the d x d Gram matrices (setup only; untimed).  Returns A_K
+    [B,Hq,S,r], B_Q, B_K [B,Hq,r,d] and the last row of A_Q [B,Hq,r], fp32."""
+    f = torch.float32
+    b, hq, s, d = Q.shape
+    g = torch.Generator(device=Q.device).manual_seed(seed)
+    t = lambda x: x.transpose(-1, -2)
+    SQ = torch.empty(b, hq, d, d, device=Q.device)
+    CQ = torch.empty(b, hq, r, d, device=Q.device)
+    GQ = torch.empty(b, hq, r, r, device=Q.device)
+    SK, CK, GK = torch.empty_like(SQ), torch.empty_like(CQ), torch.empty_like(GQ)
+    for h in range(hq):  # one head at a time keeps the fp32 temporaries small
+        q32, k32 = Q[:, h].to(f), K[:, h // groups].to(f)
+        a_q0 = torch.randn(b, s, r, generator=g, device=Q.device)
+        a_k0 = torch.randn(b, s, r, generator=g, device=Q.device)
+        SQ[:, h], SK[:, h] = t(q32) @ q32, t(k32) @ k32
+        CQ[:, h], CK[:, h] = t(a_q0) @ q32, t(a_k0) @ k32
+        GQ[:, h], GK[:, h] = t(a_q0) @ a_q0, t(a_k0) @ a_k0
+    solve = lambda a, bb: torch.linalg.solve(a, bb)
+    solve_r = lambda a, bb: torch.linalg.solve(a, bb, left=False)
+    XQ = XK = None
+    for _ in range(max(1, sweeps)):
+        BQ, BK = solve(GQ, CQ), solve(GK, CK)
+        XQ = solve_r(GK + BQ @ t(BQ), t(CK) + t(BQ))            # A_Q = Q XQ
+        GQ, CQ = t(XQ) @ SQ @ XQ, t(XQ) @ SQ
+        XK = solve_r(GQ + BK @ t(BK), t(CQ) + t(BK))            # A_K = K XK
+        GK, CK = t(XK) @ SK @ XK, t(XK) @ SK
+    BQ, BK = solve(GQ, CQ), solve(GK, CK)
+    A_K = torch.empty(b, hq, s, r, device=Q.device, dtype=Q.dtype)
+    for h in range(hq):
+        A_K[:, h] = (K[:, h // groups].to(f) @ XK[:, h]).to(Q.dtype)
+    a_q_last = (Q[:, :, -1:, :].to(f) @ XQ)[:, :, 0]
+    return A_K, BQ, BK, a_q_last
+
+
+def make_steps(seed: int, n_tokens: int, layers: int, w: dict, hq: int, hkv: int, rho: float, device, dtype):
+    """Per token and layer: q [B,Hq,d], k, v [B,Hkv,d].  q follows q_t = rho q_{t-1} + sqrt(1-rho^2) eps
+    per layer (rho = 0: independent N(0,1) queries, the BASELINE configs' distribution)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    b, d = w["bsz"], w["d"]
+    eps = torch.randn(n_tokens, layers, b, hq, d, generator=g, device=device)
+    q = torch.empty_like(eps)
+    prev = torch.randn(layers, b, hq, d, generator=g, device=device)
+    c = math.sqrt(max(0.0, 1.0 - rho * rho))
+    for t in range(n_tokens):
+        prev = rho * prev + c * eps[t]
+        q[t] = prev
+    k = torch.randn(n_tokens, layers, b, hkv, d, generator=g, device=device)
+    v = torch.randn(n_tokens, layers, b, hkv, d, generator=g, device=device)
+    return q.to(dtype), k.to(dtype), v.to(dtype)
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu_index)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        for ln in self.lines:
+            p = [x.strip() for x in ln.split(",")]
+            if len(p) < 9:
+                continue
+            try:
+                sm.append(float(p[1])); smax.append(float(p[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------
+def measured_hbm_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+def host_link_peak_gbs(device) -> float:
+    """Pinned host -> device copy bandwidth, best of 5, 256 MiB."""
+    n = 256 << 20
+    h = torch.empty(n, dtype=torch.uint8, pin_memory=True)
+    dv = torch.empty(n, dtype=torch.uint8, device=device)
+    best = 0.0
+    for _ in range(6):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        dv.copy_(h, non_blocking=True)
+        e1.record()
+        e1.synchronize()
+        best = max(best, n / (e0.elapsed_time(e1) * 1e-3) / 1e9)
+    return best
+
+
+def build_layers(w, layers, hq_local, hkv_local, head_offset, device, dtype, seed, n_tokens):
+    from lrqk_b200 import LightAttentionIndicesFactory
+    facs = []
+    groups = w["hq"] // w["hkv"]
+    for li in range(layers):
+        Q, K, V = make_prompt(seed + 100 * li + head_offset, w, hq_local, hkv_local, device, dtype)
+        A_K, BQ, BK, a_q_last = factor_state(Q, K, w["r"], groups, w["max_iter"][0], seed + 7 + li)
+        fac = LightAttentionIndicesFactory(num_lite_tokens=w["m"], attn_topk=w["k"], num_key_value_groups=groups,
+                                           r=w["r"], max_iter=w["max_iter"], tol=w["tol"],
+                                           capacity=w["seq"] + n_tokens + 2 * w["m"] + 64, scaling_ratio=1.0)
+        # first resident set: the prompt-time selection with the last prompt query's factors
+        fac.load_state(A_K=A_K, B_Q=BQ.to(dtype), B_K=BK.to(dtype), keys=K, values=V,
+                       table=torch.zeros(w["bsz"], hq_local, w["k"], dtype=torch.int32, device=device))
+        st = fac.state
+        st.score_topk(a_q_last.to(dtype).contiguous(), w["seq"] - w["m"])
+        st.table.copy_(st.wanted)
+        st.fill_resident(K, V)
+        facs.append(fac)
+        del Q, K, V, A_K
+    torch.cuda.synchronize()
+    return facs
+
+
+def stage_bytes(w, hq, hkv, cand, misses, e=2):
+    """Algorithmic bytes per layer-step of each kernel (N = B*Hq heads on this rank)."""
+    n = w["bsz"] * hq
+    k, m, r, d = w["k"], w["m"], w["r"], w["d"]
+    return {
+        "lite_append": n * 2 * d * e + w["bsz"] * hkv * 2 * d * e,
+        "project_update": n * (k + m) * (d + r) * e + 4 * n * r * d * e,
+        "score_topk": n * cand * r * e + n * k * 4,
+        "slot_diff": 3 * n * k * 4 + n * k,
+        "miss_gather": misses * 2 * d * e,
+        "flash_decode": n * (k + m) * 2 * d * e + 2 * n * d * e,
+    }
+
+
+def run_ours(args):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    w = WORKLOADS[args.workload]
+    dtype = torch.float32 if args.workload == "cfg0" else torch.bfloat16
+    if w["hkv"] % world != 0:
+        raise SystemExit(f"{w['hkv']} KV heads do not shard over {world} ranks")
+    hkv_l, hq_l = w["hkv"] // world, w["hq"] // world
+    n_tokens = args.warmup + 3 * args.steps + 8
+    layers = args.layers
+    t_setup = time.time()
+    facs = build_layers(w, layers, hq_l, hkv_l, rank * 1000, device, dtype, args.seed, n_tokens)
+    q_all, k_all, v_all = make_steps(args.seed + 1 + rank, n_tokens, layers, w, hq_l, hkv_l, args.rho, device, dtype)
+    gathered = torch.empty(world, w["bsz"], hq_l, w["d"], dtype=dtype, device=device) if world > 1 else None
+    setup_s = time.time() - t_setup
+
+    def token(t, sink=None):
+        for li, fac in enumerate(facs):
+            out = fac.decode_attend(q_all[t, li], k_all[t, li], v_all[t, li])
+            if world > 1:
+                dist.all_gather_into_tensor(gathered, out.squeeze(2))
+            if sink is not None:
+                sink[li].copy_(out.squeeze(2), non_blocking=True)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    tcur = 0
+    for _ in range(args.warmup):
+        token(tcur); tcur += 1
+    # ---- device-resident timing ----
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        token(tcur); tcur += 1
+    e1.record()
+    barrier()
+    ms_dev = e0.elapsed_time(e1)
+    # ---- end to end: pinned host inputs, host-visible outputs, one sync per token ----
+    hq_pin = q_all[tcur:tcur + args.steps].cpu().pin_memory()
+    hk_pin = k_all[tcur:tcur + args.steps].cpu().pin_memory()
+    hv_pin = v_all[tcur:tcur + args.steps].cpu().pin_memory()
+    out_pin = torch.empty(layers, w["bsz"], hq_l, w["d"], dtype=dtype).pin_memory()
+    dq, dk, dv = torch.empty_like(q_all[0]), torch.empty_like(k_all[0]), torch.empty_like(v_all[0])
+    barrier()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    for i in range(args.steps):
+        dq.copy_(hq_pin[i], non_blocking=True); dk.copy_(hk_pin[i], non_blocking=True); dv.copy_(hv_pin[i], non_blocking=True)
+        for li, fac in enumerate(facs):
+            out = fac.decode_attend(dq[li], dk[li], dv[li])
+            if world > 1:
+                dist.all_gather_into_tensor(gathered, out.squeeze(2))
+            out_pin[li].copy_(out.squeeze(2), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    e3.record()
+    barrier()
+    clocks = sampler.stop()
+    ms_e2e = e2.elapsed_time(e3)
+    tcur += args.steps
+    h2d = (dq.numel() + dk.numel() + dv.numel()) * dq.element_size()
+    d2h = out_pin.numel() * out_pin.element_size()
+    # ---- per-kernel timing: the same step issued stage by stage with events in between ----
+    names = ["lite_append", "project_update", "score_topk", "slot_diff", "miss_gather", "flash_decode"]
+    evs, miss_total, cand_seen = [], 0, 0
+    miss_acc = torch.zeros((), dtype=torch.int64, device=device)
+    for _ in range(args.steps):
+        for li, fac in enumerate(facs):
+            st = fac.state
+            fac._reserve()
+            q, k, v = q_all[tcur, li], k_all[tcur, li], v_all[tcur, li]
+            slot, position, flush_rows, host_row, cand = fac._step_counters()
+            cand_seen = cand
+            marks = [torch.cuda.Event(enable_timing=True) for _ in range(7)]
+            marks[0].record()
+            st.lite_append(k, v, slot, position, flush_rows, host_row); marks[1].record()
+            st.project_update(q, k, w["max_iter"][1], w["tol"], position); marks[2].record()
+            st.score_topk(st.q_hat, cand); marks[3].record()
+            st.slot_diff(); marks[4].record()
+            st.miss_gather(); marks[5].record()
+            st.flash_decode(q); marks[6].record()
+            miss_acc += st.miss_count.sum()
+            evs.append(marks)
+        tcur += 1
+    torch.cuda.synchronize()
+    stage_us = {n: statistics.mean(m[i].elapsed_time(m[i + 1]) for m in evs) * 1e3 for i, n in enumerate(names)}
+    misses_per_step = float(miss_acc.item()) / len(evs)
+    miss_rate = misses_per_step / (w["bsz"] * hq_l * w["k"])
+
+    # max over ranks
+    vals = torch.tensor([ms_dev, ms_e2e], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+    ms_dev, ms_e2e = vals.tolist()
+    us_per_layer = ms_dev * 1e3 / (args.steps * layers)
+    us_per_layer_e2e = ms_e2e * 1e3 / (args.steps * layers)
+
+    hbm_peak, peak_kind = measured_hbm_peak()
+    link_peak = host_link_peak_gbs(device)
+    bytes_ = stage_bytes(w, hq_l, hkv_l, cand_seen, misses_per_step, e=2 if dtype == torch.bfloat16 else 4)
+    per_kernel = {}
+    for n in names:
+        gbs = bytes_[n] / (stage_us[n] * 1e-6) / 1e9 if stage_us[n] > 0 else 0.0
+        bound = "host_link" if n == "miss_gather" else "hbm"
+        peak = link_peak if n == "miss_gather" else hbm_peak
+        per_kernel[n] = {"us": round(stage_us[n], 2), "bytes": int(bytes_[n]), "bound": bound,
+                         "achieved": round(gbs, 1), "peak": round(peak, 1), "unit": "GB/s", "frac": round(gbs / peak, 4)}
+    dominant = max(names, key=lambda n: stage_us[n])
+    roof = dict(per_kernel[dominant])
+    roof.update({"kernel": dominant, "traffic": None,
+                 "peak_source": ("MEASURED_PEAKS.json hbm_gbs" if peak_kind == "measured" else "fallback 6650 GB/s")
+                 if dominant != "miss_gather" else "pinned host->device cudaMemcpy measured in this run"})
+    hbm_kernel = max((n for n in names if n != "miss_gather"), key=lambda n: stage_us[n])
+    roof_hbm = dict(per_kernel[hbm_kernel]); roof_hbm["kernel"] = hbm_kernel
+    roof_hbm["peak_source"] = "MEASURED_PEAKS.json hbm_gbs" if peak_kind == "measured" else "fallback 6650 GB/s"
+
+    line = {
+        "metric": "decode_us_per_layer_128k" if args.workload == "cfg2-layer" else f"decode_us_per_layer_{args.workload}",
+        "value": round(us_per_layer, 2), "unit": "us/layer/step", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms_dev / args.steps, 4), "higher_is_better": False,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16" if dtype == torch.bfloat16 else "f32",
+        "data": "synthetic",
+        "config": {"workload": args.workload, **{k2: (list(v2) if isinstance(v2, tuple) else v2) for k2, v2 in w.items()},
+                   "layers_cycled": layers, "query_rho": args.rho, "sharding": f"kv-heads/{world}",
+                   "l2": "inputs larger than L2: each layer's A_K is %.0f MB and %d layer states are cycled"
+                         % (w["bsz"] * hq_l * w["seq"] * w["r"] * 2 / 1e6, layers)},
+        "tokens_per_s_8b_equiv": round(1e6 / (us_per_layer * 32), 2),
+        "miss_rate": round(miss_rate, 4), "setup_s": round(setup_s, 1),
+        "e2e": {"value": round(us_per_layer_e2e, 2), "unit": "us/layer/step", "h2d_bytes_per_step": int(h2d),
+                "d2h_bytes_per_step": int(d2h)},
+        "gpu_launches": int(args.steps * layers * 7),
+        "roofline": roof, "roofline_hbm": roof_hbm, "kernels": per_kernel,
+        "host_link_peak_gbs": round(link_peak, 1), "clocks": clocks,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline_from_state(facs[0], w, q_all, k_all, v_all, tcur, n_steps=5)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    for fac in facs:
+        fac.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU legs (the only code here that may touch oracle/)
+# ------------------------------------------------------------------------------------------------
+def _oracle():
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import lrqk_oracle
+    return lrqk_oracle
+
+
+def oracle_layer_from_tensors(orc, w, A_K, B_Q, B_K, Kres, Vres, table, host, host_len, cur_len, lite_indices, lite_len):
+    lay = orc.OracleLayer(w["r"], w["k"], w["m"], w["hq"] // w["hkv"], w["max_iter"], (w["tol"], w["tol"]),
+                          capacity=A_K.shape[2], faithful=True)
+    lay.A_K, lay.a_len = A_K, cur_len
+    lay.B_Q, lay.B_K, lay.Kres, lay.Vres = B_Q, B_K, Kres, Vres
+    lay.table = table
+    lay.host, lay.host_len = host, host_len
+    lay.current_len, lay.lite_indices, lay.lite_len = cur_len, list(lite_indices), lite_len
+    return lay
+
+
+def time_oracle_steps(orc, lay, steps_qkv, warmup: int):
+    times = []
+    for i, (q, k, v) in enumerate(steps_qkv):
+        t0 = time.perf_counter()
+        lay.decode(q, k, v, want_attention=True)
+        dt = time.perf_counter() - t0
+        lay.trace.clear()
+        if i >= warmup:
+            times.append(dt)
+    return times
+
+
+def cpu_baseline_from_state(fac, w, q_all, k_all, v_all, tcur, n_steps):
+    """The oracle's decode step (the reference's op sequence on torch CPU, fp32 arithmetic on the
+    bf16-stored state) on layer 0's current state, a few steps, on this box's host cores."""
+    orc = _oracle()
+    st = fac.state
+    lay = oracle_layer_from_tensors(
+        orc, w, st.A_K.cpu(), st.B_Q.cpu(), st.B_K.cpu(), st.K_res.cpu(), st.V_res.cpu(),
+        st.table.cpu().numpy().copy(), st.host.data.clone(), st.host.current_len, fac.current_len,
+        fac.lite_indices, fac.lite_len)
+    steps = [(q_all[tcur - 1 - i, 0].cpu().unsqueeze(2), k_all[tcur - 1 - i, 0].cpu().unsqueeze(2),
+              v_all[tcur - 1 - i, 0].cpu().unsqueeze(2)) for i in range(n_steps + 2)]
+    times = time_oracle_steps(orc, lay, steps, warmup=2)
+    return {"value": round(statistics.median(times) * 1e6, 1), "unit": "us/layer/step", "cores": torch.get_num_threads(),
+            "kind": "port", "sample": f"{len(times)} decode steps of one layer (after 2 warm-up steps), median",
+            "host_cpus": os.cpu_count()}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    orc = _oracle()
+    w = WORKLOADS[args.workload]
+    dtype = torch.float32 if args.workload == "cfg0" else torch.bfloat16
+    dev = torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
+    groups = w["hq"] // w["hkv"]
+    # one layer's state; the heavy Gram products of the synthetic set-up run wherever is fastest,
+    # the timed decode steps run on the host cores only
+    Q, K, V = make_prompt(args.seed, w, w["hq"], w["hkv"], dev, dtype)
+    A_K, BQ, BK, a_q_last = factor_state(Q, K, w["r"], groups, w["max_iter"][0], args.seed + 7)
+    A_K, BQ, BK, a_q_last, K, V = (x.cpu() for x in (A_K, BQ.to(dtype), BK.to(dtype), a_q_last.to(dtype), K, V))
+    del Q
+    s, m, k, d = w["seq"], w["m"], w["k"], w["d"]
+    n_tokens = args.warmup + args.steps
+    cap = s + n_tokens + 2 * m + 64
+    A_full = torch.zeros(w["bsz"], w["hq"], cap, w["r"], dtype=dtype); A_full[:, :, :s] = A_K
+    host = torch.zeros(w["bsz"], w["hkv"], cap, 2 * d, dtype=dtype); host[:, :, :s] = torch.cat([K, V], -1)
+    table = orc.topk_sorted(orc.proxy_scores(A_K[:, :, :s - m], a_q_last[:, :, None]), k)
+    idx = torch.from_numpy(table.astype("int64"))[..., None].expand(-1, -1, -1, d)
+    Krep, Vrep = orc.expand_kv_heads(K, groups), orc.expand_kv_heads(V, groups)
+    Kres = torch.cat([torch.gather(Krep, 2, idx), Krep[:, :, s - m:]], 2).contiguous()
+    Vres = torch.cat([torch.gather(Vrep, 2, idx), Vrep[:, :, s - m:]], 2).contiguous()
+    lay = oracle_layer_from_tensors(orc, w, A_full, BQ, BK, Kres, Vres, table, host, s, s, range(s - m, s), 0)
+    q_all, k_all, v_all = make_steps(args.seed + 1, n_tokens, 1, w, w["hq"], w["hkv"], args.rho, torch.device("cpu"), dtype)
+    steps = [(q_all[t, 0].unsqueeze(2), k_all[t, 0].unsqueeze(2), v_all[t, 0].unsqueeze(2)) for t in range(n_tokens)]
+    t0 = time.perf_counter()
+    times = time_oracle_steps(orc, lay, steps, warmup=args.warmup)
+    us = statistics.mean(times) * 1e6
+    cores = torch.get_num_threads()
+    line = {
+        "impl": "reference",
+        "metric": "decode_us_per_layer_128k" if args.workload == "cfg2-layer" else f"decode_us_per_layer_{args.workload}",
+        "value": round(us, 1), "unit": "us/layer/step", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(us / 1e3, 3), "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16" if dtype == torch.bfloat16 else "f32", "data": "synthetic",
+        "config": {"workload": args.workload, **{k2: (list(v2) if isinstance(v2, tuple) else v2) for k2, v2 in w.items()},
+                   "layers_cycled": 1, "query_rho": args.rho},
+        "cpu_baseline": {"value": round(us, 1), "unit": "us/layer/step", "cores": cores, "kind": "port",
+                         "sample": f"{len(times)} decode steps of one layer on the host cores "
+                                   f"(torch CPU ops in the reference's order + C row gather), mean"},
+        "e2e": {"value": round(us, 1), "unit": "us/layer/step", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": round(time.perf_counter() - t0, 1),
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg2-layer", choices=sorted(WORKLOADS))
+    ap.add_argument("--layers", type=int, default=8)
+    ap.add_argument("--rho", type=float, default=0.0)
+    ap.add_argument("--seed", type=int, default=2024)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

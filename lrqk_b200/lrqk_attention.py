@@ -1,0 +1,633 @@
+"""Host-side mirror of the reference's ``lrqk_attention`` module for the decode path.
+
+Same class names, constructor arguments, defaults and return conventions as the reference
+(paths below are relative to its checkout):
+
+* ``InitAQAK``                         -- lrqk_attention.py:140-143
+* ``AutoIncreaseTensor`` (+ ``SharedKV``), ``PreAllocatedTensor``, ``_CacheQKV``
+                                       -- lrqk_attention.py:844-1028
+* ``LightAttentionIndicesFactory``     -- lrqk_attention.py:1031-1613
+* ``LightAttentionIndicesNoHitMiss``   -- lrqk_attention.py:1683-1775
+* ``DynamicLRQKCache``                 -- lrqk_attention.py:1778-1970
+
+What differs is where the work happens: every numerical or data-moving stage is a CUDA kernel
+of ``liblrqk_sm100.so`` working on pre-allocated state (``LayerState``); Python keeps only the
+integer bookkeeping the reference also keeps in Python (ring slot, lengths, candidate count).
+A decode step performs no host synchronisation.  There is no CPU path: without a CUDA device
+the constructors of the compute classes raise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+from collections import defaultdict
+from typing import Dict, List, Optional, Tuple, Union
+
+import torch
+
+from . import _lib
+from .state import HostStore, LayerState, _ptr, _stream
+
+try:  # HF is only needed for the Cache base class
+    from transformers import cache_utils as _cache_utils
+    _CacheBase = _cache_utils.Cache
+except Exception:  # pragma: no cover
+    _cache_utils = None
+    _CacheBase = object
+
+
+def _pair(x):
+    if isinstance(x, (tuple, list)):
+        if len(x) != 2:
+            raise AssertionError("must be a tuple or list of length 2")
+        return tuple(x)
+    return (x, x)
+
+
+class InitAQAK(enum.Enum):
+    randn = enum.auto()
+    top = enum.auto()
+    topcol = enum.auto()
+
+
+def _resolve_init(method: Union[InitAQAK, str]) -> InitAQAK:
+    if isinstance(method, str):
+        if method not in InitAQAK.__members__:
+            raise ValueError(f"Unknown init_method: {method}. Current support {list(InitAQAK.__members__.keys())}")
+        return InitAQAK[method]
+    if not isinstance(method, InitAQAK):
+        raise ValueError(f"Unknown init_method: {method}")
+    return method
+
+
+def repeat_kv(x: torch.Tensor, n_rep: int) -> torch.Tensor:
+    """[B,Hkv,S,d] -> [B,Hkv*n_rep,S,d] (view-expand then reshape), as HF's repeat_kv."""
+    if n_rep == 1:
+        return x
+    b, h, s, d = x.shape
+    return x[:, :, None, :, :].expand(b, h, n_rep, s, d).reshape(b, h * n_rep, s, d)
+
+
+# ------------------------------------------------------------------------------------------------
+# containers
+# ------------------------------------------------------------------------------------------------
+class AutoIncreaseTensor:
+    """Growable, zero-initialised tensor along one axis (lrqk_attention.py:844-956): first
+    allocation ``max(capacity, int(len * scaling_ratio))``, later growth by ``scaling_ratio``
+    until the data fits, new space zeroed."""
+
+    def __init__(self, capacity: int = 4096, dim: int = 0, scaling_ratio: float = 1.5,
+                 device: Optional[torch.device] = None, dtype: Optional[torch.dtype] = None,
+                 pin_memory: bool = False):
+        self.capacity, self.dim, self.scaling_ratio = capacity, dim, scaling_ratio
+        self.device, self.dtype, self.pin_memory = device, dtype, pin_memory
+        self.data: Optional[torch.Tensor] = None
+        self.current_len = 0
+
+    def _alloc(self, shape):
+        pin = self.pin_memory and torch.cuda.is_available()
+        return torch.zeros(shape, device=self.device, dtype=self.dtype, pin_memory=pin)
+
+    def reserve(self, target_length: int) -> bool:
+        """Make room for `target_length` entries; True if the buffer was reallocated."""
+        if self.data is None or target_length < self.capacity:
+            return False
+        new_cap = self.capacity
+        while new_cap <= target_length:
+            new_cap = int(new_cap * self.scaling_ratio)
+        shape = list(self.data.shape)
+        shape[self.dim] = new_cap
+        grown = self._alloc(shape)
+        grown.narrow(self.dim, 0, self.current_len).copy_(self.data.narrow(self.dim, 0, self.current_len))
+        self.data, self.capacity = grown, new_cap
+        return True
+
+    @torch.inference_mode()
+    def append(self, x: torch.Tensor):
+        if self.device is None:
+            self.device = x.device
+        if self.dtype is None:
+            self.dtype = x.dtype
+        length = x.size(self.dim)
+        if self.data is None:
+            cap = max(self.capacity, int(length * self.scaling_ratio))
+            shape = list(x.shape)
+            shape[self.dim] = cap
+            self.data, self.capacity = self._alloc(shape), cap
+        else:
+            self.reserve(self.current_len + length)
+        self.data.narrow(self.dim, self.current_len, length).copy_(x.to(self.device, self.dtype))
+        self.current_len += length
+
+    def has_data(self):
+        return self.data is not None
+
+    @property
+    def shape(self) -> torch.Size:
+        s = list(self.data.shape)
+        s[self.dim] = self.current_len
+        return torch.Size(s)
+
+    def tensor(self) -> torch.Tensor:
+        return self.data.narrow(self.dim, 0, self.current_len)
+
+    def __len__(self):
+        return self.current_len
+
+    def __getitem__(self, idx):
+        if self.data is None:
+            raise IndexError("Cache is empty")
+        return self.tensor()[idx]
+
+    def take_along_dim(self, indices: torch.Tensor, dim: int = None, out=None) -> torch.Tensor:
+        if self.data is None:
+            raise IndexError("Cache is empty")
+        return torch.take_along_dim(self.data, indices, self.dim if dim is None else dim, out=out)
+
+
+class AutoIncreaseTensorSharedKV(AutoIncreaseTensor):
+    """K and V concatenated on the last axis (lrqk_attention.py:959-963)."""
+
+    def append(self, k: torch.Tensor, v: torch.Tensor):
+        return super().append(torch.cat([k, v], dim=-1))
+
+
+class PreAllocatedTensor:
+    """Fixed-capacity tensor for prompts shorter than the active set (lrqk_attention.py:966-1011)."""
+
+    def __init__(self, capacity: int, dim: int, dtype: torch.dtype = None, device: torch.device = None):
+        self.capacity, self.dim, self.dtype, self.device = capacity, dim, dtype, device
+        self.data = None
+        self.current_len = 0
+
+    @classmethod
+    def from_tensor(cls, capacity: int, dim: int, data: torch.Tensor):
+        out = cls(capacity, dim, data.dtype, data.device)
+        out.append(data)
+        return out
+
+    def append(self, x: torch.Tensor):
+        self.dtype = x.dtype if self.dtype is None else self.dtype
+        self.device = x.device if self.device is None else self.device
+        n = x.shape[self.dim]
+        if self.data is None:
+            shape = list(x.shape)
+            shape[self.dim] = self.capacity
+            self.data = torch.empty(shape, dtype=self.dtype, device=self.device)
+        if self.current_len + n > self.capacity:
+            raise ValueError("Not enough capacity to store the tensor")
+        self.data.narrow(self.dim, self.current_len, n).copy_(x)
+        self.current_len += n
+
+    def has_data(self):
+        return self.data is not None
+
+    def tensor(self) -> torch.Tensor:
+        return self.data.narrow(self.dim, 0, self.current_len)
+
+    def __len__(self):
+        return self.current_len
+
+    def __getitem__(self, idx):
+        return self.tensor()[idx]
+
+
+class _CacheQKV:
+    def __init__(self, capacity: int, dim: int, dtype: torch.dtype = None, device: torch.device = None):
+        self.Q = PreAllocatedTensor(capacity, dim, dtype, device)
+        self.K = PreAllocatedTensor(capacity, dim, dtype, device)
+        self.V = PreAllocatedTensor(capacity, dim, dtype, device)
+
+    def append(self, Q, K, V):
+        self.Q.append(Q)
+        self.K.append(K)
+        self.V.append(V)
+        return self.Q.tensor(), self.K.tensor(), self.V.tensor()
+
+    def __len__(self):
+        return self.Q.current_len
+
+
+class _HostKVView:
+    """What the reference exposes as ``factory.KVcpu``: ``.data`` [B,Hkv,capacity,2d] in
+    page-locked host memory and the filled length."""
+
+    def __init__(self, store: HostStore):
+        self._store = store
+
+    @property
+    def data(self) -> torch.Tensor:
+        return self._store.data
+
+    @property
+    def current_len(self) -> int:
+        return self._store.current_len
+
+    @property
+    def capacity(self) -> int:
+        return self._store.capacity
+
+    def tensor(self) -> torch.Tensor:
+        return self._store.data.narrow(2, 0, self._store.current_len)
+
+    def __len__(self):
+        return self._store.current_len
+
+
+# ------------------------------------------------------------------------------------------------
+# the per-layer engine
+# ------------------------------------------------------------------------------------------------
+class LightAttentionIndicesFactory:
+    """Per-layer selection engine: lrqk_attention.py:1031-1613.
+
+    ``prefill(q, k, v)`` factorises the prompt, stores K|V in page-locked host memory, selects
+    the first resident set and fills the lite ring.  ``decode(q, k, v)`` performs one step and
+    returns the resident ``(K, V)`` of shape [B,Hq,k+m,d] exactly like the reference;
+    ``decode_attend`` additionally runs the attention kernel and returns its output, which is
+    what the patched attention modules use.
+
+    ``weights`` other than all-ones is not supported (the reference's cache never passes it,
+    lrqk_attention.py:1811-1820).  Prompts must be longer than ``attn_topk + num_lite_tokens``.
+    """
+
+    def __init__(self, num_lite_tokens: int = 1, attn_topk: int = 128, num_key_value_groups: int = 1,
+                 r: int = 16, max_iter: Union[int, Tuple[int, int]] = 2,
+                 tol: Union[float, Tuple[float, float]] = 1e-4,
+                 weights: Tuple[float, float, float, float] = (1.0, 1.0, 1.0, 1.0), capacity: int = 4096,
+                 init_aq_ak_method: Union[InitAQAK, str] = InitAQAK.randn, scaling_ratio: float = 1.5,
+                 device: Optional[torch.device] = None, dtype: Optional[torch.dtype] = None):
+        self.num_lite_tokens, self.attn_topk, self.dim = num_lite_tokens, attn_topk, 2
+        self.num_key_value_groups, self.r = num_key_value_groups, r
+        self.max_iter, self.tol = _pair(max_iter), _pair(tol)
+        self.init_aq_ak_method = init_aq_ak_method
+        self.gpu_capacity = attn_topk + num_lite_tokens
+        self.prefill_length = 0
+        self.current_len = 0
+        if isinstance(weights, float):
+            weights = (weights,) * 4
+        if not isinstance(weights, tuple) or len(weights) != 4:
+            raise ValueError("weights must be a float or a tuple of length 4")
+        if any(w != 1.0 for w in weights):
+            raise NotImplementedError("only unit weights are implemented by the sm_100a kernels")
+        self.weights = weights
+        self.capacity, self.scaling_ratio = capacity, scaling_ratio
+        self.device, self.dtype = device, dtype
+        self.lite_len = 0
+        self.lite_indices: List[int] = [-1] * num_lite_tokens
+        self.state: Optional[LayerState] = None
+        self.verbose = False
+        self._hook = type(self).only_indices_in_cpu is not LightAttentionIndicesFactory.only_indices_in_cpu
+
+    # ---- views on the device state (names as in the reference) ---------------------------------
+    def __len__(self):
+        return self.current_len
+
+    @property
+    def Kgpu(self):
+        return None if self.state is None else self.state.K_res
+
+    @property
+    def Vgpu(self):
+        return None if self.state is None else self.state.V_res
+
+    @property
+    def B_Q(self):
+        return None if self.state is None else self.state.B_Q
+
+    @property
+    def B_K(self):
+        return None if self.state is None else self.state.B_K
+
+    @property
+    def A_K(self):
+        return self.state.A_K.narrow(2, 0, self.current_len)
+
+    @property
+    def KVcpu(self):
+        return _HostKVView(self.state.host)
+
+    @property
+    def hit_indices(self) -> Optional[torch.Tensor]:
+        """int64 [B,Hq,k,1], the position held by each selected slot (a copy of the device table)."""
+        return None if self.state is None else self.state.table.to(torch.int64).unsqueeze(-1)
+
+    @property
+    def Klite(self):
+        return self.Kgpu[:, ::self.num_key_value_groups, self.attn_topk:self.gpu_capacity, :]
+
+    @property
+    def Vlite(self):
+        return self.Vgpu[:, ::self.num_key_value_groups, self.attn_topk:self.gpu_capacity, :]
+
+    # ---- selection primitives kept callable, as in the reference -----------------------------------
+    def compute_hit_indices(self, query_states: torch.Tensor, key_states: torch.Tensor) -> torch.Tensor:
+        """Ascending top-k positions of key_states . query_states (lrqk_attention.py:1235-1273).
+        query_states [B,H,1,r]; key_states [B,H,c,r] must be a prefix view of this layer's A_K."""
+        st = self.state
+        b, h, c, _ = key_states.shape
+        if c <= self.attn_topk:
+            return torch.arange(0, c, device=query_states.device, dtype=torch.long).reshape(1, 1, -1, 1).expand(b, h, -1, 1)
+        if key_states.data_ptr() != st.A_K.data_ptr():
+            raise ValueError("compute_hit_indices scores this layer's own A_K buffer")
+        st.score_topk(query_states.reshape(b, h, self.r).contiguous(), c)
+        return st.wanted.to(torch.int64).unsqueeze(-1)
+
+    def only_indices_in_cpu(self, now_indices: torch.Tensor, new_indices: torch.Tensor):
+        """Set difference of the wanted positions against the resident ones
+        (lrqk_attention.py:1275-1315): returns (updated_indices, mask of refilled slots).
+        Subclasses may override it (the reference's hit-rate counter does); the fused step then
+        falls back to calling this method between the kernels."""
+        st = self.state
+        saved = st.table.clone()
+        st.table.copy_(now_indices.reshape(st.table.shape).to(torch.int32))
+        st.slot_diff(new_indices.reshape(st.table.shape).to(torch.int32).contiguous())
+        updated = st.table.to(torch.int64).reshape(now_indices.shape)
+        mask = st.mask.to(torch.bool).clone()
+        st.table.copy_(saved)
+        return updated, mask
+
+    # ---- prefill --------------------------------------------------------------------------------
+    def _initial_factors(self, Q: torch.Tensor, K: torch.Tensor):
+        """fp32 [B,Hq,S,r] starting factors (lrqk_attention.py:145-209); K is per KV head here and
+        is expanded only for the column gathers."""
+        method = _resolve_init(self.init_aq_ak_method)
+        b, hq, s, d = Q.shape
+        if method == InitAQAK.randn:
+            aq = torch.randn((b, hq, s, self.r), dtype=torch.float32, device=Q.device)
+            ak = torch.randn((b, hq, s, self.r), dtype=torch.float32, device=Q.device)
+            return aq, ak
+        g = self.num_key_value_groups
+        qs = Q.float().abs().sum(dim=2, keepdim=True)
+        ks = repeat_kv(K.float().abs().sum(dim=2, keepdim=True), g)
+        if method == InitAQAK.top:
+            iq = torch.topk(qs, k=self.r, dim=-1).indices
+            ik = torch.topk(ks, k=self.r, dim=-1).indices
+        else:
+            iq = ik = torch.topk(qs + ks, k=self.r, dim=-1).indices
+        aq = torch.gather(Q, -1, iq.expand(-1, -1, s, -1)).float()
+        ik_kv = ik.view(b, K.shape[1], g, 1, self.r)
+        ak = torch.gather(K[:, :, None].expand(-1, -1, g, -1, -1), -1, ik_kv.expand(-1, -1, -1, s, -1))
+        return aq.contiguous(), ak.reshape(b, hq, s, self.r).float().contiguous()
+
+    def _new_state(self, bsz, hq, hkv, d, seq_len, dtype, device) -> LayerState:
+        cap = max(self.capacity, int(seq_len * self.scaling_ratio))   # first allocation, :880
+        return LayerState(bsz, hq, hkv, d, self.r, self.attn_topk, self.num_lite_tokens, a_capacity=cap,
+                          host_capacity=cap, dtype=dtype, device=device, max_iter=self.max_iter[1])
+
+    @torch.inference_mode()
+    def prefill(self, query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor):
+        bsz, hq, seq_len, d = query_states.shape
+        hkv = key_states.shape[1]
+        assert seq_len >= self.attn_topk, "seq_len must be larger than attn_topk"
+        if hq != hkv * self.num_key_value_groups:
+            raise ValueError("num_key_value_groups does not match the head counts of q and k")
+        if seq_len <= self.gpu_capacity + 1:
+            raise NotImplementedError("prompts not longer than attn_topk + num_lite_tokens + 1 are not supported")
+        q = query_states.contiguous()
+        k = key_states.contiguous()
+        v = value_states.contiguous()
+        st = self.state = self._new_state(bsz, hq, hkv, d, seq_len, q.dtype, q.device)
+        self.prefill_length = self.current_len = seq_len
+        aq, ak = self._initial_factors(q, k)
+        nb = st.lib.lrqk_prefill_factorize_workspace_bytes(C.byref(st.c), seq_len)
+        ws = torch.empty((max(nb, 16),), dtype=torch.uint8, device=q.device)
+        a_q_last = torch.empty((bsz, hq, self.r), dtype=q.dtype, device=q.device)
+        _lib.check(st.lib.lrqk_prefill_factorize(C.byref(st.c), _ptr(q), _ptr(k), _ptr(aq), _ptr(ak), seq_len,
+                                                 self.max_iter[0], self.tol[0], _ptr(a_q_last), None, _ptr(ws),
+                                                 _stream()), "lrqk_prefill_factorize")
+        st.kv_pack_host(k, v, 0)
+        st.host.current_len = seq_len
+        st.score_topk(a_q_last, seq_len - self.num_lite_tokens)       # candidates 0 .. S-m-1, :1471-1474
+        st.table.copy_(st.wanted)
+        st.fill_resident(k, v)
+        self.lite_indices = list(range(seq_len - self.num_lite_tokens, seq_len))
+        self.lite_len = 0
+        del aq, ak, ws
+
+    def load_state(self, *, A_K, B_Q, B_K, keys, values, table, dtype=None):
+        """Adopt factors and a first resident set produced elsewhere (same layout as after
+        ``prefill``): A_K [B,Hq,S,r], B_Q/B_K [B,Hq,r,d], keys/values [B,Hkv,S,d] on the device,
+        table int [B,Hq,k] ascending.  Fills the host store, the slots and the lite ring."""
+        bsz, hq, seq_len, _ = A_K.shape
+        hkv, d = keys.shape[1], keys.shape[3]
+        dtype = keys.dtype if dtype is None else dtype
+        st = self.state = self._new_state(bsz, hq, hkv, d, seq_len, dtype, keys.device)
+        self.prefill_length = self.current_len = seq_len
+        st.A_K[:, :, :seq_len].copy_(A_K)
+        st.B_Q.copy_(B_Q)
+        st.B_K.copy_(B_K)
+        st.table.copy_(table)
+        k, v = keys.to(dtype).contiguous(), values.to(dtype).contiguous()
+        st.kv_pack_host(k, v, 0)
+        st.host.current_len = seq_len
+        st.fill_resident(k, v)
+        self.lite_indices = list(range(seq_len - self.num_lite_tokens, seq_len))
+        self.lite_len = 0
+
+    # ---- decode ---------------------------------------------------------------------------------
+    def _reserve(self):
+        st = self.state
+        if self.current_len + 1 >= st.A_K.shape[2]:                     # growth rule, :892-897
+            new_cap = st.A_K.shape[2]
+            while new_cap <= self.current_len + 1:
+                new_cap = int(new_cap * self.scaling_ratio)
+            grown = torch.zeros((st.bsz, st.q_heads, new_cap, st.r), dtype=st.dtype, device=st.device)
+            grown[:, :, :self.current_len].copy_(st.A_K[:, :, :self.current_len])
+            st.A_K = grown
+            st._rebuild_struct()
+        if st.host.current_len + self.num_lite_tokens >= st.host.capacity:
+            torch.cuda.synchronize()
+            new_cap = st.host.capacity
+            while new_cap <= st.host.current_len + self.num_lite_tokens:
+                new_cap = int(new_cap * self.scaling_ratio)
+            new = HostStore(st.bsz, st.kv_heads, new_cap, st.head_dim, st.dtype)
+            new.data[:, :, :st.host.current_len].copy_(st.host.data[:, :, :st.host.current_len])
+            new.current_len = st.host.current_len
+            st.host.close()
+            st.host = new
+            st._rebuild_struct()
+
+    def _step_counters(self):
+        """Advance the Python-side counters exactly as _append does (lrqk_attention.py:1174-1196)
+        and derive the candidate count of this step (:1562-1568)."""
+        m = self.num_lite_tokens
+        slot, position = self.lite_len, self.current_len
+        self.lite_indices[slot] = position
+        self.lite_len += 1
+        self.current_len += 1
+        flush_rows, host_row = 0, self.state.host.current_len
+        if self.lite_len >= m:
+            flush_rows = m
+            self.state.host.current_len += m
+            self.lite_len = 0
+        candidates = self.lite_indices[self.lite_len] - 1
+        return slot, position, flush_rows, host_row, candidates
+
+    def _flat(self, x: torch.Tensor, heads: int) -> torch.Tensor:
+        st = self.state
+        if x.shape[0] != st.bsz or x.shape[1] != heads or x.shape[-1] != st.head_dim or x.numel() != st.bsz * heads * st.head_dim:
+            raise ValueError(f"decode expects [B,{heads},1,{st.head_dim}], got {tuple(x.shape)}")
+        return x.reshape(st.bsz, heads, st.head_dim).contiguous()
+
+    @torch.inference_mode()
+    def _decode(self, query_states, key_states, value_states, attention: bool):
+        st = self.state
+        if st is None:
+            raise RuntimeError("decode before prefill")
+        if self.current_len <= self.gpu_capacity:
+            raise NotImplementedError("decode with fewer tokens than resident slots is not supported")
+        self._reserve()
+        q = self._flat(query_states.to(st.dtype), st.q_heads)
+        k = self._flat(key_states.to(st.dtype), st.kv_heads)
+        v = self._flat(value_states.to(st.dtype), st.kv_heads)
+        slot, position, flush_rows, host_row, candidates = self._step_counters()
+        if not self._hook:
+            st.layer_step(st.make_step_args(q, k, v, slot, position, flush_rows, host_row, candidates,
+                                            self.max_iter[1], self.tol[1], attention=attention))
+        else:
+            # a subclass observes or replaces the difference: run the stages one by one
+            st.lite_append(k, v, slot, position, flush_rows, host_row)
+            st.project_update(q, k, self.max_iter[1], self.tol[1], position)
+            st.score_topk(st.q_hat, candidates)
+            now = st.table.to(torch.int64).unsqueeze(-1)
+            new = st.wanted.to(torch.int64).unsqueeze(-1)
+            updated, mask = self.only_indices_in_cpu(now, new)
+            mask = mask.reshape(st.table.shape)
+            st.table.copy_(updated.reshape(st.table.shape).to(torch.int32))
+            st.mask.copy_(mask.to(torch.uint8))
+            idx = mask.reshape(-1, st.k).nonzero()
+            n = idx.shape[0]
+            st.miss_list[:n, 0] = idx[:, 0].int()
+            st.miss_list[:n, 1] = idx[:, 1].int()
+            st.miss_list[:n, 2] = st.table.reshape(-1, st.k)[idx[:, 0], idx[:, 1]]
+            st.counters[0] = n
+            st.miss_gather()
+            if attention:
+                st.flash_decode(q)
+        return st
+
+    def decode(self, query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor):
+        """One step; returns the resident (K, V) [B,Hq,k+m,d] (lrqk_attention.py:1506-1613)."""
+        st = self._decode(query_states, key_states, value_states, attention=False)
+        return st.K_res, st.V_res
+
+    def decode_attend(self, query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor,
+                      ) -> torch.Tensor:
+        """One step including the attention over the resident rows; returns [B,Hq,1,d] (a view
+        of a buffer that the next step overwrites)."""
+        st = self._decode(query_states, key_states, value_states, attention=True)
+        return st.attn_out.unsqueeze(2)
+
+    def miss_counts(self) -> torch.Tensor:
+        """int32 [B,Hq]: slots refilled by the last step (device tensor; reading it synchronises)."""
+        return self.state.miss_count
+
+    def close(self):
+        if self.state is not None:
+            self.state.close()
+            self.state = None
+
+
+class LightAttentionIndicesNoHitMiss(LightAttentionIndicesFactory):
+    """Comparison mode without the hit/miss table (lrqk_attention.py:1683-1775): every selected
+    row is fetched from the host store on every step."""
+
+    def only_indices_in_cpu(self, now_indices: torch.Tensor, new_indices: torch.Tensor):
+        return new_indices.clone(), torch.ones(new_indices.shape[:3], dtype=torch.bool, device=new_indices.device)
+
+
+# ------------------------------------------------------------------------------------------------
+# the cache object handed to HF models
+# ------------------------------------------------------------------------------------------------
+class DynamicLRQKCache(_CacheBase):
+    """Per-layer state machine pending -> collecting -> decoding: lrqk_attention.py:1778-1970.
+
+    ``update(q, k, v, layer_idx, attention_mask=None)`` returns the un-repeated prompt K, V while
+    prefilling and the resident [B,Hq,k+m,d] pair while decoding.  ``attend(...)`` is the fused
+    variant for patched attention modules: while decoding it returns the attention output
+    itself instead of K, V."""
+
+    class State(enum.Enum):
+        pending = 0
+        collecting = 1
+        decoding = 2
+
+    def __init__(self, r: int = 16, num_active_tokens: int = 512, lambda_Q: float = 1.0, lambda_K: float = 1.0,
+                 max_iter: Union[int, Tuple[int, int]] = 2, lite_tokens: int = 16,
+                 tol: Union[float, Tuple[float, float]] = 1e-2, max_sequence_length: int = 4096,
+                 num_key_value_groups: int = 1, lwattn_factory=LightAttentionIndicesFactory,
+                 init_aq_ak_method: Union[InitAQAK, str] = InitAQAK.randn):
+        if _CacheBase is not object:
+            try:
+                super().__init__(layers=[])
+            except TypeError:  # older HF: Cache.__init__ takes no arguments
+                super().__init__()
+        self.num_key_value_groups, self.r, self.num_active_tokens = num_key_value_groups, r, num_active_tokens
+        self.lambda_Q, self.lambda_K = lambda_Q, lambda_K
+        self.max_iter, self.tol, self.lite_tokens = _pair(max_iter), _pair(tol), lite_tokens
+        self.lwattn: Dict[int, LightAttentionIndicesFactory] = defaultdict(lambda: lwattn_factory(
+            num_lite_tokens=lite_tokens, attn_topk=num_active_tokens, num_key_value_groups=num_key_value_groups,
+            r=r, max_iter=max_iter, tol=tol, capacity=max_sequence_length, init_aq_ak_method=init_aq_ak_method))
+        self.temp_buff_cache_qkv: Dict[int, _CacheQKV] = defaultdict(lambda: _CacheQKV(num_active_tokens, 2))
+        self.sequence_state = defaultdict(lambda: DynamicLRQKCache.State.pending)
+
+    def __getitem__(self, layer_idx: int):
+        raise NotImplementedError("DynamicLRQKCache does not support indexing")
+
+    def __iter__(self):
+        raise NotImplementedError("DynamicLRQKCache does not support iteration")
+
+    def __len__(self):
+        return len(self.sequence_state)
+
+    def get_seq_length(self, layer_idx=0):
+        return len(self.lwattn[layer_idx])
+
+    def get_max_cache_shape(self, *a, **kw) -> Optional[int]:
+        return None
+
+    @property
+    def seen_tokens(self):
+        return self.get_seq_length()
+
+    def is_decoding(self, layer_idx: int) -> bool:
+        return self.sequence_state[layer_idx] == self.State.decoding
+
+    def _prefill_states(self, query_states, key_states, value_states, layer_idx, attention_mask):
+        state = self.sequence_state[layer_idx]
+        bsz, _, seq_len, _ = key_states.shape
+        if state == self.State.pending:
+            if attention_mask is not None:                       # zero padded positions, :1901-1903
+                key_states.mul_(attention_mask.view(bsz, 1, seq_len, 1))
+                value_states.mul_(attention_mask.view(bsz, 1, seq_len, 1))
+            if seq_len < self.num_active_tokens:                 # too short to factorise, :1910-1918
+                self.temp_buff_cache_qkv[layer_idx].append(query_states, key_states, value_states)
+                self.sequence_state[layer_idx] = self.State.collecting
+            else:
+                self.lwattn[layer_idx].prefill(query_states, key_states, value_states)
+                self.sequence_state[layer_idx] = self.State.decoding
+            return key_states, value_states
+        buf = self.temp_buff_cache_qkv[layer_idx]                # collecting, :1928-1958
+        if len(buf) + seq_len < self.num_active_tokens:
+            _, k_all, v_all = buf.append(query_states, key_states, value_states)
+            return k_all, v_all
+        q_all, k_all, v_all = buf.append(query_states, key_states, value_states)
+        self.lwattn[layer_idx].prefill(q_all, k_all, v_all)
+        self.sequence_state[layer_idx] = self.State.decoding
+        del self.temp_buff_cache_qkv[layer_idx]
+        return k_all, v_all
+
+    def update(self, query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor,
+               layer_idx: int, attention_mask: Optional[torch.Tensor] = None):
+        if any(c is None for c in (query_states, key_states, value_states)):
+            raise ValueError("None of query_states, key_states, and value_states can be None")
+        if self.sequence_state[layer_idx] != self.State.decoding:
+            return self._prefill_states(query_states, key_states, value_states, layer_idx, attention_mask)
+        return self.lwattn[layer_idx].decode(query_states, key_states, value_states)
+
+    def attend(self, query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor,
+               layer_idx: int) -> torch.Tensor:
+        """Decode-state only: one step plus attention, returns [B,Hq,1,d]."""
+        if self.sequence_state[layer_idx] != self.State.decoding:
+            raise RuntimeError("attend() is only valid once the layer is decoding; use update() before")
+        return self.lwattn[layer_idx].decode_attend(query_states, key_states, value_states)
