@@ -1,12 +1,19 @@
 // Per-step rank-r projection of (q, k) and update of the right factors B_Q, B_K.
 //
-// Kernel 1 (project): one thread-block cluster per (batch, query head).  The active set -- the k
-// slot-table rows followed by the m lite rows -- is cut over the CTAs of the cluster; each CTA
-// streams its share of the resident keys once (s_j = q . K_j), gathers the matching rank-r rows
-// of A_K and accumulates  w = sum_j s_j a_j  and  G = sum_j a_j^T a_j  in registers.  The
-// partial sums meet in CTA 0 through distributed shared memory, which then runs the r x r
-// solves (LU with partial pivoting, one warp, matrix in shared memory) for every alternation
-// and leaves each iterate in the workspace.
+// Kernel 1 (project): one thread-block cluster per (batch, query head).
+//   * CTA 0 is the solver.  While its peers stream, it loads B_Q and B_K, forms their r x r Gram
+//     matrices and the vectors q B_Q^T, k B_K^T, q k^T, and solves for the initial k_hat.
+//   * CTAs 1.. stream the active set (the k slot-table rows, then the m lite rows), cut into
+//     equal shares: s_j = q . K_j from the resident keys, the matching rank-r rows a_j gathered
+//     from A_K, and the partial sums  w = sum_j s_j a_j,  G = sum_j a_j^T a_j  in registers.
+//     (A cluster of one CTA does both jobs in turn.)
+//   * The partial sums meet in CTA 0 through distributed shared memory; it then runs the
+//     alternating r x r solves and leaves every iterate in the workspace.
+//   Each r x r system is a fixed symmetric positive definite matrix (a Gram matrix) plus a
+//   rank-one term that changes from solve to solve.  The two fixed matrices are inverted once
+//   (Gauss-Jordan without row exchanges, one warp, matrix rows in registers); every solve is
+//   then a Sherman-Morrison update plus one step of iterative refinement, two small
+//   matrix-vector products by one warp, instead of a fresh factorisation on the critical path.
 //
 // Kernel 2 (update): the early-exit test of the reference is a mean over ALL heads, so it can
 // only be evaluated after kernel 1 has finished for every head.  Each CTA (one per head)
@@ -23,7 +30,9 @@ namespace lrqk {
 namespace {
 
 constexpr int kPThreads = 256;
-constexpr int kTileRows = 64;
+constexpr int kPWarps = kPThreads / 32;
+constexpr int kBatch = 8;       // key rows a warp keeps in flight
+constexpr int kGramPart = 4096; // floats of scratch for the per-group partial Gram matrices
 
 template <typename T, int EL> struct RowLoad;
 template <> struct RowLoad<float, 4> {
@@ -57,63 +66,218 @@ struct ProjectParams {
   const int32_t *table, *lite_pos;
   int64_t a_capacity;
   int32_t q_heads, groups, k, m, max_iter, n_heads;
-  float *ws;  // [N][max_iter][2R+2]
+  int32_t tile_rows;  // rows a streaming CTA handles per pass over its buffers
+  float *ws;          // [N][max_iter][2R+2]
 };
 
-// In-place solve of M x = b by LU with partial pivoting, executed by ONE warp.
-// M: R x R, leading dimension LD (destroyed); b: R (overwritten with x).
-template <int R, int LD>
-__device__ void warp_lu_solve(float *M, float *b) {
+// Rows of the streaming buffers (bounded so that the buffers stay near 40 KiB).
+template <int R> constexpr int max_tile_rows() { return R >= 64 ? 160 : (R == 32 ? 320 : 512); }
+
+// 1/x from the hardware approximation plus one Newton step (about 1 ulp); a full IEEE division
+// would sit on the critical path of every elimination column.
+__device__ __forceinline__ float fast_rcp(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return fmaf(fmaf(-x, r, 1.0f), r, r);
+}
+
+// X^T X for a row-major X [nrows][ldx] with R columns, accumulated by all threads of the CTA.
+// The R x R result is cut into 4 x 4 register tiles; the (R/4)^2 threads of a group cover it and
+// the kPThreads / (R/4)^2 groups take every NG-th row each.  A thread loads its four row- and
+// four column-operands with two 16-byte shared-memory loads per row of X.  The per-group
+// partial sums are folded through `part` (kGramPart floats) into `out` (R x R, symmetric to the
+// last bit because both triangles see the same operands in the same order).
+template <int R>
+__device__ __forceinline__ void gram_xtx(const float *X, int ldx, int nrows, float *part, float *out, bool add) {
+  constexpr int TE = R / 4, TG = TE * TE, NG = kPThreads / TG;
+  const int tid = threadIdx.x, grp = tid / TG, ty = (tid % TG) / TE, tx = tid % TE;
+  float acc[4][4];
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[a][c] = 0.0f;
+#pragma unroll 4
+  for (int row = grp; row < nrows; row += NG) {
+    const float4 r4 = *reinterpret_cast<const float4 *>(X + row * ldx + 4 * ty);
+    const float4 c4 = *reinterpret_cast<const float4 *>(X + row * ldx + 4 * tx);
+    const float rr[4] = {r4.x, r4.y, r4.z, r4.w}, cc[4] = {c4.x, c4.y, c4.z, c4.w};
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[a][c] = fmaf(rr[a], cc[c], acc[a][c]);
+  }
+  __syncthreads();  // `part` may still be in use by a previous call
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) part[grp * R * R + (4 * ty + a) * R + 4 * tx + c] = acc[a][c];
+  __syncthreads();
+  for (int i = tid; i < R * R; i += kPThreads) {
+    float s = add ? out[i] : 0.0f;
+#pragma unroll
+    for (int g = 0; g < NG; ++g) s += part[g * R * R + i];
+    out[i] = s;
+  }
+  __syncthreads();
+}
+
+// out[c] = sum_rows coef[row] * X[row][c] for a row-major X [nrows][ldx] with R columns.
+template <int R>
+__device__ __forceinline__ void weighted_colsum(const float *X, int ldx, int nrows, const float *coef, float *part,
+                                                float *out, bool add) {
+  constexpr int NGW = kPThreads / R;
+  const int tid = threadIdx.x, c = tid % R, g = tid / R;
+  float acc = 0.0f;
+#pragma unroll 4
+  for (int row = g; row < nrows; row += NGW) acc = fmaf(coef[row], X[row * ldx + c], acc);
+  __syncthreads();
+  part[g * R + c] = acc;
+  __syncthreads();
+  if (tid < R) {
+    float s = add ? out[tid] : 0.0f;
+#pragma unroll
+    for (int gg = 0; gg < NGW; ++gg) s += part[gg * R + tid];
+    out[tid] = s;
+  }
+  __syncthreads();
+}
+
+// Inverse of a symmetric positive definite G (R x R in shared memory) into Gi, executed by ONE
+// warp with the matrix in registers: lane i owns row i (and i+32 when R = 64) of [G | I].
+// Gauss-Jordan elimination without row exchanges.  In step c the pivot row is non-zero exactly in
+// columns c .. R+c, so each row keeps only that sliding window of R+1 entries; after every step
+// the window is rotated by one so that the pivot column always sits at index 0.  Register
+// indices therefore stay compile-time constants inside a ROLLED loop over the columns (straight-
+// line elimination code would run once per launch and be bound by instruction fetch), and the
+// only communication is the shuffle broadcast of the pivot row.  No barriers.
+template <int R>
+__device__ __forceinline__ void warp_spd_inverse(const float *G, float *Gi) {
+  constexpr int RPL = (R + 31) / 32;
+  constexpr unsigned kFull = 0xFFFFFFFFu;
   const int lane = threadIdx.x & 31;
+  float w[RPL][R + 1], diag[RPL];
+#pragma unroll
+  for (int t = 0; t < RPL; ++t) {
+    const int i = lane + 32 * t;
+#pragma unroll
+    for (int k = 0; k < R; ++k) w[t][k] = i < R ? G[k * R + i] : 0.0f;  // G is symmetric
+    w[t][R] = i == 0 ? 1.0f : 0.0f;                                     // column R: first column of I
+    diag[t] = 1.0f;
+  }
+#pragma unroll 1
   for (int c = 0; c < R; ++c) {
-    float best = -1.0f;
-    int bi = c;
-    for (int i = lane; i < R; i += 32) {
-      if (i >= c) {
-        const float v = fabsf(M[i * LD + c]);
-        if (v > best) { best = v; bi = i; }
-      }
+    const int owner = c & 31, slot = c >> 5;
+    float src0 = w[0][0];
+#pragma unroll
+    for (int t = 1; t < RPL; ++t) src0 = slot == t ? w[t][0] : src0;
+    const float piv = __shfl_sync(kFull, src0, owner);
+    const float rp = fast_rcp(piv);
+    float l[RPL];
+#pragma unroll
+    for (int t = 0; t < RPL; ++t) {
+      const bool is_pivot_row = lane == owner && slot == t;
+      if (is_pivot_row) diag[t] = piv;
+      l[t] = is_pivot_row ? 0.0f : w[t][0] * rp;
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xFFFFFFFFu, best, o);
-      const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
-      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    for (int k = 1; k <= R; ++k) {
+      float src = w[0][k];
+#pragma unroll
+      for (int t = 1; t < RPL; ++t) src = slot == t ? w[t][k] : src;
+      const float pk = __shfl_sync(kFull, src, owner);
+#pragma unroll
+      for (int t = 0; t < RPL; ++t) w[t][k - 1] = fmaf(-l[t], pk, w[t][k]);  // update and rotate
     }
-    if (bi != c) {
-      for (int j = lane; j < R; j += 32) {
-        const float t = M[c * LD + j];
-        M[c * LD + j] = M[bi * LD + j];
-        M[bi * LD + j] = t;
+#pragma unroll
+    for (int t = 0; t < RPL; ++t) w[t][R] = lane + 32 * t == c + 1 ? 1.0f : 0.0f;  // next column of I
+  }
+#pragma unroll
+  for (int t = 0; t < RPL; ++t) {
+    const int i = lane + 32 * t;
+    const float rd = fast_rcp(diag[t]);
+    if (i < R) {
+#pragma unroll
+      for (int j = 0; j < R; ++j) Gi[j * R + i] = w[t][j] * rd;  // element (i, j), stored column-wise
+    }
+  }
+  __syncwarp();
+}
+
+// x = (G + v^T v)^-1 b for symmetric G with a known inverse Gi (Sherman-Morrison), followed by one
+// step of iterative refinement against G itself.  Executed by ONE warp; lane i owns row i (and
+// i+32).  G and Gi are read column-wise (they are symmetric), which is free of bank conflicts.
+// x and tmp are R floats of shared memory; x receives the result.
+template <int R>
+__device__ __forceinline__ void warp_rank1_solve(const float *G, const float *Gi, const float *v, const float *b,
+                                                 float *x, float *tmp) {
+  constexpr int RPL = (R + 31) / 32;
+  const int lane = threadIdx.x & 31;
+  float y[RPL], z[RPL], vi[RPL], bi[RPL], xv[RPL];
+#pragma unroll
+  for (int t = 0; t < RPL; ++t) {
+    const int i = lane + 32 * t;
+    y[t] = z[t] = 0.0f;
+    vi[t] = i < R ? v[i] : 0.0f;
+    bi[t] = i < R ? b[i] : 0.0f;
+    if (i < R) {
+#pragma unroll 8
+      for (int j = 0; j < R; ++j) {
+        const float gij = Gi[j * R + i];
+        y[t] = fmaf(gij, b[j], y[t]);
+        z[t] = fmaf(gij, v[j], z[t]);
       }
-      if (lane == 0) { const float t = b[c]; b[c] = b[bi]; b[bi] = t; }
     }
-    __syncwarp();
-    const float rp = 1.0f / M[c * LD + c];
-    const float bc = b[c];
-    for (int i = c + 1 + lane; i < R; i += 32) {
-      const float l = M[i * LD + c] * rp;
-      for (int j = c + 1; j < R; ++j) M[i * LD + j] = fmaf(-l, M[c * LD + j], M[i * LD + j]);
-      b[i] = fmaf(-l, bc, b[i]);
+  }
+  float alpha = 0.0f, beta = 0.0f;
+#pragma unroll
+  for (int t = 0; t < RPL; ++t) { alpha = fmaf(vi[t], y[t], alpha); beta = fmaf(vi[t], z[t], beta); }
+  alpha = warp_sum(alpha);
+  beta = warp_sum(beta);
+  const float inv = 1.0f / (1.0f + beta);
+  float vx = 0.0f;
+#pragma unroll
+  for (int t = 0; t < RPL; ++t) {
+    xv[t] = y[t] - z[t] * (alpha * inv);
+    vx = fmaf(vi[t], xv[t], vx);
+    if (lane + 32 * t < R) x[lane + 32 * t] = xv[t];
+  }
+  vx = warp_sum(vx);
+  __syncwarp();
+  // residual r = b - G x - v (v . x), then the same solve for the correction
+#pragma unroll
+  for (int t = 0; t < RPL; ++t) {
+    const int i = lane + 32 * t;
+    float r = bi[t] - vi[t] * vx;
+    if (i < R) {
+#pragma unroll 8
+      for (int j = 0; j < R; ++j) r = fmaf(-G[j * R + i], x[j], r);
+      tmp[i] = r;
     }
-    __syncwarp();
   }
-  for (int c = R - 1; c >= 0; --c) {
-    const float xc = b[c] / M[c * LD + c];
-    __syncwarp();
-    if (lane == 0) b[c] = xc;
-    for (int i = lane; i < c; i += 32) b[i] = fmaf(-M[i * LD + c], xc, b[i]);
-    __syncwarp();
+  __syncwarp();
+  float dalpha = 0.0f, dy[RPL];
+#pragma unroll
+  for (int t = 0; t < RPL; ++t) {
+    const int i = lane + 32 * t;
+    dy[t] = 0.0f;
+    if (i < R) {
+#pragma unroll 8
+      for (int j = 0; j < R; ++j) dy[t] = fmaf(Gi[j * R + i], tmp[j], dy[t]);
+    }
+    dalpha = fmaf(vi[t], dy[t], dalpha);
   }
+  dalpha = warp_sum(dalpha);
+  __syncwarp();
+#pragma unroll
+  for (int t = 0; t < RPL; ++t)
+    if (lane + 32 * t < R) x[lane + 32 * t] = xv[t] + dy[t] - z[t] * (dalpha * inv);
+  __syncwarp();
 }
 
 template <typename T, int R, int D>
-__global__ void __launch_bounds__(kPThreads) project_kernel(ProjectParams p) {
-  constexpr int EL = D / 32;                   // key elements per lane
-  constexpr int MT = R >= 16 ? R / 16 : 1;     // Gram micro-tile edge per thread
-  constexpr int GT = R >= 16 ? 16 : R;         // threads per Gram edge
-  constexpr int LDB = D + 1;                   // padded leading dimension of B in shared memory
-  constexpr int LDM = R + 1;
+__global__ void __launch_bounds__(kPThreads, 2) project_kernel(ProjectParams p) {
+  constexpr int EL = D / 32;       // key elements per lane
+  constexpr int LDT = R + 4;       // leading dimension of the transposed right factors in shared memory
 
   cg::cluster_group cluster = cg::this_cluster();
   const int rank = (int)cluster.block_rank();
@@ -122,22 +286,33 @@ __global__ void __launch_bounds__(kPThreads) project_kernel(ProjectParams p) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int b_idx = n / p.q_heads, h = n % p.q_heads;
   const int kvh = h / p.groups, kv_heads = p.q_heads / p.groups;
+  const bool solver = rank == 0;
+  const bool streamer = csize == 1 || rank > 0;
+  const int n_streamers = csize == 1 ? 1 : csize - 1;
 
   extern __shared__ __align__(16) float sm[];
-  float *Gp = sm;                         // [R][R] partial Gram of this CTA
-  float *wp = Gp + R * R;                 // [R]
-  float *S = wp + R;                      // [kTileRows]
-  float *At = S + kTileRows;              // [kTileRows][R]
-  float *qs = At + kTileRows * R;         // [D]
+  float *Gp = sm;                         // [R][R] A^T A over this CTA's rows
+  float *wp = Gp + R * R;                 // [R]    sum_j s_j a_j over this CTA's rows
+  float *qs = wp + R;                     // [D]
   float *ks = qs + D;                     // [D]
-  // rank 0 only:
-  float *BQ = ks + D;                     // [R][LDB]
-  float *BK = BQ + R * LDB;               // [R][LDB]
-  float *GQ = BK + R * LDB;               // [R][R]   B_Q B_Q^T + A^T A
-  float *GK = GQ + R * R;                 // [R][R]   B_K B_K^T
-  float *Mw = GK + R * R;                 // [R][LDM] LU work matrix
-  float *vec = Mw + R * LDM;              // 6 vectors of R: qrhs, kbk, khat, qhat, rhs, khat_new
-  float *misc = vec + 6 * R;              // [4]
+  float *part = ks + D;                   // [kGramPart] partial sums of the group reductions
+  float *region = part + kGramPart;
+  // streaming buffers
+  float *S = region;                                              // [tile_rows]
+  int32_t *pos_s = reinterpret_cast<int32_t *>(S + p.tile_rows);  // [tile_rows]
+  float *At = reinterpret_cast<float *>(pos_s + p.tile_rows);     // [tile_rows][R]
+  // solver buffers: they share the region with the streaming buffers unless this CTA does both jobs
+  float *sol = csize == 1 ? At + p.tile_rows * R : region;
+  float *BtQ = sol;                       // [D][LDT] B_Q transposed
+  float *BtK = BtQ + D * LDT;             // [D][LDT]
+  float *GQ = BtK + D * LDT;              // [R][R]  B_Q B_Q^T (+ A^T A)
+  float *GQi = GQ + R * R;
+  float *GK = GQi + R * R;                // [R][R]  B_K B_K^T
+  float *GKi = GK + R * R;
+  float *vec = GKi + R * R;               // vectors of R: qrhs, kbk, khat, qhat, knew, rhs, tmp
+  float *misc = vec + 7 * R;              // [4]
+  float *qrhs = vec, *kbk = vec + R, *khat = vec + 2 * R, *qhat = vec + 3 * R, *knew = vec + 4 * R;
+  float *rhs = vec + 5 * R, *tmpv = vec + 6 * R;
 
   const T *qg = reinterpret_cast<const T *>(p.q) + (int64_t)n * D;
   const T *kg = reinterpret_cast<const T *>(p.k_new) + ((int64_t)b_idx * kv_heads + kvh) * D;
@@ -147,193 +322,146 @@ __global__ void __launch_bounds__(kPThreads) project_kernel(ProjectParams p) {
   }
   __syncthreads();
 
-  // ---- phase 1: this CTA's share of the active rows -------------------------------------------
-  const int n_act = p.k + p.m;
-  const int chunk = (n_act + csize - 1) / csize;
-  const int j_begin = rank * chunk;
-  const int j_end = min(n_act, j_begin + chunk);
-
-  float qf[EL];
+  // ---- streaming CTAs: their share of the active rows ------------------------------------------
+  if (streamer) {
+    const int n_act = p.k + p.m;
+    const int srank = csize == 1 ? 0 : rank - 1;
+    const int chunk = (n_act + n_streamers - 1) / n_streamers;
+    const int j_begin = srank * chunk;
+    const int j_end = min(n_act, j_begin + chunk);
+    float qf[EL];
 #pragma unroll
-  for (int e = 0; e < EL; ++e) qf[e] = qs[lane * EL + e];
-
-  const T *Kres = reinterpret_cast<const T *>(p.K_res) + (int64_t)n * n_act * D;
-  const T *AK = reinterpret_cast<const T *>(p.A_K) + (int64_t)n * p.a_capacity * R;
-  const int32_t *tab = p.table + (int64_t)n * p.k;
-
-  const int ty = tid / GT, tx = tid % GT;
-  const bool gram_thread = tid < GT * GT;
-  float gacc[MT][MT];
-#pragma unroll
-  for (int a = 0; a < MT; ++a)
-#pragma unroll
-    for (int c = 0; c < MT; ++c) gacc[a][c] = 0.0f;
-  float wacc = 0.0f;
-
-  for (int t0 = j_begin; t0 < j_end; t0 += kTileRows) {
-    const int rows = min(kTileRows, j_end - t0);
-    // (i) s_j = q . K_j : each warp takes rows warp, warp+8, ...; loads issued eight at a time
-    constexpr int RPW = kTileRows / (kPThreads / 32);
-    float kv[RPW][EL];
-#pragma unroll
-    for (int u = 0; u < RPW; ++u) {
-      const int row = warp + u * (kPThreads / 32);
-      if (row < rows) RowLoad<T, EL>::run(Kres + (int64_t)(t0 + row) * D + lane * EL, kv[u]);
-      else {
-#pragma unroll
-        for (int e = 0; e < EL; ++e) kv[u][e] = 0.0f;
+    for (int e = 0; e < EL; ++e) qf[e] = qs[lane * EL + e];
+    const T *Kres = reinterpret_cast<const T *>(p.K_res) + (int64_t)n * n_act * D;
+    const T *AK = reinterpret_cast<const T *>(p.A_K) + (int64_t)n * p.a_capacity * R;
+    const int32_t *tab = p.table + (int64_t)n * p.k;
+    bool first = true;
+    for (int t0 = j_begin; t0 < j_end || first; t0 += p.tile_rows) {
+      const int rows = max(0, min(p.tile_rows, j_end - t0));
+      for (int i = tid; i < rows; i += kPThreads) {
+        const int j = t0 + i;
+        pos_s[i] = j < p.k ? tab[j] : p.lite_pos[j - p.k];
       }
-    }
-    // (ii) rank-r rows of the same tokens
+      __syncthreads();
+      // rank-r rows of the tile's tokens: 16-byte pieces, gathered by all threads
+      constexpr int CPR = R * (int)sizeof(T) / 16;  // 16-byte pieces per row
+      constexpr int EPV = Elt<T>::kPerVec;
+      for (int i = tid; i < rows * CPR; i += kPThreads) {
+        const int row = i / CPR, c = i % CPR;
+        float f[EPV];
+        Elt<T>::unpack(ld16(AK + (int64_t)pos_s[row] * R + c * EPV), f);
 #pragma unroll
-    for (int u = 0; u < RPW; ++u) {
-      const int row = warp + u * (kPThreads / 32);
-      if (row < rows) {
-        const int j = t0 + row;
-        const int pos = j < p.k ? tab[j] : p.lite_pos[j - p.k];
-        for (int c = lane; c < R; c += 32) At[row * R + c] = Elt<T>::to_float(AK[(int64_t)pos * R + c]);
-      } else {
-        for (int c = lane; c < R; c += 32) At[row * R + c] = 0.0f;
+        for (int e = 0; e < EPV; ++e) At[row * R + c * EPV + e] = f[e];
       }
-    }
+      // s_j = q . K_j : a warp takes rows warp, warp + 8, ... with kBatch rows in flight
+      for (int r0 = warp; r0 < rows; r0 += kPWarps * kBatch) {
+        float kv[kBatch][EL];
 #pragma unroll
-    for (int u = 0; u < RPW; ++u) {
-      const int row = warp + u * (kPThreads / 32);
+        for (int u = 0; u < kBatch; ++u) {
+          const int row = r0 + u * kPWarps;
+          if (row < rows) RowLoad<T, EL>::run(Kres + (int64_t)(t0 + row) * D + lane * EL, kv[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+          const int row = r0 + u * kPWarps;
+          float acc = 0.0f;
+          if (row < rows) {
+#pragma unroll
+            for (int e = 0; e < EL; ++e) acc = fmaf(kv[u][e], qf[e], acc);
+          }
+          acc = warp_sum(acc);
+          if (lane == 0 && row < rows) S[row] = acc;
+        }
+      }
+      __syncthreads();
+      gram_xtx<R>(At, R, rows, part, Gp, !first);
+      weighted_colsum<R>(At, R, rows, S, part, wp, !first);
+      first = false;
+    }
+  }
+
+  // ---- solver CTA: everything that does not depend on the active rows ----------------------------
+  if (solver) {
+    const T *BQg = reinterpret_cast<const T *>(p.B_Q) + (int64_t)n * R * D;
+    const T *BKg = reinterpret_cast<const T *>(p.B_K) + (int64_t)n * R * D;
+    constexpr int EPV = Elt<T>::kPerVec;
+    for (int i = tid; i < R * D / EPV; i += kPThreads) {
+      const int a = (i * EPV) / D, e = (i * EPV) % D;
+      float fq[EPV], fk[EPV];
+      Elt<T>::unpack(ld16(BQg + (int64_t)i * EPV), fq);
+      Elt<T>::unpack(ld16(BKg + (int64_t)i * EPV), fk);
+#pragma unroll
+      for (int x = 0; x < EPV; ++x) { BtQ[(e + x) * LDT + a] = fq[x]; BtK[(e + x) * LDT + a] = fk[x]; }
+    }
+    __syncthreads();
+    gram_xtx<R>(BtQ, LDT, D, part, GQ, false);             // B_Q B_Q^T
+    gram_xtx<R>(BtK, LDT, D, part, GK, false);             // B_K B_K^T
+    weighted_colsum<R>(BtQ, LDT, D, qs, part, qrhs, false);  // q B_Q^T
+    weighted_colsum<R>(BtK, LDT, D, ks, part, kbk, false);   // k B_K^T
+    if (warp == 0) {
       float acc = 0.0f;
-#pragma unroll
-      for (int e = 0; e < EL; ++e) acc = fmaf(kv[u][e], qf[e], acc);
+      for (int e = lane; e < D; e += 32) acc = fmaf(qs[e], ks[e], acc);
       acc = warp_sum(acc);
-      if (lane == 0) S[row] = row < rows ? acc : 0.0f;
+      if (lane == 0) misc[0] = acc;  // q k^T
     }
     __syncthreads();
-    // (iii) accumulate w and G over the tile
-    if (gram_thread) {
-      for (int row = 0; row < rows; ++row) {
-        float ar[MT], ac[MT];
-#pragma unroll
-        for (int a = 0; a < MT; ++a) { ar[a] = At[row * R + ty * MT + a]; ac[a] = At[row * R + tx * MT + a]; }
-#pragma unroll
-        for (int a = 0; a < MT; ++a)
-#pragma unroll
-          for (int c = 0; c < MT; ++c) gacc[a][c] = fmaf(ar[a], ac[c], gacc[a][c]);
+    if (warp == 0) {  // invert B_K B_K^T, then k_hat0 = k B_K^T (B_K B_K^T)^-1
+      warp_spd_inverse<R>(GK, GKi);
+      for (int i = lane; i < R; i += 32) {
+        float acc = 0.0f;
+#pragma unroll 8
+        for (int j = 0; j < R; ++j) acc = fmaf(GKi[j * R + i], kbk[j], acc);
+        tmpv[i] = acc;
+      }
+      __syncwarp();
+      // one refinement step against G_K itself
+      for (int i = lane; i < R; i += 32) {
+        float r = kbk[i];
+#pragma unroll 8
+        for (int j = 0; j < R; ++j) r = fmaf(-GK[j * R + i], tmpv[j], r);
+        rhs[i] = r;
+      }
+      __syncwarp();
+      for (int i = lane; i < R; i += 32) {
+        float acc = tmpv[i];
+#pragma unroll 8
+        for (int j = 0; j < R; ++j) acc = fmaf(GKi[j * R + i], rhs[j], acc);
+        khat[i] = acc;
       }
     }
-    if (tid < R) {
-      for (int row = 0; row < rows; ++row) wacc = fmaf(S[row], At[row * R + tid], wacc);
-    }
-    __syncthreads();
   }
-  if (gram_thread) {
-#pragma unroll
-    for (int a = 0; a < MT; ++a)
-#pragma unroll
-      for (int c = 0; c < MT; ++c) Gp[(ty * MT + a) * R + tx * MT + c] = gacc[a][c];
-  }
-  if (tid < R) wp[tid] = wacc;
 
-  cluster.sync();
-  if (rank != 0) {
-    cluster.sync();  // stay resident until CTA 0 has read the partial sums
+  cluster.sync();  // partial sums of every streaming CTA are in place
+  if (!solver) {
+    cluster.sync();  // stay resident until CTA 0 has read them
     return;
   }
-
-  // ---- phase 2 (CTA 0): combine, build the small systems, solve ---------------------------------
+  const int first_rank = csize == 1 ? 0 : 1;
   for (int i = tid; i < R * R; i += kPThreads) {
-    float s = Gp[i];
-    for (int c = 1; c < csize; ++c) s += cluster.map_shared_rank(Gp, c)[i];
-    GQ[i] = s;  // A^T A for now
+    float s = 0.0f;
+    for (int c = first_rank; c < csize; ++c) s += cluster.map_shared_rank(Gp, c)[i];
+    GQ[i] += s;  // B_Q B_Q^T + A^T A
   }
   if (tid < R) {
-    float s = wp[tid];
-    for (int c = 1; c < csize; ++c) s += cluster.map_shared_rank(wp, c)[tid];
-    vec[tid] = s;  // (q K^T) A for now
+    float s = 0.0f;
+    for (int c = first_rank; c < csize; ++c) s += cluster.map_shared_rank(wp, c)[tid];
+    qrhs[tid] += s;  // q B_Q^T + (q K^T) A
   }
   cluster.sync();  // peers may retire
 
-  const T *BQg = reinterpret_cast<const T *>(p.B_Q) + (int64_t)n * R * D;
-  const T *BKg = reinterpret_cast<const T *>(p.B_K) + (int64_t)n * R * D;
-  for (int i = tid; i < R * D; i += kPThreads) {
-    const int a = i / D, e = i % D;
-    BQ[a * LDB + e] = Elt<T>::to_float(BQg[i]);
-    BK[a * LDB + e] = Elt<T>::to_float(BKg[i]);
-  }
-  __syncthreads();
-  // Gram matrices of the right factors
-  if (gram_thread) {
-    float accq[MT][MT], acck[MT][MT];
-#pragma unroll
-    for (int a = 0; a < MT; ++a)
-#pragma unroll
-      for (int c = 0; c < MT; ++c) { accq[a][c] = 0.0f; acck[a][c] = 0.0f; }
-    for (int e = 0; e < D; ++e) {
-      float rq[MT], cq[MT], rk[MT], ck[MT];
-#pragma unroll
-      for (int a = 0; a < MT; ++a) {
-        rq[a] = BQ[(ty * MT + a) * LDB + e]; cq[a] = BQ[(tx * MT + a) * LDB + e];
-        rk[a] = BK[(ty * MT + a) * LDB + e]; ck[a] = BK[(tx * MT + a) * LDB + e];
-      }
-#pragma unroll
-      for (int a = 0; a < MT; ++a)
-#pragma unroll
-        for (int c = 0; c < MT; ++c) {
-          accq[a][c] = fmaf(rq[a], cq[c], accq[a][c]);
-          acck[a][c] = fmaf(rk[a], ck[c], acck[a][c]);
-        }
-    }
-#pragma unroll
-    for (int a = 0; a < MT; ++a)
-#pragma unroll
-      for (int c = 0; c < MT; ++c) {
-        const int idx = (ty * MT + a) * R + tx * MT + c;
-        GQ[idx] += accq[a][c];
-        GK[idx] = acck[a][c];
-      }
-  }
-  // q B_Q^T, k B_K^T (one warp per output, strided) and q k^T
-  float *qrhs = vec, *kbk = vec + R, *khat = vec + 2 * R, *qhat = vec + 3 * R, *knew = vec + 5 * R;
-  for (int a = warp; a < 2 * R + 1; a += kPThreads / 32) {
-    float acc = 0.0f;
-    if (a < R) {
-      for (int e = lane; e < D; e += 32) acc = fmaf(qs[e], BQ[a * LDB + e], acc);
-    } else if (a < 2 * R) {
-      for (int e = lane; e < D; e += 32) acc = fmaf(ks[e], BK[(a - R) * LDB + e], acc);
-    } else {
-      for (int e = lane; e < D; e += 32) acc = fmaf(qs[e], ks[e], acc);
-    }
-    acc = warp_sum(acc);
-    if (lane == 0) {
-      if (a < R) qrhs[a] += acc;       // q B_Q^T + (q K^T) A
-      else if (a < 2 * R) kbk[a - R] = acc;
-      else misc[0] = acc;
-    }
-  }
-  __syncthreads();
-
   float *ws = p.ws + (int64_t)n * p.max_iter * (2 * R + 2);
   if (warp == 0) {
+    warp_spd_inverse<R>(GQ, GQi);
     const float qk = misc[0];
-    // k_hat0 = k B_K^T (B_K B_K^T)^-1
-    for (int i = lane; i < R * R; i += 32) Mw[(i / R) * LDM + (i % R)] = GK[i];
-    for (int i = lane; i < R; i += 32) khat[i] = kbk[i];
-    __syncwarp();
-    warp_lu_solve<R, LDM>(Mw, khat);
     for (int it = 0; it < p.max_iter; ++it) {
       // q_hat = (qrhs + qk * k_hat)(GQ + k_hat^T k_hat)^-1
-      for (int i = lane; i < R * R; i += 32) {
-        const int a = i / R, c = i % R;
-        Mw[a * LDM + c] = fmaf(khat[a], khat[c], GQ[i]);
-      }
-      for (int i = lane; i < R; i += 32) qhat[i] = fmaf(qk, khat[i], qrhs[i]);
+      for (int i = lane; i < R; i += 32) rhs[i] = fmaf(qk, khat[i], qrhs[i]);
       __syncwarp();
-      warp_lu_solve<R, LDM>(Mw, qhat);
+      warp_rank1_solve<R>(GQ, GQi, khat, rhs, qhat, tmpv);
       // k_hat' = (kbk + qk * q_hat)(GK + q_hat^T q_hat)^-1
-      for (int i = lane; i < R * R; i += 32) {
-        const int a = i / R, c = i % R;
-        Mw[a * LDM + c] = fmaf(qhat[a], qhat[c], GK[i]);
-      }
-      for (int i = lane; i < R; i += 32) knew[i] = fmaf(qk, qhat[i], kbk[i]);
+      for (int i = lane; i < R; i += 32) rhs[i] = fmaf(qk, qhat[i], kbk[i]);
       __syncwarp();
-      warp_lu_solve<R, LDM>(Mw, knew);
+      warp_rank1_solve<R>(GK, GKi, qhat, rhs, knew, tmpv);
       float ssd = 0.0f;
       for (int i = lane; i < R; i += 32) {
         const float dlt = khat[i] - knew[i];
@@ -344,9 +472,10 @@ __global__ void __launch_bounds__(kPThreads) project_kernel(ProjectParams p) {
       for (int i = lane; i < R; i += 32) {
         w[i] = qhat[i];
         w[R + i] = knew[i];
-        khat[i] = knew[i];
       }
       if (lane == 0) w[2 * R] = ssd;
+      __syncwarp();
+      for (int i = lane; i < R; i += 32) khat[i] = knew[i];
       __syncwarp();
     }
   }
@@ -444,25 +573,33 @@ __global__ void __launch_bounds__(D) update_kernel(UpdateParams p) {
   }
 }
 
-template <typename T, int R, int D>
-size_t project_smem_bytes() {
-  return sizeof(float) * (size_t)(R * R + R + kTileRows + kTileRows * R + 2 * D + 2 * R * (D + 1) + 2 * R * R +
-                                  R * (R + 1) + 6 * R + 4);
+template <int R, int D>
+size_t project_smem_bytes(int tile_rows, int csize) {
+  const size_t common = (size_t)R * R + R + 2 * D + kGramPart;
+  const size_t stream = (size_t)tile_rows * (2 + R);
+  const size_t solve = 2 * (size_t)D * (R + 4) + 4 * (size_t)R * R + 7 * R + 4;
+  return sizeof(float) * (common + (csize == 1 ? stream + solve : (stream > solve ? stream : solve)));
 }
 
 template <typename T, int R, int D>
-int launch(const lrqk_layer *L, const ProjectParams &pp, const UpdateParams &up, cudaStream_t stream) {
+int launch(const lrqk_layer *L, ProjectParams pp, const UpdateParams &up, cudaStream_t stream) {
   const int n_heads = L->bsz * L->q_heads;
-  const size_t smem = project_smem_bytes<T, R, D>();
-  auto kern = project_kernel<T, R, D>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    LRQK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr_set = true;
-  }
-  // CTAs per head: as many as keep the grid within about two CTAs per SM, at least 64 rows each
+  const int n_act = L->k + L->m;
+  // CTAs per head: one solver plus streaming CTAs with at least ~128 rows each, while the grid
+  // stays within about two CTAs per SM
   int csize = 1;
-  while (csize < 8 && n_heads * csize * 2 <= 2 * kNumSMs && (L->k + L->m) / (csize * 2) >= kTileRows) csize *= 2;
+  while (csize < 8 && n_heads * csize * 2 <= 2 * kNumSMs && n_act / (csize * 2 - 1) >= 128) csize *= 2;
+  const int n_streamers = csize == 1 ? 1 : csize - 1;
+  const int chunk = (n_act + n_streamers - 1) / n_streamers;
+  const int passes = (chunk + max_tile_rows<R>() - 1) / max_tile_rows<R>();
+  pp.tile_rows = ((chunk + passes - 1) / passes + 7) / 8 * 8;
+  const size_t smem = project_smem_bytes<R, D>(pp.tile_rows, csize);
+  auto kern = project_kernel<T, R, D>;
+  static size_t smem_set = 0;
+  if (smem > smem_set) {
+    LRQK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    smem_set = smem;
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(csize, n_heads, 1);
   cfg.blockDim = dim3(kPThreads, 1, 1);
@@ -520,6 +657,7 @@ extern "C" int lrqk_decode_project_update(const lrqk_layer *L, const void *q, co
   pp.a_capacity = L->a_capacity;
   pp.q_heads = L->q_heads; pp.groups = L->q_heads / L->kv_heads; pp.k = L->k; pp.m = L->m;
   pp.max_iter = max_iter; pp.n_heads = L->bsz * L->q_heads;
+  pp.tile_rows = 0;
   pp.ws = reinterpret_cast<float *>(workspace);
   UpdateParams up;
   up.A_K = L->A_K; up.B_Q = L->B_Q; up.B_K = L->B_K; up.q = q; up.k_new = k_new;

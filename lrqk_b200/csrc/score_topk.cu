@@ -26,6 +26,8 @@ constexpr int kThreads = 512;
 constexpr int kTile = 4 * kThreads;  // keys handled per compaction tile
 constexpr int kBins0 = 2048;         // 11-bit digits for passes 0 and 1, 10 bits for pass 2
 constexpr int kUnroll = 4;
+constexpr int kCandPerWarp = 128;      // per-warp list of keys still matching the radix prefix
+constexpr int kCandCap = kCandPerWarp * (kThreads / 32);
 
 template <int VB> struct Vec;
 template <> struct Vec<32> {
@@ -111,8 +113,38 @@ __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t *s
   return res;
 }
 
+// Keys live in shared memory with one pad word per 32 so that both access patterns used below
+// (thread-strided and one contiguous run per thread) are free of bank conflicts.
+__device__ __forceinline__ int phys(int i) { return i + (i >> 5); }
+
+// Find the bin that holds the `need`-th largest key given cluster-wide bin totals in `tot_hist`
+// (kBins0 words, larger bin = larger keys).  Returns through bcast[0] the bin, bcast[1] the
+// count still needed inside that bin.  All threads must call.
+__device__ __forceinline__ void pick_bin(const uint32_t *tot_hist, uint32_t need, uint32_t *scratch,
+                                         uint32_t *bcast) {
+  const int tid = threadIdx.x;
+  const uint4 x = *reinterpret_cast<const uint4 *>(tot_hist + 4 * tid);
+  const uint32_t tot[4] = {x.x, x.y, x.z, x.w};
+  const uint32_t mine = tot[0] + tot[1] + tot[2] + tot[3];
+  uint32_t all;
+  const uint32_t below_incl = block_exclusive_scan(mine, scratch, all) + mine;
+  uint32_t above = all - below_incl;  // keys in bins above this thread's four bins
+  if (above < need && need <= above + mine) {
+#pragma unroll
+    for (int j = 3; j >= 0; --j) {
+      if (above + tot[j] >= need) {
+        bcast[0] = (uint32_t)(4 * tid + j);
+        bcast[1] = need - above;
+        break;
+      }
+      above += tot[j];
+    }
+  }
+  __syncthreads();
+}
+
 template <typename T, int R>
-__global__ void __launch_bounds__(kThreads) score_topk_kernel(ScoreTopkParams p) {
+__global__ void __launch_bounds__(kThreads, 2) score_topk_kernel(ScoreTopkParams p) {
   constexpr int RB = R * (int)sizeof(T);          // bytes per row
   constexpr int VB = RB >= 32 ? 32 : 16;          // bytes per lane
   constexpr int LPR = RB / VB;                    // lanes per row
@@ -125,16 +157,22 @@ __global__ void __launch_bounds__(kThreads) score_topk_kernel(ScoreTopkParams p)
   const int rank = (int)cluster.block_rank();
   const int csize = (int)cluster.num_blocks();
   const int n = blockIdx.y;
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
   extern __shared__ __align__(16) uint32_t smem[];
-  uint32_t *keys = smem;                          // [seg_len]
-  uint32_t *hist = keys + p.seg_len;              // [2][kBins0]
-  uint32_t *scratch = hist + 2 * kBins0;          // [32]
-  uint32_t *bcast = scratch + 32;                 // [8]  {bin, need} then {gt, eq}
+  uint32_t *keys = smem;                                    // [seg_len + seg_len/32], padded
+  uint32_t *hloc = keys + p.seg_len + (p.seg_len >> 5);     // [kBins0] this CTA's histogram of the pass
+  uint32_t *htot = hloc + kBins0;                           // [2][kBins0] cluster totals (peers add into them)
+  uint32_t *cand = htot + 2 * kBins0;                       // [kCandCap] local indices still matching the prefix
+  uint32_t *scratch = cand + kCandCap;                      // [32]
+  uint32_t *bcast = scratch + 32;                           // [8]  {bin, need, n_cand}
+  uint32_t *cnts = bcast + 8;                               // [16][2] (greater, equal) per rank, written by peers
+  uint32_t *wcount = cnts + 32;                             // [16] candidates seen by each warp
 
-  for (int i = tid; i < 2 * kBins0; i += kThreads) hist[i] = 0;
+  for (int i = tid; i < 3 * kBins0; i += kThreads) hloc[i] = 0;
+  if (tid < 8) bcast[tid] = 0;
   __syncthreads();
+  cluster.barrier_arrive();  // peers may add into my totals once they have seen this
 
   // ---- streaming pass: scores -> keys in shared memory, pass-0 histogram on the fly -------
   const int64_t seg_begin = (int64_t)rank * p.seg_len;
@@ -147,8 +185,7 @@ __global__ void __launch_bounds__(kThreads) score_topk_kernel(ScoreTopkParams p)
     for (int e = 0; e < EPL; ++e) qf[e] = Elt<T>::to_float(qh[e]);
   }
   const char *base = reinterpret_cast<const char *>(p.A_K) + ((int64_t)n * p.a_capacity) * RB + lane_in_row * VB;
-  // rows of this segment that hold candidates
-  int64_t seg_rows = p.candidates - seg_begin;
+  int64_t seg_rows = p.candidates - seg_begin;   // rows of this segment that hold candidates
   if (seg_rows < 0) seg_rows = 0;
   if (seg_rows > p.seg_len) seg_rows = p.seg_len;
   const int n_iter_rows = (int)((seg_rows + RPI * kUnroll - 1) / (RPI * kUnroll)) * (RPI * kUnroll);
@@ -175,124 +212,132 @@ __global__ void __launch_bounds__(kThreads) score_topk_kernel(ScoreTopkParams p)
         uint32_t key = 0;
         if (local < seg_rows) {
           key = order_key(acc);
-          atomicAdd(&hist[key >> 21], 1u);
+          atomicAdd(&hloc[key >> 21], 1u);
           if (p.scores_out) p.scores_out[(int64_t)n * p.scores_stride + seg_begin + local] = acc;
         }
-        keys[local] = key;
+        keys[phys(local)] = key;
       }
     }
   }
-  for (int i = n_iter_rows + tid; i < p.seg_len; i += kThreads) keys[i] = 0;  // padding sorts last
+  for (int i = n_iter_rows + tid; i < p.seg_len; i += kThreads) keys[phys(i)] = 0;  // padding sorts last
   __syncthreads();
+  cluster.barrier_wait();
 
   // ---- radix select of the k-th largest key over the whole cluster ---------------------------
+  // Three passes (11 + 11 + 10 bits).  Each CTA adds the non-zero bins of its histogram into
+  // every peer's total through distributed shared memory, so that after one cluster barrier each
+  // CTA finds the digit locally.  Passes 1 and 2 only visit the keys that matched so far.
   uint32_t prefix = 0;
   uint32_t need = (uint32_t)p.k;
 #pragma unroll 1
   for (int pass = 0; pass < 3; ++pass) {
     const int shift = pass == 0 ? 21 : (pass == 1 ? 10 : 0);
     const int bits = pass == 2 ? 10 : 11;
-    const int prev_shift = pass == 1 ? 21 : 10;   // pass > 0: keys must match `prefix` above this
-    uint32_t *h = hist + (pass & 1) * kBins0;
-    if (pass > 0) {
-      if (pass == 2) {
-        for (int i = tid; i < kBins0; i += kThreads) h[i] = 0;
-        __syncthreads();
-      }
-      const uint32_t dmask = (1u << bits) - 1;
+    const uint32_t dmask = (1u << bits) - 1;
+    if (pass == 1) {
+      // candidates: keys whose top 11 bits equal the chosen bin; every warp keeps a private list
+      // (position counter in a register, slots handed out by ballot) so that no atomic is shared
+      uint32_t mine_n = 0;
+      uint32_t *wl = cand + warp * kCandPerWarp;
       for (int i = tid; i < p.seg_len; i += kThreads) {
-        const uint32_t key = keys[i];
-        if ((key >> prev_shift) == prefix) atomicAdd(&h[(key >> shift) & dmask], 1u);
-      }
-    }
-    cluster.sync();  // every CTA's histogram of this pass is complete
-    // cluster-wide totals of this thread's four bins
-    uint32_t tot[4] = {0, 0, 0, 0};
-    for (int c = 0; c < csize; ++c) {
-      const uint32_t *rh = cluster.map_shared_rank(h, c);
-      const uint4 x = *reinterpret_cast<const uint4 *>(rh + 4 * tid);
-      tot[0] += x.x; tot[1] += x.y; tot[2] += x.z; tot[3] += x.w;
-    }
-    // count of keys in bins above this thread's bins (reverse exclusive scan)
-    const uint32_t mine = tot[0] + tot[1] + tot[2] + tot[3];
-    uint32_t all;
-    const uint32_t below_incl = block_exclusive_scan(mine, scratch, all) + mine;
-    uint32_t above = all - below_incl;
-    if (above < need && need <= above + mine) {
-#pragma unroll
-      for (int j = 3; j >= 0; --j) {
-        if (above + tot[j] >= need) {
-          bcast[0] = (uint32_t)(4 * tid + j);
-          bcast[1] = need - above;
-          break;
+        const uint32_t key = keys[phys(i)];
+        const bool hit = (key >> 21) == prefix;
+        const uint32_t bal = __ballot_sync(0xFFFFFFFFu, hit);
+        if (hit) {
+          atomicAdd(&hloc[(key >> shift) & dmask], 1u);
+          const uint32_t at = mine_n + __popc(bal & ((1u << lane) - 1));
+          if (at < (uint32_t)kCandPerWarp) wl[at] = (uint32_t)i;
         }
-        above += tot[j];
+        mine_n += __popc(bal);
+      }
+      if (lane == 0) wcount[warp] = mine_n;
+      __syncthreads();
+    } else if (pass == 2) {
+      const uint32_t mine_n = wcount[warp];
+      bool overflow = false;
+      for (int w = 0; w < kThreads / 32; ++w) overflow |= wcount[w] > (uint32_t)kCandPerWarp;
+      if (!overflow) {
+        const uint32_t *wl = cand + warp * kCandPerWarp;
+        for (uint32_t c = lane; c < mine_n; c += 32) {
+          const uint32_t key = keys[phys((int)wl[c])];
+          if ((key >> 10) == prefix) atomicAdd(&hloc[key & dmask], 1u);
+        }
+      } else {  // some warp met more matches than its list holds: visit every key
+        for (int i = tid; i < p.seg_len; i += kThreads) {
+          const uint32_t key = keys[phys(i)];
+          if ((key >> 10) == prefix) atomicAdd(&hloc[key & dmask], 1u);
+        }
+      }
+      __syncthreads();
+    }
+    uint32_t *ht = htot + (pass & 1) * kBins0;
+#pragma unroll
+    for (int j = 0; j < kBins0 / kThreads; ++j) {
+      const int b = tid + j * kThreads;
+      const uint32_t v = hloc[b];
+      if (v) {
+        hloc[b] = 0;
+        for (int c = 0; c < csize; ++c) atomicAdd(cluster.map_shared_rank(ht, c) + b, v);
       }
     }
-    __syncthreads();
+    cluster.sync();  // every CTA's contribution has landed
+    pick_bin(ht, need, scratch, bcast);
     prefix = (prefix << bits) | bcast[0];
     need = bcast[1];
+    if (pass == 0) {  // totals[0] is used again by pass 2; peers add to it only after the next barrier
+#pragma unroll
+      for (int j = 0; j < kBins0 / kThreads; ++j) ht[tid + j * kThreads] = 0;
+    }
     __syncthreads();
   }
   const uint32_t T_key = prefix;       // the k-th largest key
   const uint32_t need_ties = need;     // how many keys equal to it are taken (lowest positions)
 
-  // ---- per-CTA counts, exchanged through distributed shared memory ---------------------------
-  {
-    uint32_t g = 0, e = 0;
-    for (int i = tid; i < p.seg_len; i += kThreads) {
-      const uint32_t key = keys[i];
-      g += key > T_key;
-      e += key == T_key;
-    }
-    uint32_t gt_total, eq_total;
-    block_exclusive_scan(g, scratch, gt_total);
-    block_exclusive_scan(e, scratch, eq_total);
-    if (tid == 0) { bcast[2] = gt_total; bcast[3] = eq_total; }
+  // ---- ordered compaction: one contiguous run of keys per thread ------------------------------
+  const int per = p.seg_len / kThreads;
+  uint32_t cg_ = 0, ce_ = 0;
+#pragma unroll 4
+  for (int j = 0; j < per; ++j) {
+    const uint32_t key = keys[phys(tid * per + j)];
+    cg_ += key > T_key;
+    ce_ += key == T_key;
+  }
+  uint32_t cta_total;
+  const uint32_t ex = block_exclusive_scan(cg_ | (ce_ << 16), scratch, cta_total);  // counts fit 16 bits
+  if (tid < csize) {  // tell every rank how many keys this CTA holds above / at the threshold
+    uint32_t *rc = cluster.map_shared_rank(cnts, tid);
+    rc[2 * rank] = cta_total & 0xFFFFu;
+    rc[2 * rank + 1] = cta_total >> 16;
   }
   cluster.sync();
   uint32_t out_base = 0, tie_base = 0, quota = 0;
   for (int c = 0; c <= rank; ++c) {
-    const uint32_t *rb = cluster.map_shared_rank(bcast, c);
-    const uint32_t g = rb[2], e = rb[3];
+    const uint32_t g = cnts[2 * c], e = cnts[2 * c + 1];
     const uint32_t left = need_ties > tie_base ? need_ties - tie_base : 0;
     const uint32_t q = e < left ? e : left;
     if (c < rank) { out_base += g + q; tie_base += e; }
     else quota = q;
   }
-
-  // ---- ordered compaction of this segment ------------------------------------------------------
   int32_t *out = p.wanted + (int64_t)n * p.k;
-  uint32_t gt_run = 0, eq_run = 0;
-  const int n_tiles = (int)((seg_rows + kTile - 1) / kTile);
-  for (int t = 0; t < n_tiles; ++t) {
-    const uint4 kv = *reinterpret_cast<const uint4 *>(keys + t * kTile + 4 * tid);
-    const uint32_t kk[4] = {kv.x, kv.y, kv.z, kv.w};
-    uint32_t cg_ = 0, ce_ = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) { cg_ += kk[j] > T_key; ce_ += kk[j] == T_key; }
-    uint32_t tile_total;
-    const uint32_t ex = block_exclusive_scan(cg_ | (ce_ << 16), scratch, tile_total);
-    uint32_t gb = gt_run + (ex & 0xFFFFu), eb = eq_run + (ex >> 16);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const bool is_g = kk[j] > T_key, is_e = kk[j] == T_key;
-      if (is_g || (is_e && eb < quota)) {
-        const uint32_t pos = out_base + gb + (eb < quota ? eb : quota);
-        if (pos < (uint32_t)p.k) out[pos] = (int32_t)(seg_begin + t * kTile + 4 * tid + j);
-      }
-      gb += is_g;
-      eb += is_e;
+  uint32_t gb = ex & 0xFFFFu, eb = ex >> 16;
+#pragma unroll 4
+  for (int j = 0; j < per; ++j) {
+    const int i = tid * per + j;
+    const uint32_t key = keys[phys(i)];
+    const bool is_g = key > T_key, is_e = key == T_key;
+    if (is_g || (is_e && eb < quota)) {
+      const uint32_t pos = out_base + gb + (eb < quota ? eb : quota);
+      if (pos < (uint32_t)p.k) out[pos] = (int32_t)(seg_begin + i);
     }
-    gt_run += tile_total & 0xFFFFu;
-    eq_run += tile_total >> 16;
+    gb += is_g;
+    eb += is_e;
   }
-  cluster.sync();  // keep shared memory alive until every peer has read the counts
+  // no peer touches this CTA's shared memory after the last cluster barrier above
 }
 
 template <typename T, int R>
 int launch_score_topk(const ScoreTopkParams &p, int n_heads, int csize, cudaStream_t stream) {
-  const size_t smem = ((size_t)p.seg_len + 2 * kBins0 + 32 + 8) * sizeof(uint32_t);
+  const size_t smem = ((size_t)p.seg_len + (p.seg_len >> 5) + 3 * kBins0 + kCandCap + 32 + 8 + 32 + 16) * sizeof(uint32_t);
   auto kern = score_topk_kernel<T, R>;
   static size_t smem_set = 0;
   static bool nonportable_set = false;
@@ -337,7 +382,7 @@ int dispatch_rank(int r, const ScoreTopkParams &p, int n_heads, int csize, cudaS
 // The keys of a segment must fit in shared memory; beyond that, more CTAs per head are used
 // while the grid stays within about two resident CTAs per SM.
 int plan_score_topk(int64_t candidates, int n_heads, int *csize_out, int *seg_len_out) {
-  const int64_t max_seg = 49152;  // 192 KiB of keys
+  const int64_t max_seg = 45056;  // 176 KiB of keys next to the histograms
   int best = -1;
   for (int cs = 1; cs <= 16; cs *= 2) {
     const int64_t seg = ceil_div64(ceil_div64(candidates, cs), kTile) * kTile;
