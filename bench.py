@@ -60,42 +60,6 @@ def make_prompt(seed: int, w: dict, hq: int, hkv: int, device, dtype):
     return Q, K, V
 
 
-def factor_state(Q, K, r: int, groups: int, sweeps: int, seed: int):
-    """Rank-r factors for a synthetic prompt, from a random start, by the reference's alternating
-    least squares written on the d x d Gram matrices (setup only; untimed).  Returns A_K
-    [B,Hq,S,r], B_Q, B_K [B,Hq,r,d] and the last row of A_Q [B,Hq,r], fp32."""
-    f = torch.float32
-    b, hq, s, d = Q.shape
-    g = torch.Generator(device=Q.device).manual_seed(seed)
-    t = lambda x: x.transpose(-1, -2)
-    SQ = torch.empty(b, hq, d, d, device=Q.device)
-    CQ = torch.empty(b, hq, r, d, device=Q.device)
-    GQ = torch.empty(b, hq, r, r, device=Q.device)
-    SK, CK, GK = torch.empty_like(SQ), torch.empty_like(CQ), torch.empty_like(GQ)
-    for h in range(hq):  # one head at a time keeps the fp32 temporaries small
-        q32, k32 = Q[:, h].to(f), K[:, h // groups].to(f)
-        a_q0 = torch.randn(b, s, r, generator=g, device=Q.device)
-        a_k0 = torch.randn(b, s, r, generator=g, device=Q.device)
-        SQ[:, h], SK[:, h] = t(q32) @ q32, t(k32) @ k32
-        CQ[:, h], CK[:, h] = t(a_q0) @ q32, t(a_k0) @ k32
-        GQ[:, h], GK[:, h] = t(a_q0) @ a_q0, t(a_k0) @ a_k0
-    solve = lambda a, bb: torch.linalg.solve(a, bb)
-    solve_r = lambda a, bb: torch.linalg.solve(a, bb, left=False)
-    XQ = XK = None
-    for _ in range(max(1, sweeps)):
-        BQ, BK = solve(GQ, CQ), solve(GK, CK)
-        XQ = solve_r(GK + BQ @ t(BQ), t(CK) + t(BQ))            # A_Q = Q XQ
-        GQ, CQ = t(XQ) @ SQ @ XQ, t(XQ) @ SQ
-        XK = solve_r(GQ + BK @ t(BK), t(CQ) + t(BK))            # A_K = K XK
-        GK, CK = t(XK) @ SK @ XK, t(XK) @ SK
-    BQ, BK = solve(GQ, CQ), solve(GK, CK)
-    A_K = torch.empty(b, hq, s, r, device=Q.device, dtype=Q.dtype)
-    for h in range(hq):
-        A_K[:, h] = (K[:, h // groups].to(f) @ XK[:, h]).to(Q.dtype)
-    a_q_last = (Q[:, :, -1:, :].to(f) @ XQ)[:, :, 0]
-    return A_K, BQ, BK, a_q_last
-
-
 def make_steps(seed: int, n_tokens: int, layers: int, w: dict, hq: int, hkv: int, rho: float, device, dtype):
     """Per token and layer: q [B,Hq,d], k, v [B,Hkv,d].  q follows q_t = rho q_{t-1} + sqrt(1-rho^2) eps
     per layer (rho = 0: independent N(0,1) queries, the BASELINE configs' distribution)."""
@@ -191,26 +155,29 @@ def host_link_peak_gbs(device) -> float:
 
 
 def build_layers(w, layers, hq_local, hkv_local, head_offset, device, dtype, seed, n_tokens):
+    """One factory per layer, prefilled through the public API (prompt factorisation, host store,
+    first selection, lite ring).  Returns the factories and the mean prefill time per layer."""
     from lrqk_b200 import LightAttentionIndicesFactory
-    facs = []
+    facs, ms = [], []
     groups = w["hq"] // w["hkv"]
     for li in range(layers):
         Q, K, V = make_prompt(seed + 100 * li + head_offset, w, hq_local, hkv_local, device, dtype)
-        A_K, BQ, BK, a_q_last = factor_state(Q, K, w["r"], groups, w["max_iter"][0], seed + 7 + li)
         fac = LightAttentionIndicesFactory(num_lite_tokens=w["m"], attn_topk=w["k"], num_key_value_groups=groups,
                                            r=w["r"], max_iter=w["max_iter"], tol=w["tol"],
-                                           capacity=w["seq"] + n_tokens + 2 * w["m"] + 64, scaling_ratio=1.0)
-        # first resident set: the prompt-time selection with the last prompt query's factors
-        fac.load_state(A_K=A_K, B_Q=BQ.to(dtype), B_K=BK.to(dtype), keys=K, values=V,
-                       table=torch.zeros(w["bsz"], hq_local, w["k"], dtype=torch.int32, device=device))
-        st = fac.state
-        st.score_topk(a_q_last.to(dtype).contiguous(), w["seq"] - w["m"])
-        st.table.copy_(st.wanted)
-        st.fill_resident(K, V)
+                                           capacity=w["seq"] + n_tokens + 2 * w["m"] + 64, scaling_ratio=1.0,
+                                           init_aq_ak_method="randn")
+        torch.manual_seed(seed + 7 + li)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fac.prefill(Q, K, V)
+        e1.record()
+        e1.synchronize()
+        ms.append(e0.elapsed_time(e1))
         facs.append(fac)
-        del Q, K, V, A_K
+        del Q, K, V
     torch.cuda.synchronize()
-    return facs
+    return facs, statistics.mean(ms)
 
 
 def stage_bytes(w, hq, hkv, cand, misses, e=2):
@@ -245,7 +212,7 @@ def run_ours(args):
     n_tokens = args.warmup + 3 * args.steps + 8
     layers = args.layers
     t_setup = time.time()
-    facs = build_layers(w, layers, hq_l, hkv_l, rank * 1000, device, dtype, args.seed, n_tokens)
+    facs, prefill_ms = build_layers(w, layers, hq_l, hkv_l, rank * 1000, device, dtype, args.seed, n_tokens)
     q_all, k_all, v_all = make_steps(args.seed + 1 + rank, n_tokens, layers, w, hq_l, hkv_l, args.rho, device, dtype)
     gathered = torch.empty(world, w["bsz"], hq_l, w["d"], dtype=dtype, device=device) if world > 1 else None
     setup_s = time.time() - t_setup
@@ -367,7 +334,7 @@ def run_ours(args):
                    "l2": "inputs larger than L2: each layer's A_K is %.0f MB and %d layer states are cycled"
                          % (w["bsz"] * hq_l * w["seq"] * w["r"] * 2 / 1e6, layers)},
         "tokens_per_s_8b_equiv": round(1e6 / (us_per_layer * 32), 2),
-        "miss_rate": round(miss_rate, 4), "setup_s": round(setup_s, 1),
+        "miss_rate": round(miss_rate, 4), "setup_s": round(setup_s, 1), "prefill_ms_per_layer": round(prefill_ms, 2),
         "e2e": {"value": round(us_per_layer_e2e, 2), "unit": "us/layer/step", "h2d_bytes_per_step": int(h2d),
                 "d2h_bytes_per_step": int(d2h)},
         "gpu_launches": int(args.steps * layers * 7),
@@ -440,25 +407,17 @@ def run_reference(args):
     orc = _oracle()
     w = WORKLOADS[args.workload]
     dtype = torch.float32 if args.workload == "cfg0" else torch.bfloat16
-    dev = torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
     groups = w["hq"] // w["hkv"]
-    # one layer's state; the heavy Gram products of the synthetic set-up run wherever is fastest,
-    # the timed decode steps run on the host cores only
-    Q, K, V = make_prompt(args.seed, w, w["hq"], w["hkv"], dev, dtype)
-    A_K, BQ, BK, a_q_last = factor_state(Q, K, w["r"], groups, w["max_iter"][0], args.seed + 7)
-    A_K, BQ, BK, a_q_last, K, V = (x.cpu() for x in (A_K, BQ.to(dtype), BK.to(dtype), a_q_last.to(dtype), K, V))
-    del Q
-    s, m, k, d = w["seq"], w["m"], w["k"], w["d"]
+    # one layer: the oracle's own prompt factorisation and first selection, then the timed steps
+    Q, K, V = make_prompt(args.seed, w, w["hq"], w["hkv"], torch.device("cpu"), dtype)
     n_tokens = args.warmup + args.steps
-    cap = s + n_tokens + 2 * m + 64
-    A_full = torch.zeros(w["bsz"], w["hq"], cap, w["r"], dtype=dtype); A_full[:, :, :s] = A_K
-    host = torch.zeros(w["bsz"], w["hkv"], cap, 2 * d, dtype=dtype); host[:, :, :s] = torch.cat([K, V], -1)
-    table = orc.topk_sorted(orc.proxy_scores(A_K[:, :, :s - m], a_q_last[:, :, None]), k)
-    idx = torch.from_numpy(table.astype("int64"))[..., None].expand(-1, -1, -1, d)
-    Krep, Vrep = orc.expand_kv_heads(K, groups), orc.expand_kv_heads(V, groups)
-    Kres = torch.cat([torch.gather(Krep, 2, idx), Krep[:, :, s - m:]], 2).contiguous()
-    Vres = torch.cat([torch.gather(Vrep, 2, idx), Vrep[:, :, s - m:]], 2).contiguous()
-    lay = oracle_layer_from_tensors(orc, w, A_full, BQ, BK, Kres, Vres, table, host, s, s, range(s - m, s), 0)
+    lay = orc.OracleLayer(w["r"], w["k"], w["m"], groups, w["max_iter"], (w["tol"], w["tol"]),
+                          capacity=w["seq"] + n_tokens + 2 * w["m"] + 64, scaling_ratio=1.0, faithful=True)
+    torch.manual_seed(args.seed + 7)
+    tp = time.perf_counter()
+    lay.prefill(Q, K, V)
+    prefill_s = time.perf_counter() - tp
+    del Q, K, V
     q_all, k_all, v_all = make_steps(args.seed + 1, n_tokens, 1, w, w["hq"], w["hkv"], args.rho, torch.device("cpu"), dtype)
     steps = [(q_all[t, 0].unsqueeze(2), k_all[t, 0].unsqueeze(2), v_all[t, 0].unsqueeze(2)) for t in range(n_tokens)]
     t0 = time.perf_counter()
@@ -477,7 +436,7 @@ def run_reference(args):
                          "sample": f"{len(times)} decode steps of one layer on the host cores "
                                    f"(torch CPU ops in the reference's order + C row gather), mean"},
         "e2e": {"value": round(us, 1), "unit": "us/layer/step", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "wall_s": round(time.perf_counter() - t0, 1),
+        "wall_s": round(time.perf_counter() - t0, 1), "prefill_s_one_layer": round(prefill_s, 1),
     }
     print(json.dumps(line), flush=True)
 

@@ -102,7 +102,7 @@ class AutoIncreaseTensor:
         self.data, self.capacity = grown, new_cap
         return True
 
-    @torch.inference_mode()
+    @torch.no_grad()
     def append(self, x: torch.Tensor):
         if self.device is None:
             self.device = x.device
@@ -374,7 +374,7 @@ class LightAttentionIndicesFactory:
         return LayerState(bsz, hq, hkv, d, self.r, self.attn_topk, self.num_lite_tokens, a_capacity=cap,
                           host_capacity=cap, dtype=dtype, device=device, max_iter=self.max_iter[1])
 
-    @torch.inference_mode()
+    @torch.no_grad()
     def prefill(self, query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor):
         bsz, hq, seq_len, d = query_states.shape
         hkv = key_states.shape[1]
@@ -469,7 +469,7 @@ class LightAttentionIndicesFactory:
             raise ValueError(f"decode expects [B,{heads},1,{st.head_dim}], got {tuple(x.shape)}")
         return x.reshape(st.bsz, heads, st.head_dim).contiguous()
 
-    @torch.inference_mode()
+    @torch.no_grad()
     def _decode(self, query_states, key_states, value_states, attention: bool):
         st = self.state
         if st is None:
