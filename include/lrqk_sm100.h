@@ -170,6 +170,27 @@ int lrqk_flash_decode(const lrqk_layer *L, const void *q, void *out, int32_t row
                       void *workspace, lrqk_stream_t stream);
 
 /* ------------------------------------------------------------------------------------
+ * The same attention for callers that can neither allocate nor pass a workspace.
+ * No counterpart in the reference: it exists for hosts whose device memory is entirely owned by
+ * their own pool at call time (a serving runtime's plugin hook, a loop whose rules forbid
+ * allocator calls) and that therefore cannot satisfy lrqk_flash_decode's workspace argument.
+ * The scratch is an array compiled into the library (lrqk_flash_decode_static_capacity_bytes(),
+ * 4 MiB, resident on every GPU that loads the library until the process exits).  This entry and
+ * everything it calls allocate nothing.
+ *   - Limit: B*Hq heads times the split count chosen for `rows` must fit the array (about 240
+ *     heads at head_dim 128); larger shapes return LRQK_ECAPACITY and lrqk_last_cuda_error()
+ *     says how many bytes were needed.
+ *   - The first call on a device looks up the array's device address (once per device, with that
+ *     device current); make that first call outside any stream capture.
+ *   - All calls share the one array and it keeps the previous call's contents; the entry clears
+ *     the part that must start at zero on `stream` before launching.  Two calls that can overlap
+ *     on the GPU (different streams, no ordering between them) race on it: serialise them.
+ * ---------------------------------------------------------------------------------- */
+size_t lrqk_flash_decode_static_capacity_bytes(void);
+int lrqk_flash_decode_static(const lrqk_layer *L, const void *q, void *out, int32_t rows, float scale,
+                             lrqk_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
  * One whole decode step of a layer: the six calls above in the reference's order
  * (LightAttentionIndicesFactory.decode, lrqk_attention.py:1506-1613, followed by the
  * attention call).  Host-side counters (ring slot, positions, candidate count) are the

@@ -73,6 +73,9 @@ _SIGNATURES = {
     "lrqk_flash_decode_workspace_bytes": (C.c_size_t, [C.POINTER(Layer), C.c_int32]),
     "lrqk_flash_decode": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_void_p, C.c_int32, C.c_float, C.c_void_p,
                                     C.c_void_p]),
+    "lrqk_flash_decode_static_capacity_bytes": (C.c_size_t, []),
+    "lrqk_flash_decode_static": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_void_p, C.c_int32, C.c_float,
+                                           C.c_void_p]),
     "lrqk_layer_step": (C.c_int, [C.POINTER(Layer), C.POINTER(StepArgs), C.c_void_p]),
     "lrqk_d0_indices_select": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
                                          C.c_void_p]),

@@ -15,6 +15,8 @@ void note_cuda_error(cudaError_t e) {
   cudaGetLastError();  // clear the sticky-free error so later launches are judged on their own
 }
 
+void note_error_text(const char *text) { snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "%s", text); }
+
 int check_device() {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return LRQK_ENODEVICE; }

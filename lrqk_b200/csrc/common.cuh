@@ -13,6 +13,7 @@ constexpr int kNumSMs = 148;  // B200: two dies of 74 SMs
 
 // ---- host side -------------------------------------------------------------------------
 void note_cuda_error(cudaError_t e);
+void note_error_text(const char *text);  // free-form detail, returned by lrqk_last_cuda_error()
 
 #define LRQK_CUDA_TRY(expr)                      \
   do {                                           \

@@ -6,6 +6,7 @@
 // workspace.  The CTA that finishes last for a head (an atomic ticket) folds the partials in
 // split order and writes the output row, then re-arms the ticket.
 #include <math.h>
+#include <stdio.h>
 
 #include "common.cuh"
 
@@ -212,6 +213,88 @@ extern "C" int lrqk_flash_decode(const lrqk_layer *L, const void *q, void *out, 
     LRQK_DISPATCH_DTYPE(L->dtype, T, (flash_decode_kernel<T, 64><<<grid, kAThreads, 0, s>>>(p)));
   } else {
     return LRQK_EUNSUPPORTED;
+  }
+  LRQK_LAUNCH_CHECK();
+  return LRQK_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Attention without any allocation by anyone: the split partials and tickets live in an array
+// that is part of the library image.
+//
+// Meant for callers that hold no allocator they may use at the time of the call: a plugin hook of
+// a serving runtime that has already handed every byte of device memory to its own block pool, a
+// latency-critical loop whose rules forbid allocator calls, an embedding host that only passes
+// the input and output buffers through.  Such callers cannot size and provide the workspace
+// lrqk_flash_decode() asks for, and this library must not call cudaMalloc on their behalf.
+//
+// The array is a file-scope __device__ object, so every GPU that loads the library carries it
+// (kStaticScratchBytes) until the process exits.  In host code its name is only a handle; the
+// address a kernel can use is obtained once per device with cudaGetSymbolAddress, while that
+// device is current, and cached.
+// ---------------------------------------------------------------------------------------------
+namespace lrqk {
+namespace {
+constexpr size_t kStaticScratchBytes = 4u << 20;  // 4 MiB: up to 240 heads of head_dim 128
+constexpr int kMaxDevices = 64;
+static __device__ __align__(256) unsigned char g_static_attn_scratch[kStaticScratchBytes];
+static void *g_static_scratch_ptr[kMaxDevices] = {};  // device-usable address, per device
+}  // namespace
+}  // namespace lrqk
+
+extern "C" size_t lrqk_flash_decode_static_capacity_bytes(void) { return lrqk::kStaticScratchBytes; }
+
+extern "C" int lrqk_flash_decode_static(const lrqk_layer *L, const void *q, void *out, int32_t rows, float scale,
+                                        lrqk_stream_t stream) {
+  using namespace lrqk;
+  int rc = check_device();
+  if (rc != LRQK_OK) return rc;
+  rc = check_layer(L);
+  if (rc != LRQK_OK) return rc;
+  if (!q || !out || !L->K_res || !L->V_res) return LRQK_EINVAL;
+  if (rows <= 0) return LRQK_EINVAL;
+  if (rows > L->k + L->m) return LRQK_ECAPACITY;
+  const int n_heads = L->bsz * L->q_heads;
+  if (n_heads > 65535) return LRQK_EUNSUPPORTED;
+  if (L->head_dim != 128 && L->head_dim != 64) return LRQK_EUNSUPPORTED;
+  const int splits = plan_splits(n_heads, rows);
+  const size_t ticket_bytes = ((size_t)n_heads * sizeof(int32_t) + 255) / 256 * 256;
+  const size_t need = ticket_bytes + (size_t)n_heads * splits * (size_t)(L->head_dim + 2) * sizeof(float);
+  if (need > kStaticScratchBytes) {
+    char msg[200];
+    snprintf(msg, sizeof(msg),
+             "lrqk_flash_decode_static: %d heads x %d splits need %zu bytes of scratch, the built-in array holds %zu; "
+             "use lrqk_flash_decode with a caller-provided workspace",
+             n_heads, splits, need, kStaticScratchBytes);
+    note_error_text(msg);
+    return LRQK_ECAPACITY;
+  }
+  int dev = -1;
+  LRQK_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return LRQK_EUNSUPPORTED;
+  if (!g_static_scratch_ptr[dev]) {  // set-up, once per device, with that device current
+    void *ptr = nullptr;
+    LRQK_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_attn_scratch));
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  char *scratch = reinterpret_cast<char *>(g_static_scratch_ptr[dev]);
+  cudaStream_t s = as_stream(stream);
+  // the array keeps whatever the previous call left: the tickets must start at zero
+  LRQK_CUDA_TRY(cudaMemsetAsync(scratch, 0, ticket_bytes, s));
+  AttnParams p;
+  p.q = q; p.K_res = L->K_res; p.V_res = L->V_res; p.out = out;
+  p.tickets = reinterpret_cast<int32_t *>(scratch);
+  p.partial = reinterpret_cast<float *>(scratch + ticket_bytes);
+  p.slots = L->k + L->m;
+  p.rows = rows;
+  p.splits = splits;
+  p.chunk = (rows + splits - 1) / splits;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  dim3 grid(splits, n_heads, 1);
+  if (L->head_dim == 128) {
+    LRQK_DISPATCH_DTYPE(L->dtype, T, (flash_decode_kernel<T, 128><<<grid, kAThreads, 0, s>>>(p)));
+  } else {
+    LRQK_DISPATCH_DTYPE(L->dtype, T, (flash_decode_kernel<T, 64><<<grid, kAThreads, 0, s>>>(p)));
   }
   LRQK_LAUNCH_CHECK();
   return LRQK_OK;
