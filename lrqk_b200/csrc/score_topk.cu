@@ -1,13 +1,16 @@
 // Proxy scoring over the rank-r key factors fused with a cluster-wide radix top-k.
 //
-// One thread-block cluster per (batch, query head).  The candidate rows of A_K are cut into
-// one contiguous segment per CTA.  Each CTA streams its segment once from HBM with 32-byte
-// evict-first loads, forms the fp32 dot product with q_hat and keeps the scores -- as
-// order-preserving 32-bit keys -- in shared memory; they never travel to global memory.  The
-// k-th largest key is then found by a three-pass (11+11+10 bit) radix select whose per-CTA
-// histograms are summed through distributed shared memory, and the selected positions are
-// written in ascending order by an ordered compaction (block scans inside a CTA, a DSMEM
-// exchange of counts between CTAs).  Of equal scores the lower position wins.
+// One thread-block cluster per (batch, query head), one CTA of 1024 threads per SM.  The
+// candidate rows of A_K are cut into one contiguous segment per CTA.  Each CTA streams its
+// segment once from HBM with 32-byte evict-first loads, forms the fp32 dot product with q_hat
+// and keeps the scores -- as order-preserving 32-bit keys -- in shared memory; they never
+// travel to global memory.  The k-th largest key is then found by a three-pass (11+11+10 bit)
+// radix select: every CTA builds the histogram of its own keys, and after ONE cluster barrier
+// per pass each CTA reads its peers' histograms through distributed shared memory, so that it
+// knows both the cluster totals (which digit holds the k-th key) and how many of the larger
+// keys sit in lower-ranked CTAs (where its own output starts).  No further exchange is needed:
+// the selected positions are written in ascending order by an ordered compaction in which every
+// thread owns a contiguous run of keys.  Of equal scores the lower position wins.
 //
 // Summation order of a score (fixed, so results are reproducible): the r columns are split
 // over `lanes = row_bytes / vector_bytes` lanes, each lane sums its run left to right with
@@ -22,12 +25,11 @@ namespace cg = cooperative_groups;
 namespace lrqk {
 namespace {
 
-constexpr int kThreads = 512;
-constexpr int kTile = 4 * kThreads;  // keys handled per compaction tile
-constexpr int kBins0 = 2048;         // 11-bit digits for passes 0 and 1, 10 bits for pass 2
+constexpr int kThreads = 1024;
+constexpr int kWarps = kThreads / 32;
+constexpr int kBins = 2048;          // 11-bit digits for passes 0 and 1, 10 bits for pass 2
 constexpr int kUnroll = 4;
-constexpr int kCandPerWarp = 128;      // per-warp list of keys still matching the radix prefix
-constexpr int kCandCap = kCandPerWarp * (kThreads / 32);
+constexpr int kGranule = 4096;       // segment lengths are multiples of this many rows
 
 template <int VB> struct Vec;
 template <> struct Vec<32> {
@@ -77,102 +79,90 @@ struct ScoreTopkParams {
   int64_t a_capacity;
   int64_t candidates;
   int32_t k;
-  int32_t seg_len;      // rows per CTA, multiple of kTile
+  int32_t seg_len;      // rows per CTA, multiple of kGranule
+  uint32_t seg_magic;   // ceil(2^32 / (seg_len / kGranule))
   int32_t *wanted;      // [N, k]
   float *scores_out;    // optional [N, scores_stride]
   int64_t scores_stride;
 };
 
-// Exclusive block scan of one 32-bit value per thread (kThreads threads); returns the
-// exclusive prefix and, through `total`, the block sum.  `scratch` holds 17 words.
-__device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t *scratch, uint32_t &total) {
+// Inclusive block scan of NV 32-bit values per thread at once (kThreads threads).  The values are
+// replaced by their inclusive prefixes; `tot` receives the block sums.  `scratch`: NV*(kWarps+1) words.
+template <int NV>
+__device__ __forceinline__ void block_inclusive_scan(uint32_t (&v)[NV], uint32_t *scratch, uint32_t (&tot)[NV]) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  uint32_t inc = v;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
-    uint32_t t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
-    if (lane >= o) inc += t;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const uint32_t x = __shfl_up_sync(0xFFFFFFFFu, v[i], o);
+      if (lane >= o) v[i] += x;
+    }
   }
-  if (lane == 31) scratch[warp] = inc;
+  if (lane == 31) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) scratch[i * (kWarps + 1) + warp] = v[i];
+  }
   __syncthreads();
   if (warp == 0) {
-    uint32_t w = lane < (kThreads / 32) ? scratch[lane] : 0;
-    uint32_t winc = w;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      uint32_t t = __shfl_up_sync(0xFFFFFFFFu, winc, o);
-      if (lane >= o) winc += t;
+    for (int i = 0; i < NV; ++i) {
+      const uint32_t w0 = scratch[i * (kWarps + 1) + lane];
+      uint32_t w = w0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t x = __shfl_up_sync(0xFFFFFFFFu, w, o);
+        if (lane >= o) w += x;
+      }
+      scratch[i * (kWarps + 1) + lane] = w - w0;  // exclusive warp offsets
+      if (lane == 31) scratch[i * (kWarps + 1) + kWarps] = w;
     }
-    if (lane < (kThreads / 32)) scratch[lane] = winc - w;  // exclusive warp offsets
-    if (lane == 31) scratch[16] = winc;                     // block total
   }
   __syncthreads();
-  const uint32_t res = scratch[warp] + inc - v;
-  total = scratch[16];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    v[i] += scratch[i * (kWarps + 1) + warp];
+    tot[i] = scratch[i * (kWarps + 1) + kWarps];
+  }
   __syncthreads();  // scratch may be reused right away
-  return res;
 }
 
-// Keys live in shared memory with one pad word per 32 so that both access patterns used below
-// (thread-strided and one contiguous run per thread) are free of bank conflicts.
-__device__ __forceinline__ int phys(int i) { return i + (i >> 5); }
-
-// Find the bin that holds the `need`-th largest key given cluster-wide bin totals in `tot_hist`
-// (kBins0 words, larger bin = larger keys).  Returns through bcast[0] the bin, bcast[1] the
-// count still needed inside that bin.  All threads must call.
-__device__ __forceinline__ void pick_bin(const uint32_t *tot_hist, uint32_t need, uint32_t *scratch,
-                                         uint32_t *bcast) {
-  const int tid = threadIdx.x;
-  const uint4 x = *reinterpret_cast<const uint4 *>(tot_hist + 4 * tid);
-  const uint32_t tot[4] = {x.x, x.y, x.z, x.w};
-  const uint32_t mine = tot[0] + tot[1] + tot[2] + tot[3];
-  uint32_t all;
-  const uint32_t below_incl = block_exclusive_scan(mine, scratch, all) + mine;
-  uint32_t above = all - below_incl;  // keys in bins above this thread's four bins
-  if (above < need && need <= above + mine) {
-#pragma unroll
-    for (int j = 3; j >= 0; --j) {
-      if (above + tot[j] >= need) {
-        bcast[0] = (uint32_t)(4 * tid + j);
-        bcast[1] = need - above;
-        break;
-      }
-      above += tot[j];
-    }
-  }
-  __syncthreads();
+// Where the key of local row i lives in shared memory.  Thread t of the compaction owns the
+// 4*V consecutive rows [4*V*t, 4*V*(t+1)); its j-th group of four keys is the 16-byte vector
+// j*kThreads + t, so that the threads of a warp read neighbouring vectors.  `magic` = ceil(2^32 / V).
+__device__ __forceinline__ int key_slot(int i, int V, uint32_t magic) {
+  const uint32_t vec = (uint32_t)i >> 2;
+  const uint32_t t = V == 1 ? vec : __umulhi(vec, magic);  // vec / V, exact for vec < 2^16 (2^32 / 1 does not fit)
+  const uint32_t j = vec - t * (uint32_t)V;
+  return (int)(((j * kThreads + t) << 2) | ((uint32_t)i & 3u));
 }
 
 template <typename T, int R>
-__global__ void __launch_bounds__(kThreads, 2) score_topk_kernel(ScoreTopkParams p) {
+__global__ void __launch_bounds__(kThreads, 1) score_topk_kernel(ScoreTopkParams p) {
   constexpr int RB = R * (int)sizeof(T);          // bytes per row
   constexpr int VB = RB >= 32 ? 32 : 16;          // bytes per lane
   constexpr int LPR = RB / VB;                    // lanes per row
   constexpr int NW = VB / 4;                      // 32-bit words per lane
   constexpr int EPL = Unpack<T, NW>::kElts;       // elements per lane
   constexpr int RPI = kThreads / LPR;             // rows per CTA-wide load
-  static_assert(kTile % (RPI * kUnroll) == 0, "tile must be a whole number of unrolled loads");
+  static_assert(kGranule % (RPI * kUnroll) == 0, "a granule must be a whole number of unrolled loads");
 
   cg::cluster_group cluster = cg::this_cluster();
   const int rank = (int)cluster.block_rank();
   const int csize = (int)cluster.num_blocks();
   const int n = blockIdx.y;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x;
 
   extern __shared__ __align__(16) uint32_t smem[];
-  uint32_t *keys = smem;                                    // [seg_len + seg_len/32], padded
-  uint32_t *hloc = keys + p.seg_len + (p.seg_len >> 5);     // [kBins0] this CTA's histogram of the pass
-  uint32_t *htot = hloc + kBins0;                           // [2][kBins0] cluster totals (peers add into them)
-  uint32_t *cand = htot + 2 * kBins0;                       // [kCandCap] local indices still matching the prefix
-  uint32_t *scratch = cand + kCandCap;                      // [32]
-  uint32_t *bcast = scratch + 32;                           // [8]  {bin, need, n_cand}
-  uint32_t *cnts = bcast + 8;                               // [16][2] (greater, equal) per rank, written by peers
-  uint32_t *wcount = cnts + 32;                             // [16] candidates seen by each warp
+  uint32_t *keys = smem;                       // [seg_len]
+  uint32_t *hist = keys + p.seg_len;           // [3][kBins] this CTA's histogram of each pass (peers read it)
+  uint32_t *scratch = hist + 3 * kBins;          // [2*(kWarps + 1)]
+  uint32_t *bcast = scratch + 2 * (kWarps + 1);  // [6]
 
-  for (int i = tid; i < 3 * kBins0; i += kThreads) hloc[i] = 0;
-  if (tid < 8) bcast[tid] = 0;
+  for (int i = tid; i < 3 * kBins; i += kThreads) hist[i] = 0;
   __syncthreads();
-  cluster.barrier_arrive();  // peers may add into my totals once they have seen this
+  const int V = p.seg_len / (4 * kThreads);  // 16-byte key vectors per thread
+  const uint32_t magic = p.seg_magic;
 
   // ---- streaming pass: scores -> keys in shared memory, pass-0 histogram on the fly -------
   const int64_t seg_begin = (int64_t)rank * p.seg_len;
@@ -212,132 +202,131 @@ __global__ void __launch_bounds__(kThreads, 2) score_topk_kernel(ScoreTopkParams
         uint32_t key = 0;
         if (local < seg_rows) {
           key = order_key(acc);
-          atomicAdd(&hloc[key >> 21], 1u);
+          atomicAdd(&hist[key >> 21], 1u);
           if (p.scores_out) p.scores_out[(int64_t)n * p.scores_stride + seg_begin + local] = acc;
         }
-        keys[phys(local)] = key;
+        keys[key_slot(local, V, magic)] = key;
       }
     }
   }
-  for (int i = n_iter_rows + tid; i < p.seg_len; i += kThreads) keys[phys(i)] = 0;  // padding sorts last
+  for (int i = n_iter_rows + tid; i < p.seg_len; i += kThreads) keys[key_slot(i, V, magic)] = 0;  // padding sorts last
   __syncthreads();
-  cluster.barrier_wait();
 
   // ---- radix select of the k-th largest key over the whole cluster ---------------------------
-  // Three passes (11 + 11 + 10 bits).  Each CTA adds the non-zero bins of its histogram into
-  // every peer's total through distributed shared memory, so that after one cluster barrier each
-  // CTA finds the digit locally.  Passes 1 and 2 only visit the keys that matched so far.
+  // Three passes (11 + 11 + 10 bits).  A pass: local histogram of the digit among the keys that
+  // match the prefix found so far; one cluster barrier; every CTA reads all histograms of the
+  // cluster (two bins per thread and peer) and picks the digit itself.  From the same reads it
+  // learns how many keys above the chosen digit lie in lower-ranked CTAs.
   uint32_t prefix = 0;
   uint32_t need = (uint32_t)p.k;
+  uint32_t out_base = 0;  // selected keys held by lower-ranked CTAs
+  uint32_t quota = 0;     // how many keys equal to the threshold this CTA contributes
 #pragma unroll 1
   for (int pass = 0; pass < 3; ++pass) {
     const int shift = pass == 0 ? 21 : (pass == 1 ? 10 : 0);
     const int bits = pass == 2 ? 10 : 11;
     const uint32_t dmask = (1u << bits) - 1;
-    if (pass == 1) {
-      // candidates: keys whose top 11 bits equal the chosen bin; every warp keeps a private list
-      // (position counter in a register, slots handed out by ballot) so that no atomic is shared
-      uint32_t mine_n = 0;
-      uint32_t *wl = cand + warp * kCandPerWarp;
-      for (int i = tid; i < p.seg_len; i += kThreads) {
-        const uint32_t key = keys[phys(i)];
-        const bool hit = (key >> 21) == prefix;
-        const uint32_t bal = __ballot_sync(0xFFFFFFFFu, hit);
-        if (hit) {
-          atomicAdd(&hloc[(key >> shift) & dmask], 1u);
-          const uint32_t at = mine_n + __popc(bal & ((1u << lane) - 1));
-          if (at < (uint32_t)kCandPerWarp) wl[at] = (uint32_t)i;
-        }
-        mine_n += __popc(bal);
-      }
-      if (lane == 0) wcount[warp] = mine_n;
-      __syncthreads();
-    } else if (pass == 2) {
-      const uint32_t mine_n = wcount[warp];
-      bool overflow = false;
-      for (int w = 0; w < kThreads / 32; ++w) overflow |= wcount[w] > (uint32_t)kCandPerWarp;
-      if (!overflow) {
-        const uint32_t *wl = cand + warp * kCandPerWarp;
-        for (uint32_t c = lane; c < mine_n; c += 32) {
-          const uint32_t key = keys[phys((int)wl[c])];
-          if ((key >> 10) == prefix) atomicAdd(&hloc[key & dmask], 1u);
-        }
-      } else {  // some warp met more matches than its list holds: visit every key
-        for (int i = tid; i < p.seg_len; i += kThreads) {
-          const uint32_t key = keys[phys(i)];
-          if ((key >> 10) == prefix) atomicAdd(&hloc[key & dmask], 1u);
-        }
+    uint32_t *hl = hist + pass * kBins;
+    if (pass > 0) {
+      // histogram of the next digit among the keys that match the prefix so far; four keys per load
+      const uint4 *k4 = reinterpret_cast<const uint4 *>(keys);
+      const int pshift = shift + bits;
+      for (int i = tid; i < (p.seg_len >> 2); i += kThreads) {
+        const uint4 v = k4[i];
+        if ((v.x >> pshift) == prefix) atomicAdd(&hl[(v.x >> shift) & dmask], 1u);
+        if ((v.y >> pshift) == prefix) atomicAdd(&hl[(v.y >> shift) & dmask], 1u);
+        if ((v.z >> pshift) == prefix) atomicAdd(&hl[(v.z >> shift) & dmask], 1u);
+        if ((v.w >> pshift) == prefix) atomicAdd(&hl[(v.w >> shift) & dmask], 1u);
       }
       __syncthreads();
     }
-    uint32_t *ht = htot + (pass & 1) * kBins0;
-#pragma unroll
-    for (int j = 0; j < kBins0 / kThreads; ++j) {
-      const int b = tid + j * kThreads;
-      const uint32_t v = hloc[b];
-      if (v) {
-        hloc[b] = 0;
-        for (int c = 0; c < csize; ++c) atomicAdd(cluster.map_shared_rank(ht, c) + b, v);
-      }
+    cluster.sync();  // every CTA's histogram of this pass is complete and visible
+    uint32_t tot[2] = {0u, 0u}, low[2] = {0u, 0u};
+    for (int c = 0; c < csize; ++c) {
+      const uint2 v = *reinterpret_cast<const uint2 *>(cluster.map_shared_rank(hl, c) + 2 * tid);
+      tot[0] += v.x; tot[1] += v.y;
+      if (c < rank) { low[0] += v.x; low[1] += v.y; }
     }
-    cluster.sync();  // every CTA's contribution has landed
-    pick_bin(ht, need, scratch, bcast);
-    prefix = (prefix << bits) | bcast[0];
-    need = bcast[1];
-    if (pass == 0) {  // totals[0] is used again by pass 2; peers add to it only after the next barrier
+    if (pass == 2) cluster.barrier_arrive();  // this CTA reads no peer's memory after this point
+    const uint32_t mine = tot[0] + tot[1];
+    uint32_t inc[2] = {mine, low[0] + low[1]}, all[2];
+    block_inclusive_scan<2>(inc, scratch, all);
+    uint32_t above = all[0] - inc[0];      // keys in bins above this thread's two bins
+    uint32_t above_low = all[1] - inc[1];  // those of them held by lower-ranked CTAs
+    if (above < need && need <= above + mine) {
 #pragma unroll
-      for (int j = 0; j < kBins0 / kThreads; ++j) ht[tid + j * kThreads] = 0;
+      for (int j = 1; j >= 0; --j) {
+        if (above + tot[j] >= need) {
+          bcast[0] = (uint32_t)(2 * tid + j);
+          bcast[1] = need - above;
+          bcast[2] = above_low;
+          bcast[3] = low[j];
+          break;
+        }
+        above += tot[j];
+        above_low += low[j];
+      }
     }
     __syncthreads();
-  }
-  const uint32_t T_key = prefix;       // the k-th largest key
-  const uint32_t need_ties = need;     // how many keys equal to it are taken (lowest positions)
-
-  // ---- ordered compaction: one contiguous run of keys per thread ------------------------------
-  const int per = p.seg_len / kThreads;
-  uint32_t cg_ = 0, ce_ = 0;
-#pragma unroll 4
-  for (int j = 0; j < per; ++j) {
-    const uint32_t key = keys[phys(tid * per + j)];
-    cg_ += key > T_key;
-    ce_ += key == T_key;
-  }
-  uint32_t cta_total;
-  const uint32_t ex = block_exclusive_scan(cg_ | (ce_ << 16), scratch, cta_total);  // counts fit 16 bits
-  if (tid < csize) {  // tell every rank how many keys this CTA holds above / at the threshold
-    uint32_t *rc = cluster.map_shared_rank(cnts, tid);
-    rc[2 * rank] = cta_total & 0xFFFFu;
-    rc[2 * rank + 1] = cta_total >> 16;
-  }
-  cluster.sync();
-  uint32_t out_base = 0, tie_base = 0, quota = 0;
-  for (int c = 0; c <= rank; ++c) {
-    const uint32_t g = cnts[2 * c], e = cnts[2 * c + 1];
-    const uint32_t left = need_ties > tie_base ? need_ties - tie_base : 0;
-    const uint32_t q = e < left ? e : left;
-    if (c < rank) { out_base += g + q; tie_base += e; }
-    else quota = q;
-  }
-  int32_t *out = p.wanted + (int64_t)n * p.k;
-  uint32_t gb = ex & 0xFFFFu, eb = ex >> 16;
-#pragma unroll 4
-  for (int j = 0; j < per; ++j) {
-    const int i = tid * per + j;
-    const uint32_t key = keys[phys(i)];
-    const bool is_g = key > T_key, is_e = key == T_key;
-    if (is_g || (is_e && eb < quota)) {
-      const uint32_t pos = out_base + gb + (eb < quota ? eb : quota);
-      if (pos < (uint32_t)p.k) out[pos] = (int32_t)(seg_begin + i);
+    prefix = (prefix << bits) | bcast[0];
+    need = bcast[1];
+    out_base += bcast[2];
+    if (pass == 2) {
+      const uint32_t ties_low = bcast[3];          // keys equal to the threshold in lower-ranked CTAs
+      const uint32_t ties_mine = hl[bcast[0]];
+      const uint32_t left = need > ties_low ? need - ties_low : 0u;
+      quota = ties_mine < left ? ties_mine : left;
+      out_base += ties_low < need ? ties_low : need;
     }
-    gb += is_g;
-    eb += is_e;
+    __syncthreads();  // bcast is rewritten by the next pass
   }
-  // no peer touches this CTA's shared memory after the last cluster barrier above
+  const uint32_t T_key = prefix;  // the k-th largest key
+
+  // ---- ordered compaction: every thread owns 4*V consecutive rows -----------------------------
+  // Selected keys are rare, so a group of four keys is looked at closely only if its largest
+  // reaches the threshold.  Counts travel as one word: keys above the threshold in the low half,
+  // equal keys in the high half.
+  const uint4 *k4 = reinterpret_cast<const uint4 *>(keys);
+  uint32_t cnt[1] = {0u};
+  for (int j = 0; j < V; ++j) {
+    const uint4 v = k4[j * kThreads + tid];
+    if (max(max(v.x, v.y), max(v.z, v.w)) >= T_key) {
+      cnt[0] += (uint32_t)(v.x > T_key) + (uint32_t)(v.y > T_key) + (uint32_t)(v.z > T_key) + (uint32_t)(v.w > T_key) +
+                (((uint32_t)(v.x == T_key) + (uint32_t)(v.y == T_key) + (uint32_t)(v.z == T_key) +
+                  (uint32_t)(v.w == T_key)) << 16);
+    }
+  }
+  const uint32_t own = cnt[0];
+  uint32_t cta_total[1];
+  block_inclusive_scan<1>(cnt, scratch, cta_total);
+  if (own != 0u) {
+    const uint32_t at = cnt[0] - own;
+    uint32_t g_at = at & 0xFFFFu, e_at = at >> 16;
+    int32_t *out = p.wanted + (int64_t)n * p.k;
+    const int32_t first = (int32_t)seg_begin + tid * 4 * V;
+    for (int j = 0; j < V; ++j) {
+      const uint4 v = k4[j * kThreads + tid];
+      if (max(max(v.x, v.y), max(v.z, v.w)) >= T_key) {
+        const uint32_t kk[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const bool is_g = kk[t] > T_key, is_e = kk[t] == T_key;
+          if (is_g || (is_e && e_at < quota)) {
+            const uint32_t pos = out_base + g_at + (e_at < quota ? e_at : quota);
+            if (pos < (uint32_t)p.k) out[pos] = first + 4 * j + t;
+          }
+          g_at += is_g;
+          e_at += is_e;
+        }
+      }
+    }
+  }
+  cluster.barrier_wait();  // peers may still be reading this CTA's histograms
 }
 
 template <typename T, int R>
 int launch_score_topk(const ScoreTopkParams &p, int n_heads, int csize, cudaStream_t stream) {
-  const size_t smem = ((size_t)p.seg_len + (p.seg_len >> 5) + 3 * kBins0 + kCandCap + 32 + 8 + 32 + 16) * sizeof(uint32_t);
+  const size_t smem = ((size_t)p.seg_len + 3 * kBins + 2 * (kWarps + 1) + 6) * sizeof(uint32_t);
   auto kern = score_topk_kernel<T, R>;
   static size_t smem_set = 0;
   static bool nonportable_set = false;
@@ -379,22 +368,22 @@ int dispatch_rank(int r, const ScoreTopkParams &p, int n_heads, int csize, cudaS
 }  // namespace
 
 // Cluster size and segment length for `candidates` rows per head and n_heads heads.
-// The keys of a segment must fit in shared memory; beyond that, more CTAs per head are used
-// while the grid stays within about two resident CTAs per SM.
+// One CTA per SM (its keys fill most of the SM's shared memory).  The smallest cluster whose
+// segment fits is grown while the whole grid still fits the SMs in a single, evenly loaded
+// wave and every CTA keeps at least one granule of rows.
 int plan_score_topk(int64_t candidates, int n_heads, int *csize_out, int *seg_len_out) {
-  const int64_t max_seg = 45056;  // 176 KiB of keys next to the histograms
+  const int64_t max_seg = 49152;  // 192 KiB of keys next to the histograms
   int best = -1;
   for (int cs = 1; cs <= 16; cs *= 2) {
-    const int64_t seg = ceil_div64(ceil_div64(candidates, cs), kTile) * kTile;
+    const int64_t seg = ceil_div64(ceil_div64(candidates, cs), kGranule) * kGranule;
     if (seg > max_seg) continue;
     if (best < 0) { best = cs; continue; }  // smallest cluster whose segment fits
-    // grow the cluster (portable sizes only) while the whole grid stays resident at once
-    // (two 80-KiB CTAs per SM) and every CTA still gets at least one full tile of rows
-    if (cs <= 8 && (int64_t)n_heads * cs <= 2 * kNumSMs && ceil_div64(candidates, cs) >= kTile) best = cs;
+    // (clusters of more than 8 CTAs are not grown into: they launch far more slowly)
+    if (cs <= 8 && (int64_t)n_heads * cs <= kNumSMs && ceil_div64(candidates, cs) >= kGranule) best = cs;
   }
   if (best < 0) return LRQK_EUNSUPPORTED;
   *csize_out = best;
-  *seg_len_out = (int)(ceil_div64(ceil_div64(candidates, best), kTile) * kTile);
+  *seg_len_out = (int)(ceil_div64(ceil_div64(candidates, best), kGranule) * kGranule);
   return LRQK_OK;
 }
 
@@ -426,6 +415,10 @@ extern "C" int lrqk_score_topk(const lrqk_layer *L, const void *q_hat, int64_t c
   rc = plan_score_topk(candidates, n_heads, &csize, &seg_len);
   if (rc != LRQK_OK) return rc;
   p.seg_len = seg_len;
+  {
+    const uint32_t v = (uint32_t)(seg_len / kGranule);
+    p.seg_magic = (uint32_t)((0x100000000ull + v - 1) / v);
+  }
   LRQK_DISPATCH_DTYPE(L->dtype, T, return dispatch_rank<T>(L->r, p, n_heads, csize, as_stream(stream)));
   return LRQK_EUNSUPPORTED;
 }
