@@ -1,10 +1,19 @@
 // Exact single-query attention over the resident rows, split over the row axis.
 //
-// Grid (splits, B*Hq).  A CTA streams its slice of K_res and V_res once with 16-byte loads
-// (a K or V row is spread over d*elt/16 lanes), keeps a running (max, sum, accumulator) per
-// lane group in fp32 with base-2 exponentials, and leaves one partial per split in the
-// workspace.  The CTA that finishes last for a head (an atomic ticket) folds the partials in
-// split order and writes the output row, then re-arms the ticket.
+// Grid (splits, B*Hq), sized so that the whole grid is resident at once.  A CTA owns a contiguous
+// run of rows of one head.  Everything it reads is requested before anything is waited for: one
+// thread starts a bulk asynchronous copy (cp.async.bulk, completion on an mbarrier) that brings
+// the run of K_res into shared memory, and every thread loads its share of V_res into registers.
+// Scores are formed as soon as the keys have landed (a row spread over the lanes of a sub-warp,
+// 16 bytes each), the softmax weights are taken against the run's maximum in base 2, and the
+// weighted sum of the values follows from the registers.  One partial
+// (unnormalised sum, maximum, weight sum) per split goes to the workspace; the CTA that finishes
+// last for a head (an atomic ticket) folds the partials in split order, writes the output row and
+// re-arms the ticket.  Runs longer than the staging buffers are processed in several rounds with
+// the usual running-maximum rescale.
+//
+// The wait on the mbarrier is bounded: if it runs out, the CTA records it in the status word,
+// contributes an empty partial and still takes its ticket, so nothing is left waiting.
 #include <math.h>
 #include <stdio.h>
 
@@ -13,128 +22,194 @@
 namespace lrqk {
 namespace {
 
-constexpr int kAThreads = 128;
-constexpr int kAUnroll = 4;
-constexpr int kMaxSplits = 32;
+constexpr int kAThreads = 256;
+constexpr int kAWarps = kAThreads / 32;
+constexpr int kMaxSplits = 64;
+constexpr int kStageBytes = 32 * 1024;        // staging buffer for the keys of one round
+constexpr uint32_t kWaitLimit = 1u << 22;     // polls of an mbarrier before giving up
 
 struct AttnParams {
   const void *q, *K_res, *V_res;
   void *out;
   float *partial;     // [N][splits][D+2]
   int32_t *tickets;   // [N]
+  int32_t *status;    // set to LRQK_ETIMEOUT if a bounded wait ran out
   int32_t slots;      // rows allocated per head (k + m)
   int32_t rows;       // rows attended
   int32_t splits, chunk;
   float scale_log2;   // softmax scale * log2(e)
 };
 
-template <int EPV>
-__device__ __forceinline__ void merge_state(float &m, float &l, float (&acc)[EPV], float m2, float l2,
-                                            const float (&acc2)[EPV]) {
-  const float mn = fmaxf(m, m2);
-  if (mn == -INFINITY) return;  // both empty
-  const float c1 = exp2f(m - mn), c2 = exp2f(m2 - mn);
-  l = l * c1 + l2 * c2;
-#pragma unroll
-  for (int e = 0; e < EPV; ++e) acc[e] = acc[e] * c1 + acc2[e] * c2;
-  m = mn;
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity) {
+  const uint32_t a = smem_addr(bar);
+  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(a), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
 }
 
 template <typename T, int D>
-__global__ void __launch_bounds__(kAThreads) flash_decode_kernel(AttnParams p) {
+__global__ void __launch_bounds__(kAThreads, 4) flash_decode_kernel(AttnParams p) {
   constexpr int EPV = Elt<T>::kPerVec;            // elements per 16-byte vector
   constexpr int LPR = D / EPV;                    // lanes per row
-  constexpr int GPW = 32 / LPR;                   // rows handled side by side in a warp
-  constexpr int NWARP = kAThreads / 32;
+  constexpr int GROUPS = kAThreads / LPR;         // rows handled side by side by the CTA
+  constexpr int ROW_BYTES = D * (int)sizeof(T);
+  constexpr int STAGE_ROWS = kStageBytes / ROW_BYTES;
+  constexpr int RPT = STAGE_ROWS / GROUPS;        // rows per thread and round (8 for every supported shape)
   const int split = blockIdx.x, n = blockIdx.y;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int lir = lane % LPR, grp = lane / LPR;
+  const int lir = tid % LPR, grp = tid / LPR;
 
-  __shared__ float sm_acc[NWARP][LPR][EPV + 2];
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  T *sK = reinterpret_cast<T *>(smem_raw);                         // [STAGE_ROWS][D]; reused for the group sums
+  float *s_w = reinterpret_cast<float *>(smem_raw + kStageBytes);  // [STAGE_ROWS] scores, then weights
+  float *s_red = s_w + STAGE_ROWS;                                 // [kAWarps] block reduction
+  uint64_t *bar = reinterpret_cast<uint64_t *>(s_red + kAWarps);
   __shared__ int is_last;
 
-  float qf[EPV];
-  {
-    float raw[EPV];
-    Elt<T>::unpack(ld16(reinterpret_cast<const T *>(p.q) + (int64_t)n * D + lir * EPV), raw);
-#pragma unroll
-    for (int e = 0; e < EPV; ++e) qf[e] = raw[e] * p.scale_log2;
-  }
-  const T *Kb = reinterpret_cast<const T *>(p.K_res) + (int64_t)n * p.slots * D + lir * EPV;
-  const T *Vb = reinterpret_cast<const T *>(p.V_res) + (int64_t)n * p.slots * D + lir * EPV;
   const int r_begin = split * p.chunk;
   const int r_end = min(p.rows, r_begin + p.chunk);
+  const char *Kg = reinterpret_cast<const char *>(p.K_res) + ((int64_t)n * p.slots) * ROW_BYTES;
+  const char *Vg = reinterpret_cast<const char *>(p.V_res) + ((int64_t)n * p.slots) * ROW_BYTES + lir * 16;
 
-  float m_run = -INFINITY, l_run = 0.0f, acc[EPV];
-#pragma unroll
-  for (int e = 0; e < EPV; ++e) acc[e] = 0.0f;
-
-  constexpr int STEP = NWARP * GPW;  // rows per CTA-wide load
-  for (int base = r_begin; base < r_end; base += kAUnroll * STEP) {  // CTA-uniform trip count
-    const int r0 = base + warp * GPW + grp;
-    uint4 kv[kAUnroll], vv[kAUnroll];
-#pragma unroll
-    for (int u = 0; u < kAUnroll; ++u) {
-      const int row = r0 + u * STEP;
-      if (row < r_end) {
-        kv[u] = ld16(Kb + (int64_t)row * D);
-        vv[u] = ld16(Vb + (int64_t)row * D);
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < kAUnroll; ++u) {
-      const int row = r0 + u * STEP;
-      const bool valid = row < r_end;
-      float kf[EPV], vf[EPV];
-      float s = 0.0f;
-      if (valid) {
-        Elt<T>::unpack(kv[u], kf);
-        Elt<T>::unpack(vv[u], vf);
-#pragma unroll
-        for (int e = 0; e < EPV; ++e) s = fmaf(kf[e], qf[e], s);
-      }
-#pragma unroll
-      for (int o = LPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
-      if (valid) {
-        const float mn = fmaxf(m_run, s);
-        const float corr = exp2f(m_run - mn);  // exp2f(-inf) = 0 on the first row
-        const float pr = exp2f(s - mn);
-        l_run = l_run * corr + pr;
-#pragma unroll
-        for (int e = 0; e < EPV; ++e) acc[e] = acc[e] * corr + pr * vf[e];
-        m_run = mn;
-      }
-    }
-  }
-  // fold the row groups of a warp, then the warps of the CTA
-#pragma unroll
-  for (int o = LPR; o < 32; o <<= 1) {
-    const float m2 = __shfl_xor_sync(0xFFFFFFFFu, m_run, o);
-    const float l2 = __shfl_xor_sync(0xFFFFFFFFu, l_run, o);
-    float a2[EPV];
-#pragma unroll
-    for (int e = 0; e < EPV; ++e) a2[e] = __shfl_xor_sync(0xFFFFFFFFu, acc[e], o);
-    merge_state<EPV>(m_run, l_run, acc, m2, l2, a2);
-  }
-  if (grp == 0) {
-#pragma unroll
-    for (int e = 0; e < EPV; ++e) sm_acc[warp][lir][e] = acc[e];
-    sm_acc[warp][lir][EPV] = m_run;
-    sm_acc[warp][lir][EPV + 1] = l_run;
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(bar)));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  float *part = p.partial + ((int64_t)n * p.splits + split) * (D + 2);
-  if (warp == 0 && grp == 0) {
+
+  float m_run = -INFINITY, l_run = 0.0f;
+  float2 acc[EPV / 2], qf[EPV / 2];  // pairs of neighbouring dimensions: two fused multiply-adds per instruction
 #pragma unroll
-    for (int w = 1; w < NWARP; ++w) {
-      float a2[EPV];
+  for (int e = 0; e < EPV / 2; ++e) acc[e] = make_float2(0.0f, 0.0f);
+  bool timed_out = false;
+  uint32_t parity = 0;
+
+  for (int base = r_begin; base < r_end; base += STAGE_ROWS) {  // CTA-uniform trip count
+    const int nrows = min(STAGE_ROWS, r_end - base);
+    // everything this round reads is requested before anything is waited for: the keys by one bulk
+    // copy into shared memory, the values straight into registers
+    if (tid == 0) {
+      const uint32_t bytes = (uint32_t)nrows * ROW_BYTES;
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(smem_addr(sK)), "l"(Kg + (int64_t)base * ROW_BYTES), "r"(bytes), "r"(smem_addr(bar)) : "memory");
+    }
+    if (base == r_begin) {
+      float raw[EPV];
+      Elt<T>::unpack(ld16(reinterpret_cast<const T *>(p.q) + (int64_t)n * D + lir * EPV), raw);
 #pragma unroll
-      for (int e = 0; e < EPV; ++e) a2[e] = sm_acc[w][lir][e];
-      merge_state<EPV>(m_run, l_run, acc, sm_acc[w][lir][EPV], sm_acc[w][lir][EPV + 1], a2);
+      for (int e = 0; e < EPV / 2; ++e) qf[e] = make_float2(raw[2 * e] * p.scale_log2, raw[2 * e + 1] * p.scale_log2);
+    }
+    uint4 vv[RPT];
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+      const int j = grp + i * GROUPS;
+      vv[i] = j < nrows ? ld_stream16(Vg + (int64_t)(base + j) * ROW_BYTES) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    // ---- scores of this round -------------------------------------------------------------
+    if (!mbar_wait_bounded(bar, parity)) timed_out = true;
+    float sc[RPT];
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+      const int j = grp + i * GROUPS;
+      float2 s2 = make_float2(0.0f, 0.0f);
+      if (j < nrows) {
+        float kf[EPV];
+        Elt<T>::unpack(*reinterpret_cast<const uint4 *>(sK + (size_t)j * D + lir * EPV), kf);
+#pragma unroll
+        for (int e = 0; e < EPV / 2; ++e) s2 = __ffma2_rn(make_float2(kf[2 * e], kf[2 * e + 1]), qf[e], s2);
+      }
+      sc[i] = s2.x + s2.y;
+    }
+    // The RPT partial sums of a lane are folded over the LPR lanes of its row group by a
+    // transposing butterfly: each step halves the number of values a lane carries, so the fold
+    // costs RPT - 1 + log2(LPR / RPT) shuffles instead of RPT * log2(LPR).  Every lane of the
+    // warp takes part in every shuffle.
+    int mine = 0;  // which of the thread's rows this lane ends up holding the full score of
+    {
+      int o = LPR / 2;
+#pragma unroll
+      for (int half = RPT / 2; half >= 1; half >>= 1, o >>= 1) {
+        const bool up = (lir & o) != 0;
+#pragma unroll
+        for (int i = 0; i < half; ++i) {
+          const float send = up ? sc[i] : sc[i + half];
+          const float keep = up ? sc[i + half] : sc[i];
+          sc[i] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, o);
+        }
+        if (up) mine += half;
+      }
+#pragma unroll
+      for (; o >= 1; o >>= 1) sc[0] += __shfl_xor_sync(0xFFFFFFFFu, sc[0], o);
+    }
+    float mx = -INFINITY;
+    {
+      const int j = grp + mine * GROUPS;
+      if (j < nrows) {
+        s_w[j] = sc[0];  // (lanes that hold the same row write the same value)
+        mx = sc[0];
+      }
     }
 #pragma unroll
-    for (int e = 0; e < EPV; ++e) part[lir * EPV + e] = acc[e];
-    if (lir == 0) { part[D] = m_run; part[D + 1] = l_run; }
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+    if (lane == 0) s_red[warp] = mx;
+    __syncthreads();
+#pragma unroll
+    for (int w = 0; w < kAWarps; ++w) mx = fmaxf(mx, s_red[w]);
+    const float m_new = fmaxf(m_run, mx);
+    const float corr = exp2f(m_run - m_new);  // exp2f(-inf) = 0 in the first round
+    // ---- weighted sum of the values -------------------------------------------------------
+    l_run *= corr;
+#pragma unroll
+    for (int e = 0; e < EPV / 2; ++e) { acc[e].x *= corr; acc[e].y *= corr; }
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+      const int j = grp + i * GROUPS;
+      if (j < nrows) {
+        float vf[EPV];
+        Elt<T>::unpack(vv[i], vf);
+        const float w = exp2f(s_w[j] - m_new);
+        l_run += w;
+        const float2 w2 = make_float2(w, w);
+#pragma unroll
+        for (int e = 0; e < EPV / 2; ++e) acc[e] = __ffma2_rn(w2, make_float2(vf[2 * e], vf[2 * e + 1]), acc[e]);
+      }
+    }
+    m_run = m_new;
+    parity ^= 1u;
+    __syncthreads();  // the key buffer, s_w and s_red are rewritten by the next round
+  }
+  if (timed_out) {  // contribute nothing rather than garbage
+    atomicExch(p.status, (int32_t)LRQK_ETIMEOUT);
+    m_run = -INFINITY; l_run = 0.0f;
+#pragma unroll
+    for (int e = 0; e < EPV / 2; ++e) acc[e] = make_float2(0.0f, 0.0f);
+  }
+  // fold the row groups in group order; the key buffer is free now
+  float *g_acc = reinterpret_cast<float *>(sK);  // [GROUPS][D + 1]
+#pragma unroll
+  for (int e = 0; e < EPV / 2; ++e) {
+    g_acc[grp * (D + 1) + lir * EPV + 2 * e] = acc[e].x;
+    g_acc[grp * (D + 1) + lir * EPV + 2 * e + 1] = acc[e].y;
+  }
+  if (lir == 0) g_acc[grp * (D + 1) + D] = l_run;
+  __syncthreads();
+  float *part = p.partial + ((int64_t)n * p.splits + split) * (D + 2);
+  for (int c = tid; c <= D; c += kAThreads) {
+    float s = 0.0f;
+#pragma unroll 8
+    for (int g = 0; g < GROUPS; ++g) s += g_acc[g * (D + 1) + c];
+    if (c < D) part[c] = s;
+    else { part[D] = m_run; part[D + 1] = s; }
   }
   __threadfence();
   __syncthreads();
@@ -145,32 +220,95 @@ __global__ void __launch_bounds__(kAThreads) flash_decode_kernel(AttnParams p) {
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  // fold the partials of this head in split order
+  // fold the partials of this head in split order.  They are first brought into shared memory by
+  // all threads at once (one trip to memory), up to kFoldSplits splits at a time.
+  constexpr int kFoldSplits = 32;
+  float *buf = reinterpret_cast<float *>(smem_raw);  // [kFoldSplits][D + 2]
   const float *ph = p.partial + (int64_t)n * p.splits * (D + 2);
-  float mx = -INFINITY;
-  for (int s = 0; s < p.splits; ++s) mx = fmaxf(mx, __ldcg(ph + (int64_t)s * (D + 2) + D));
-  for (int e = tid; e < D; e += kAThreads) {
-    float num = 0.0f, den = 0.0f;
-    for (int s = 0; s < p.splits; ++s) {
-      const float *ps = ph + (int64_t)s * (D + 2);
-      const float ms = __ldcg(ps + D);
-      if (ms == -INFINITY) continue;
-      const float c = exp2f(ms - mx);
-      num = fmaf(__ldcg(ps + e), c, num);
-      den = fmaf(__ldcg(ps + D + 1), c, den);
+  float mx = -INFINITY, num = 0.0f, den = 0.0f;
+  for (int s0 = 0; s0 < p.splits; s0 += kFoldSplits) {
+    const int ns = min(kFoldSplits, p.splits - s0);
+    __syncthreads();
+    for (int i = tid; i < ns * (D + 2); i += kAThreads) buf[i] = __ldcg(ph + (int64_t)s0 * (D + 2) + i);
+    __syncthreads();
+    if (tid < D) {
+      for (int s = 0; s < ns; ++s) {
+        const float ms = buf[s * (D + 2) + D];
+        if (ms == -INFINITY) continue;
+        const float mn = fmaxf(mx, ms);
+        const float c0 = exp2f(mx - mn), c1 = exp2f(ms - mn);
+        num = num * c0 + buf[s * (D + 2) + tid] * c1;
+        den = den * c0 + buf[s * (D + 2) + D + 1] * c1;
+        mx = mn;
+      }
     }
-    reinterpret_cast<T *>(p.out)[(int64_t)n * D + e] = Elt<T>::from_float(num / den);
   }
+  if (tid < D) reinterpret_cast<T *>(p.out)[(int64_t)n * D + tid] = Elt<T>::from_float(num / den);
   if (tid == 0) p.tickets[n] = 0;  // re-arm for the next call
 }
 
-int plan_splits(int n_heads, int rows) {
-  int splits = (4 * kNumSMs + n_heads - 1) / n_heads;
+// Rows per staging round for a row of `row_bytes`, and the split count for `rows` rows:
+// one round per CTA while the split count allows it.
+int plan_splits(int row_bytes, int rows) {
+  const int stage_rows = kStageBytes / row_bytes;
+  int splits = (rows + stage_rows - 1) / stage_rows;
   if (splits > kMaxSplits) splits = kMaxSplits;
-  const int by_rows = rows / 32;
-  if (splits > by_rows) splits = by_rows;
   if (splits < 1) splits = 1;
   return splits;
+}
+
+constexpr size_t kAttnSmem = (size_t)kStageBytes + (kStageBytes / 128) * sizeof(float) + kAWarps * sizeof(float) + 16 + 128;
+
+// Workspace layout: [n_heads] tickets, one status word, padding to 256 bytes, then the partials.
+size_t ticket_region_bytes(int n_heads) { return ((size_t)(n_heads + 1) * sizeof(int32_t) + 255) / 256 * 256; }
+
+int launch_flash_decode(const lrqk_layer *L, const void *q, void *out, int32_t rows, float scale, void *scratch,
+                        cudaStream_t s) {
+  const int n_heads = L->bsz * L->q_heads;
+  AttnParams p;
+  p.q = q; p.K_res = L->K_res; p.V_res = L->V_res; p.out = out;
+  p.tickets = reinterpret_cast<int32_t *>(scratch);
+  p.status = p.tickets + n_heads;
+  p.partial = reinterpret_cast<float *>(reinterpret_cast<char *>(scratch) + ticket_region_bytes(n_heads));
+  p.slots = L->k + L->m;
+  p.rows = rows;
+  p.splits = plan_splits((int)(L->head_dim * elt_size(L->dtype)), rows);
+  p.chunk = (rows + p.splits - 1) / p.splits;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  dim3 grid(p.splits, n_heads, 1);
+#define LRQK_ATTN_LAUNCH(T, D)                                                                              \
+  do {                                                                                                      \
+    auto kern = flash_decode_kernel<T, D>;                                                                  \
+    static bool attr_set = false;                                                                           \
+    if (!attr_set) {                                                                                        \
+      LRQK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem)); \
+      attr_set = true;                                                                                      \
+    }                                                                                                       \
+    kern<<<grid, kAThreads, kAttnSmem, s>>>(p);                                                             \
+  } while (0)
+  if (L->head_dim == 128) {
+    LRQK_DISPATCH_DTYPE(L->dtype, T, LRQK_ATTN_LAUNCH(T, 128));
+  } else if (L->head_dim == 64) {
+    LRQK_DISPATCH_DTYPE(L->dtype, T, LRQK_ATTN_LAUNCH(T, 64));
+  } else {
+    return LRQK_EUNSUPPORTED;
+  }
+#undef LRQK_ATTN_LAUNCH
+  LRQK_LAUNCH_CHECK();
+  return LRQK_OK;
+}
+
+int check_attn_args(const lrqk_layer *L, const void *q, const void *out, int32_t rows) {
+  int rc = check_device();
+  if (rc != LRQK_OK) return rc;
+  rc = check_layer(L);
+  if (rc != LRQK_OK) return rc;
+  if (!q || !out || !L->K_res || !L->V_res) return LRQK_EINVAL;
+  if (rows <= 0) return LRQK_EINVAL;
+  if (rows > L->k + L->m) return LRQK_ECAPACITY;
+  if (L->bsz * L->q_heads > 65535) return LRQK_EUNSUPPORTED;
+  if (L->head_dim != 128 && L->head_dim != 64) return LRQK_EUNSUPPORTED;
+  return LRQK_OK;
 }
 
 }  // namespace
@@ -179,43 +317,17 @@ int plan_splits(int n_heads, int rows) {
 extern "C" size_t lrqk_flash_decode_workspace_bytes(const lrqk_layer *L, int32_t rows) {
   (void)rows;
   if (!L) return 0;
-  const size_t n = (size_t)L->bsz * L->q_heads;
-  return n * sizeof(int32_t) + 256 + n * lrqk::kMaxSplits * (size_t)(L->head_dim + 2) * sizeof(float);
+  const int n = L->bsz * L->q_heads;
+  return lrqk::ticket_region_bytes(n) + (size_t)n * lrqk::kMaxSplits * (size_t)(L->head_dim + 2) * sizeof(float);
 }
 
 extern "C" int lrqk_flash_decode(const lrqk_layer *L, const void *q, void *out, int32_t rows, float scale,
                                  void *workspace, lrqk_stream_t stream) {
   using namespace lrqk;
-  int rc = check_device();
+  const int rc = check_attn_args(L, q, out, rows);
   if (rc != LRQK_OK) return rc;
-  rc = check_layer(L);
-  if (rc != LRQK_OK) return rc;
-  if (!q || !out || !workspace || !L->K_res || !L->V_res) return LRQK_EINVAL;
-  if (rows <= 0) return LRQK_EINVAL;
-  if (rows > L->k + L->m) return LRQK_ECAPACITY;
-  const int n_heads = L->bsz * L->q_heads;
-  if (n_heads > 65535) return LRQK_EUNSUPPORTED;
-  AttnParams p;
-  p.q = q; p.K_res = L->K_res; p.V_res = L->V_res; p.out = out;
-  p.tickets = reinterpret_cast<int32_t *>(workspace);
-  const size_t off = ((size_t)n_heads * sizeof(int32_t) + 255) / 256 * 256;
-  p.partial = reinterpret_cast<float *>(reinterpret_cast<char *>(workspace) + off);
-  p.slots = L->k + L->m;
-  p.rows = rows;
-  p.splits = plan_splits(n_heads, rows);
-  p.chunk = (rows + p.splits - 1) / p.splits;
-  p.scale_log2 = scale * 1.4426950408889634f;
-  dim3 grid(p.splits, n_heads, 1);
-  cudaStream_t s = as_stream(stream);
-  if (L->head_dim == 128) {
-    LRQK_DISPATCH_DTYPE(L->dtype, T, (flash_decode_kernel<T, 128><<<grid, kAThreads, 0, s>>>(p)));
-  } else if (L->head_dim == 64) {
-    LRQK_DISPATCH_DTYPE(L->dtype, T, (flash_decode_kernel<T, 64><<<grid, kAThreads, 0, s>>>(p)));
-  } else {
-    return LRQK_EUNSUPPORTED;
-  }
-  LRQK_LAUNCH_CHECK();
-  return LRQK_OK;
+  if (!workspace) return LRQK_EINVAL;
+  return launch_flash_decode(L, q, out, rows, scale, workspace, as_stream(stream));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -235,7 +347,7 @@ extern "C" int lrqk_flash_decode(const lrqk_layer *L, const void *q, void *out, 
 // ---------------------------------------------------------------------------------------------
 namespace lrqk {
 namespace {
-constexpr size_t kStaticScratchBytes = 4u << 20;  // 4 MiB: up to 240 heads of head_dim 128
+constexpr size_t kStaticScratchBytes = 4u << 20;  // 4 MiB: e.g. 470 heads of head_dim 128 at 2112 bf16 rows (17 splits)
 constexpr int kMaxDevices = 64;
 static __device__ __align__(256) unsigned char g_static_attn_scratch[kStaticScratchBytes];
 static void *g_static_scratch_ptr[kMaxDevices] = {};  // device-usable address, per device
@@ -247,18 +359,11 @@ extern "C" size_t lrqk_flash_decode_static_capacity_bytes(void) { return lrqk::k
 extern "C" int lrqk_flash_decode_static(const lrqk_layer *L, const void *q, void *out, int32_t rows, float scale,
                                         lrqk_stream_t stream) {
   using namespace lrqk;
-  int rc = check_device();
+  const int rc = check_attn_args(L, q, out, rows);
   if (rc != LRQK_OK) return rc;
-  rc = check_layer(L);
-  if (rc != LRQK_OK) return rc;
-  if (!q || !out || !L->K_res || !L->V_res) return LRQK_EINVAL;
-  if (rows <= 0) return LRQK_EINVAL;
-  if (rows > L->k + L->m) return LRQK_ECAPACITY;
   const int n_heads = L->bsz * L->q_heads;
-  if (n_heads > 65535) return LRQK_EUNSUPPORTED;
-  if (L->head_dim != 128 && L->head_dim != 64) return LRQK_EUNSUPPORTED;
-  const int splits = plan_splits(n_heads, rows);
-  const size_t ticket_bytes = ((size_t)n_heads * sizeof(int32_t) + 255) / 256 * 256;
+  const int splits = plan_splits((int)(L->head_dim * elt_size(L->dtype)), rows);
+  const size_t ticket_bytes = ticket_region_bytes(n_heads);
   const size_t need = ticket_bytes + (size_t)n_heads * splits * (size_t)(L->head_dim + 2) * sizeof(float);
   if (need > kStaticScratchBytes) {
     char msg[200];
@@ -279,23 +384,7 @@ extern "C" int lrqk_flash_decode_static(const lrqk_layer *L, const void *q, void
   }
   char *scratch = reinterpret_cast<char *>(g_static_scratch_ptr[dev]);
   cudaStream_t s = as_stream(stream);
-  // the array keeps whatever the previous call left: the tickets must start at zero
+  // the array keeps whatever the previous call left: the tickets and the status word must start at zero
   LRQK_CUDA_TRY(cudaMemsetAsync(scratch, 0, ticket_bytes, s));
-  AttnParams p;
-  p.q = q; p.K_res = L->K_res; p.V_res = L->V_res; p.out = out;
-  p.tickets = reinterpret_cast<int32_t *>(scratch);
-  p.partial = reinterpret_cast<float *>(scratch + ticket_bytes);
-  p.slots = L->k + L->m;
-  p.rows = rows;
-  p.splits = splits;
-  p.chunk = (rows + splits - 1) / splits;
-  p.scale_log2 = scale * 1.4426950408889634f;
-  dim3 grid(splits, n_heads, 1);
-  if (L->head_dim == 128) {
-    LRQK_DISPATCH_DTYPE(L->dtype, T, (flash_decode_kernel<T, 128><<<grid, kAThreads, 0, s>>>(p)));
-  } else {
-    LRQK_DISPATCH_DTYPE(L->dtype, T, (flash_decode_kernel<T, 64><<<grid, kAThreads, 0, s>>>(p)));
-  }
-  LRQK_LAUNCH_CHECK();
-  return LRQK_OK;
+  return launch_flash_decode(L, q, out, rows, scale, scratch, s);
 }

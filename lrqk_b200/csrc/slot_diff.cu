@@ -11,9 +11,9 @@
 namespace lrqk {
 namespace {
 
-constexpr int kDThreads = 256;
+constexpr int kDThreads = 1024;
 
-__device__ __forceinline__ uint32_t block_scan_256(uint32_t v, uint32_t *scratch, uint32_t &total) {
+__device__ __forceinline__ uint32_t block_scan(uint32_t v, uint32_t *scratch, uint32_t &total) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   uint32_t inc = v;
 #pragma unroll
@@ -69,14 +69,14 @@ __global__ void __launch_bounds__(kDThreads) slot_diff_kernel(int32_t *table, co
   uint32_t cnt = 0;
   for (int i = begin; i < end; ++i) cnt += resident[i] == 0;
   uint32_t n_missing;
-  uint32_t off = block_scan_256(cnt, scratch, n_missing);
+  uint32_t off = block_scan(cnt, scratch, n_missing);
   for (int i = begin; i < end; ++i)
     if (resident[i] == 0) missing[off++] = w[i];
   // ordered scan over the evicted slots
   cnt = 0;
   for (int i = begin; i < end; ++i) cnt += evict[i];
   uint32_t n_evict;
-  off = block_scan_256(cnt, scratch, n_evict);  // the barrier inside also publishes missing[]
+  off = block_scan(cnt, scratch, n_evict);  // the barrier inside also publishes missing[]
   if (tid == 0) {
     list_base = n_evict ? atomicAdd(list_len, (int32_t)n_evict) : 0;
     miss_count[n] = (int32_t)n_evict;
