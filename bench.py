@@ -12,8 +12,9 @@ fetch from pinned host memory + exact attention).  Inputs are seeded synthetic t
 config's distributions; nothing is read from disk.
 
 N > 1 (torchrun, one rank per GPU): KV heads are sharded across ranks (strong scaling), each rank
-owns its heads' factors, slot tables, resident rows and host store; one all-gather of the
-attention outputs per layer-step.
+owns its heads' factors, slot tables, resident rows and host store; the attention kernel stores its
+output rows into every rank's exchange buffer over NVLink (`--collective nccl`: an NCCL all-gather
+instead), once per layer-step.
 
 `--impl reference` times the CPU restatement of the reference's decode step (oracle/) on the host
 cores for the same workload; the default arm also times it on a bounded sample (`cpu_baseline`).
@@ -215,15 +216,26 @@ def run_ours(args):
     facs, prefill_ms = build_layers(w, layers, hq_l, hkv_l, rank * 1000, device, dtype, args.seed, n_tokens)
     q_all, k_all, v_all = make_steps(args.seed + 1 + rank, n_tokens, layers, w, hq_l, hkv_l, args.rho, device, dtype)
     gathered = torch.empty(world, w["bsz"], hq_l, w["d"], dtype=dtype, device=device) if world > 1 else None
+    exchange = None
+    if world > 1 and args.collective == "push":
+        from lrqk_b200 import sharding
+        exchange = sharding.HeadExchange(w["bsz"] * hq_l, w["d"], dtype)
     setup_s = time.time() - t_setup
 
-    def token(t, sink=None):
-        for li, fac in enumerate(facs):
-            out = fac.decode_attend(q_all[t, li], k_all[t, li], v_all[t, li])
+    def layer(fac, q, k, v):
+        """One layer-step; with several ranks, every rank ends up with the rows of all heads."""
+        if exchange is not None:
+            out = fac.decode_attend_push(q, k, v, exchange)   # the attention epilogue stores into every rank's buffer
+            exchange.wait()
+        else:
+            out = fac.decode_attend(q, k, v)
             if world > 1:
                 dist.all_gather_into_tensor(gathered, out.squeeze(2))
-            if sink is not None:
-                sink[li].copy_(out.squeeze(2), non_blocking=True)
+        return out
+
+    def token(t):
+        for li, fac in enumerate(facs):
+            layer(fac, q_all[t, li], k_all[t, li], v_all[t, li])
 
     def barrier():
         torch.cuda.synchronize()
@@ -257,9 +269,7 @@ def run_ours(args):
     for i in range(args.steps):
         dq.copy_(hq_pin[i], non_blocking=True); dk.copy_(hk_pin[i], non_blocking=True); dv.copy_(hv_pin[i], non_blocking=True)
         for li, fac in enumerate(facs):
-            out = fac.decode_attend(dq[li], dk[li], dv[li])
-            if world > 1:
-                dist.all_gather_into_tensor(gathered, out.squeeze(2))
+            out = layer(fac, dq[li], dk[li], dv[li])
             out_pin[li].copy_(out.squeeze(2), non_blocking=True)
         torch.cuda.current_stream().synchronize()
     e3.record()
@@ -331,13 +341,16 @@ def run_ours(args):
         "data": "synthetic",
         "config": {"workload": args.workload, **{k2: (list(v2) if isinstance(v2, tuple) else v2) for k2, v2 in w.items()},
                    "layers_cycled": layers, "query_rho": args.rho, "sharding": f"kv-heads/{world}",
+                   "exchange": ("none" if world == 1 else
+                                "attention epilogue pushes rows to every rank over NVLink (peer stores + arrival words)"
+                                if exchange is not None else "nccl all_gather_into_tensor"),
                    "l2": "inputs larger than L2: each layer's A_K is %.0f MB and %d layer states are cycled"
                          % (w["bsz"] * hq_l * w["seq"] * w["r"] * 2 / 1e6, layers)},
         "tokens_per_s_8b_equiv": round(1e6 / (us_per_layer * 32), 2),
         "miss_rate": round(miss_rate, 4), "setup_s": round(setup_s, 1), "prefill_ms_per_layer": round(prefill_ms, 2),
         "e2e": {"value": round(us_per_layer_e2e, 2), "unit": "us/layer/step", "h2d_bytes_per_step": int(h2d),
                 "d2h_bytes_per_step": int(d2h)},
-        "gpu_launches": int(args.steps * layers * 7),
+        "gpu_launches": int(args.steps * layers * (7 + (1 if exchange is not None else 0))),
         "roofline": roof, "roofline_hbm": roof_hbm, "kernels": per_kernel,
         "host_link_peak_gbs": round(link_peak, 1), "clocks": clocks,
     }
@@ -345,6 +358,10 @@ def run_ours(args):
         line["cpu_baseline"] = cpu_baseline_from_state(facs[0], w, q_all, k_all, v_all, tcur, n_steps=5)
     if rank == 0:
         print(json.dumps(line), flush=True)
+    if exchange is not None:
+        exchange.check_status()
+        dist.barrier()
+        exchange.close()
     for fac in facs:
         fac.close()
     if world > 1:
@@ -452,6 +469,8 @@ def main():
     ap.add_argument("--rho", type=float, default=0.0)
     ap.add_argument("--seed", type=int, default=2024)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--collective", default="push", choices=["push", "nccl"],
+                    help="N > 1: how the attention rows of all heads reach every rank")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

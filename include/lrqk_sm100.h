@@ -191,11 +191,60 @@ int lrqk_flash_decode_static(const lrqk_layer *L, const void *q, void *out, int3
                              lrqk_stream_t stream);
 
 /* ------------------------------------------------------------------------------------
+ * Exchange of attention outputs between the ranks that shard a layer's KV heads (one process
+ * per GPU of one node).  The reference runs on a single GPU and has no counterpart; the entry
+ * points below stand where its attention output tensor (lrqk_attention.py:2326-2334) is handed
+ * to the output projection, which needs the rows of ALL heads.
+ *
+ * Every rank owns one exchange buffer, made visible to its peers by CUDA IPC:
+ *     data  [2][world][heads_per_rank][d]  elements of the layer dtype   (two alternating halves)
+ *     flags [2][world] int32, 256-byte aligned behind the data            (arrival words)
+ * A push with sequence number seq (1, 2, 3, ...) uses half seq & 1.  The attention kernel of
+ * rank r stores each finished output row into slot [seq & 1][r] of EVERY rank's buffer with plain
+ * peer stores over NVLink and, once all its heads are done, release-stores seq into
+ * flags[seq & 1][r] of every rank.  No multicast object and no collective library is involved.
+ * A rank may run at most one push ahead of its slowest peer, which holds whenever every rank
+ * waits for push seq (lrqk_allgather_wait) before it issues push seq + 1.
+ * ---------------------------------------------------------------------------------- */
+#define LRQK_MAX_PEERS 8
+typedef struct lrqk_peer_group {
+  int32_t world, rank;
+  int32_t heads_per_rank;          /* B * Hq of one rank's shard (the same on all ranks)       */
+  int32_t head_dim, dtype;
+  void *base[LRQK_MAX_PEERS];      /* exchange buffer of every rank as seen from this device   */
+  int32_t *local_counter;          /* device int32[1] of this rank, zero before the first push */
+} lrqk_peer_group;
+
+/* Bytes of one rank's exchange buffer (data and flags). */
+size_t lrqk_peer_buffer_bytes(int32_t world, int32_t heads_per_rank, int32_t head_dim, int32_t dtype);
+/* cudaMalloc + zero-fill of an exchange buffer and its 64-byte IPC handle (allocates; set-up only). */
+int lrqk_peer_buffer_create(size_t bytes, void **dev_ptr, unsigned char handle[64]);
+/* Map a peer's buffer from its handle / undo that / free one's own buffer. */
+int lrqk_peer_buffer_open(const unsigned char handle[64], void **dev_ptr);
+int lrqk_peer_buffer_close(void *dev_ptr);
+int lrqk_peer_buffer_destroy(void *dev_ptr);
+
+/* lrqk_flash_decode whose epilogue also pushes the output rows to every rank of `g`.
+ * `out` may be NULL when only the exchange buffer is wanted. */
+int lrqk_flash_decode_push(const lrqk_layer *L, const void *q, void *out, int32_t rows, float scale,
+                           void *workspace, const lrqk_peer_group *g, int32_t seq, lrqk_stream_t stream);
+/* Wait (bounded) until push `seq` of every rank has arrived in this rank's buffer, then copy the
+ * gathered rows [world][heads_per_rank][d] to gathered_out if it is not NULL.  If the wait runs
+ * out, *status (device int32) is set to LRQK_ETIMEOUT and the copy is skipped; the kernel always
+ * returns, so the stream and the context stay usable. */
+int lrqk_allgather_wait(const lrqk_peer_group *g, int32_t seq, void *gathered_out, int32_t *status,
+                        lrqk_stream_t stream);
+/* How often lrqk_allgather_wait polls an arrival word (about 1 us per poll) before it gives up;
+ * the default, 2^22, is a few seconds.  Process-wide; applies to waits enqueued afterwards. */
+int lrqk_peer_set_wait_polls(uint32_t polls);
+
+/* ------------------------------------------------------------------------------------
  * One whole decode step of a layer: the six calls above in the reference's order
  * (LightAttentionIndicesFactory.decode, lrqk_attention.py:1506-1613, followed by the
  * attention call).  Host-side counters (ring slot, positions, candidate count) are the
  * caller's, exactly as they are Python attributes in the reference.
  * ---------------------------------------------------------------------------------- */
+struct lrqk_peer_group;
 typedef struct lrqk_step_args {
   const void *q;          /* [B,Hq,d]  */
   const void *k_new;      /* [B,Hkv,d] */
@@ -217,6 +266,8 @@ typedef struct lrqk_step_args {
   int32_t *counters;      /* device int32[4]: [0] list length, [1] status, [2] iterations, [3] spare */
   void *project_workspace;
   void *attn_workspace;
+  const struct lrqk_peer_group *peers; /* NULL, or the ranks that receive this layer's attention output */
+  int32_t push_seq;       /* sequence number of this push (see lrqk_flash_decode_push)  */
 } lrqk_step_args;
 
 int lrqk_layer_step(const lrqk_layer *L, const lrqk_step_args *a, lrqk_stream_t stream);

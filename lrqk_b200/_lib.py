@@ -48,6 +48,18 @@ class StepArgs(C.Structure):
         ("q_hat", C.c_void_p), ("wanted", C.c_void_p), ("mask", C.c_void_p), ("miss_count", C.c_void_p),
         ("miss_list", C.c_void_p), ("counters", C.c_void_p),
         ("project_workspace", C.c_void_p), ("attn_workspace", C.c_void_p),
+        ("peers", C.c_void_p), ("push_seq", C.c_int32),
+    ]
+
+
+MAX_PEERS = 8
+
+
+class PeerGroup(C.Structure):
+    """struct lrqk_peer_group."""
+    _fields_ = [
+        ("world", C.c_int32), ("rank", C.c_int32), ("heads_per_rank", C.c_int32), ("head_dim", C.c_int32),
+        ("dtype", C.c_int32), ("base", C.c_void_p * MAX_PEERS), ("local_counter", C.c_void_p),
     ]
 
 
@@ -76,6 +88,15 @@ _SIGNATURES = {
     "lrqk_flash_decode_static_capacity_bytes": (C.c_size_t, []),
     "lrqk_flash_decode_static": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_void_p, C.c_int32, C.c_float,
                                            C.c_void_p]),
+    "lrqk_peer_buffer_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
+    "lrqk_peer_buffer_create": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p]),
+    "lrqk_peer_buffer_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "lrqk_peer_buffer_close": (C.c_int, [C.c_void_p]),
+    "lrqk_peer_buffer_destroy": (C.c_int, [C.c_void_p]),
+    "lrqk_flash_decode_push": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_void_p, C.c_int32, C.c_float, C.c_void_p,
+                                         C.POINTER(PeerGroup), C.c_int32, C.c_void_p]),
+    "lrqk_peer_set_wait_polls": (C.c_int, [C.c_uint32]),
+    "lrqk_allgather_wait": (C.c_int, [C.POINTER(PeerGroup), C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
     "lrqk_layer_step": (C.c_int, [C.POINTER(Layer), C.POINTER(StepArgs), C.c_void_p]),
     "lrqk_d0_indices_select": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
                                          C.c_void_p]),

@@ -18,6 +18,7 @@
 #include <stdio.h>
 
 #include "common.cuh"
+#include "peer.cuh"
 
 namespace lrqk {
 namespace {
@@ -38,6 +39,7 @@ struct AttnParams {
   int32_t rows;       // rows attended
   int32_t splits, chunk;
   float scale_log2;   // softmax scale * log2(e)
+  PushTargets push;   // world == 0: no exchange with other ranks
 };
 
 __device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -243,7 +245,25 @@ __global__ void __launch_bounds__(kAThreads, 4) flash_decode_kernel(AttnParams p
       }
     }
   }
-  if (tid < D) reinterpret_cast<T *>(p.out)[(int64_t)n * D + tid] = Elt<T>::from_float(num / den);
+  if (tid < D) {
+    const T val = Elt<T>::from_float(num / den);
+    if (p.out) reinterpret_cast<T *>(p.out)[(int64_t)n * D + tid] = val;
+    // exchange with the other ranks: the row goes into this rank's slot of every rank's buffer
+    for (int r = 0; r < p.push.world; ++r) reinterpret_cast<T *>(p.push.data[r])[(int64_t)n * D + tid] = val;
+  }
+  if (p.push.world > 0) {
+    __threadfence_system();  // the rows are out before this head is counted
+    __syncthreads();
+    if (tid == 0) {
+      const int done = atomicAdd(p.push.local_counter, 1);
+      if (done == p.push.heads - 1) {  // every head of this rank has been pushed: raise the arrival words
+        *p.push.local_counter = 0;
+        __threadfence_system();
+        for (int r = 0; r < p.push.world; ++r)
+          asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.push.flag[r]), "r"(p.push.seq) : "memory");
+      }
+    }
+  }
   if (tid == 0) p.tickets[n] = 0;  // re-arm for the next call
 }
 
@@ -263,9 +283,24 @@ constexpr size_t kAttnSmem = (size_t)kStageBytes + (kStageBytes / 128) * sizeof(
 size_t ticket_region_bytes(int n_heads) { return ((size_t)(n_heads + 1) * sizeof(int32_t) + 255) / 256 * 256; }
 
 int launch_flash_decode(const lrqk_layer *L, const void *q, void *out, int32_t rows, float scale, void *scratch,
-                        cudaStream_t s) {
+                        cudaStream_t s, const lrqk_peer_group *g = nullptr, int32_t seq = 0) {
   const int n_heads = L->bsz * L->q_heads;
   AttnParams p;
+  p.push.world = 0;
+  if (g) {
+    const size_t esz = elt_size(L->dtype);
+    const size_t half = peer_data_bytes(g->world, g->heads_per_rank, g->head_dim, g->dtype) / 2;
+    const size_t slot = (size_t)g->heads_per_rank * g->head_dim * esz;
+    for (int r = 0; r < g->world; ++r) {
+      char *b = reinterpret_cast<char *>(g->base[r]);
+      p.push.data[r] = b + (size_t)(seq & 1) * half + (size_t)g->rank * slot;
+      p.push.flag[r] = reinterpret_cast<int32_t *>(b + 2 * half) + (seq & 1) * g->world + g->rank;
+    }
+    p.push.local_counter = g->local_counter;
+    p.push.world = g->world;
+    p.push.heads = n_heads;
+    p.push.seq = seq;
+  }
   p.q = q; p.K_res = L->K_res; p.V_res = L->V_res; p.out = out;
   p.tickets = reinterpret_cast<int32_t *>(scratch);
   p.status = p.tickets + n_heads;
@@ -303,7 +338,7 @@ int check_attn_args(const lrqk_layer *L, const void *q, const void *out, int32_t
   if (rc != LRQK_OK) return rc;
   rc = check_layer(L);
   if (rc != LRQK_OK) return rc;
-  if (!q || !out || !L->K_res || !L->V_res) return LRQK_EINVAL;
+  if (!q || !L->K_res || !L->V_res) return LRQK_EINVAL;
   if (rows <= 0) return LRQK_EINVAL;
   if (rows > L->k + L->m) return LRQK_ECAPACITY;
   if (L->bsz * L->q_heads > 65535) return LRQK_EUNSUPPORTED;
@@ -326,8 +361,20 @@ extern "C" int lrqk_flash_decode(const lrqk_layer *L, const void *q, void *out, 
   using namespace lrqk;
   const int rc = check_attn_args(L, q, out, rows);
   if (rc != LRQK_OK) return rc;
-  if (!workspace) return LRQK_EINVAL;
+  if (!workspace || !out) return LRQK_EINVAL;
   return launch_flash_decode(L, q, out, rows, scale, workspace, as_stream(stream));
+}
+
+extern "C" int lrqk_flash_decode_push(const lrqk_layer *L, const void *q, void *out, int32_t rows, float scale,
+                                      void *workspace, const lrqk_peer_group *g, int32_t seq, lrqk_stream_t stream) {
+  using namespace lrqk;
+  int rc = check_attn_args(L, q, out, rows);
+  if (rc != LRQK_OK) return rc;
+  if (!workspace || seq < 1) return LRQK_EINVAL;
+  rc = check_peer_group(g);
+  if (rc != LRQK_OK) return rc;
+  if (g->heads_per_rank != L->bsz * L->q_heads || g->head_dim != L->head_dim || g->dtype != L->dtype) return LRQK_EINVAL;
+  return launch_flash_decode(L, q, out, rows, scale, workspace, as_stream(stream), g, seq);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -361,6 +408,7 @@ extern "C" int lrqk_flash_decode_static(const lrqk_layer *L, const void *q, void
   using namespace lrqk;
   const int rc = check_attn_args(L, q, out, rows);
   if (rc != LRQK_OK) return rc;
+  if (!out) return LRQK_EINVAL;
   const int n_heads = L->bsz * L->q_heads;
   const int splits = plan_splits((int)(L->head_dim * elt_size(L->dtype)), rows);
   const size_t ticket_bytes = ticket_region_bytes(n_heads);

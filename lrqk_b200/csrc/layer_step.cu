@@ -9,7 +9,7 @@ extern "C" int lrqk_layer_step(const lrqk_layer *L, const lrqk_step_args *a, lrq
   if (!a->q || !a->k_new || !a->v_new || !a->q_hat || !a->wanted || !a->mask || !a->miss_count || !a->miss_list ||
       !a->counters || !a->project_workspace)
     return LRQK_EINVAL;
-  if (a->attn_out && !a->attn_workspace) return LRQK_EINVAL;
+  if ((a->attn_out || a->peers) && !a->attn_workspace) return LRQK_EINVAL;
   int rc = lrqk_lite_append(L, a->k_new, a->v_new, a->lite_slot, a->position, a->flush_rows, a->host_row, stream);
   if (rc != LRQK_OK) return rc;
   rc = lrqk_decode_project_update(L, a->q, a->k_new, a->max_iter, a->tol, a->position, a->q_hat, a->counters + 2,
@@ -22,7 +22,11 @@ extern "C" int lrqk_layer_step(const lrqk_layer *L, const lrqk_step_args *a, lrq
   if (rc != LRQK_OK) return rc;
   rc = lrqk_miss_gather(L, a->miss_list, a->counters, stream);
   if (rc != LRQK_OK) return rc;
-  if (a->attn_out) {
+  if (a->peers) {
+    rc = lrqk_flash_decode_push(L, a->q, a->attn_out, L->k + L->m, a->scale, a->attn_workspace, a->peers, a->push_seq,
+                                stream);
+    if (rc != LRQK_OK) return rc;
+  } else if (a->attn_out) {
     rc = lrqk_flash_decode(L, a->q, a->attn_out, L->k + L->m, a->scale, a->attn_workspace, stream);
     if (rc != LRQK_OK) return rc;
   }

@@ -470,7 +470,7 @@ class LightAttentionIndicesFactory:
         return x.reshape(st.bsz, heads, st.head_dim).contiguous()
 
     @torch.no_grad()
-    def _decode(self, query_states, key_states, value_states, attention: bool):
+    def _decode(self, query_states, key_states, value_states, attention: bool, exchange=None):
         st = self.state
         if st is None:
             raise RuntimeError("decode before prefill")
@@ -482,9 +482,14 @@ class LightAttentionIndicesFactory:
         v = self._flat(value_states.to(st.dtype), st.kv_heads)
         slot, position, flush_rows, host_row, candidates = self._step_counters()
         if not self._hook:
-            st.layer_step(st.make_step_args(q, k, v, slot, position, flush_rows, host_row, candidates,
-                                            self.max_iter[1], self.tol[1], attention=attention))
+            args = st.make_step_args(q, k, v, slot, position, flush_rows, host_row, candidates,
+                                     self.max_iter[1], self.tol[1], attention=attention)
+            if exchange is not None:
+                args.peers, args.push_seq = exchange.struct_ptr(), exchange.seq.next_push()
+            st.layer_step(args)
         else:
+            if exchange is not None:
+                raise NotImplementedError("the stage-by-stage path does not push to other ranks")
             # a subclass observes or replaces the difference: run the stages one by one
             st.lite_append(k, v, slot, position, flush_rows, host_row)
             st.project_update(q, k, self.max_iter[1], self.tol[1], position)
@@ -516,6 +521,14 @@ class LightAttentionIndicesFactory:
         """One step including the attention over the resident rows; returns [B,Hq,1,d] (a view
         of a buffer that the next step overwrites)."""
         st = self._decode(query_states, key_states, value_states, attention=True)
+        return st.attn_out.unsqueeze(2)
+
+    def decode_attend_push(self, query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor,
+                           exchange) -> torch.Tensor:
+        """decode_attend for a head-sharded layer: the attention kernel also stores this rank's rows
+        into every rank's exchange buffer (``exchange``: a sharding.HeadExchange).  Follow it with
+        ``exchange.wait()`` to obtain all ranks' rows."""
+        st = self._decode(query_states, key_states, value_states, attention=True, exchange=exchange)
         return st.attn_out.unsqueeze(2)
 
     def miss_counts(self) -> torch.Tensor:

@@ -1,0 +1,197 @@
+"""Sharding of a layer's (batch, KV head) units over the GPUs of one node, and the exchange of
+the attention outputs between the shards.
+
+Every (batch, query head) selection problem of the LRQK path is independent; the host K|V store
+is shared by the G query heads of a KV head, so the unit of ownership is a (batch, KV head) pair.
+``plan_shards`` cuts the units into one contiguous, equally sized run per rank.  Each rank then
+runs the whole per-layer step for its units only; the output projection that follows needs the
+attention rows of ALL heads, which ``HeadExchange`` delivers: the epilogue of the attention kernel
+stores each finished row into every rank's exchange buffer over NVLink (plain peer stores into
+CUDA-IPC mapped memory, one arrival word per source rank), and ``wait`` blocks the stream -- for a
+bounded time -- until all ranks' rows of that push have arrived.  The reference is single-GPU and
+has no counterpart of this file.
+
+``torch.distributed`` is used for the rendezvous only (exchange of the 64-byte IPC handles);
+with the ``gloo`` backend and no GPU the planning and bookkeeping parts still work, which is how
+the CPU tests exercise them.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib
+
+
+@dataclass(frozen=True)
+class Shard:
+    """The units [unit_begin, unit_end) of the row-major (batch, KV head) grid owned by a rank."""
+    rank: int
+    unit_begin: int
+    unit_end: int
+    bsz: int        # batch entries the shard spans
+    kv_heads: int   # KV heads per spanned batch entry
+    b0: int         # first batch entry
+    h0: int         # first KV head
+
+    @property
+    def units(self) -> int:
+        return self.unit_end - self.unit_begin
+
+
+def plan_shards(bsz: int, kv_heads: int, world: int) -> List[Shard]:
+    """Equal contiguous shards of the B x Hkv unit grid.
+
+    KV heads are split first (every rank keeps all batch entries); when there are more ranks than
+    KV heads the batch is split too, so that a shard is ``bsz/b_parts`` batch entries by
+    ``kv_heads/h_parts`` heads.  Raises ValueError when the grid does not divide evenly."""
+    if world < 1 or bsz < 1 or kv_heads < 1:
+        raise ValueError("bsz, kv_heads and world must be positive")
+    if kv_heads % world == 0:
+        h_parts, b_parts = world, 1
+    elif world % kv_heads == 0 and bsz % (world // kv_heads) == 0:
+        h_parts, b_parts = kv_heads, world // kv_heads
+    else:
+        raise ValueError(f"{bsz} x {kv_heads} (batch x KV heads) does not shard evenly over {world} ranks")
+    hb, bb = kv_heads // h_parts, bsz // b_parts
+    shards = []
+    for rank in range(world):
+        bp, hp = divmod(rank, h_parts)
+        shards.append(Shard(rank=rank, unit_begin=rank * hb * bb, unit_end=(rank + 1) * hb * bb,
+                            bsz=bb, kv_heads=hb, b0=bp * bb, h0=hp * hb))
+    return shards
+
+
+def slice_for_shard(x: torch.Tensor, shard: Shard, groups: int = 1) -> torch.Tensor:
+    """The part of a [B, H, ...] tensor a shard owns (H = kv_heads * groups of the full model)."""
+    return x[shard.b0:shard.b0 + shard.bsz, shard.h0 * groups:(shard.h0 + shard.kv_heads) * groups]
+
+
+def assemble(gathered: torch.Tensor, shards: Sequence[Shard], bsz: int, q_heads: int, groups: int) -> torch.Tensor:
+    """[world, b_local, hq_local, d] rows as the exchange delivers them -> [B, Hq, d] in model order."""
+    out = gathered.new_empty((bsz, q_heads) + tuple(gathered.shape[3:]))
+    for s in shards:
+        slice_for_shard(out, s, groups).copy_(gathered[s.rank])
+    return out
+
+
+class PushSequence:
+    """Sequence numbers of the pushes of one exchange buffer: 1, 2, 3, ...; push ``seq`` uses half
+    ``seq & 1`` of the buffer, so a rank may issue push seq + 1 only after it has waited for push
+    seq (that is what keeps a fast rank from overwriting rows a slow peer has not read yet)."""
+
+    def __init__(self):
+        self.issued = 0
+        self.waited = 0
+
+    def next_push(self) -> int:
+        if self.issued != self.waited:
+            raise RuntimeError("push %d has not been waited for; a second push would overwrite the half "
+                               "a peer may still be reading" % self.issued)
+        self.issued += 1
+        return self.issued
+
+    def next_wait(self) -> int:
+        if self.waited >= self.issued:
+            raise RuntimeError("nothing has been pushed since the last wait")
+        self.waited += 1
+        return self.waited
+
+
+class HeadExchange:
+    """Exchange buffers of all ranks, mapped into this process, plus the push/wait bookkeeping."""
+
+    def __init__(self, heads_per_rank: int, head_dim: int, dtype: torch.dtype, group=None,
+                 rank: Optional[int] = None, world: Optional[int] = None, local_ptrs: Optional[Sequence[int]] = None):
+        """Collective over ``group`` (default process group): every rank creates its buffer and the
+        IPC handles are all-gathered.  ``local_ptrs`` (with ``rank`` and ``world``) instead names
+        buffers that already live in this process -- several emulated ranks on one device, see
+        :meth:`local_group`."""
+        from .state import _DTYPES
+        self.lib = _lib.lib()
+        self.heads_per_rank, self.head_dim, self.dtype = heads_per_rank, head_dim, dtype
+        if local_ptrs is not None:
+            self.rank, self.world = rank, world
+            self.ptrs: List[int] = list(local_ptrs)
+            self.own_ptr, self._owns = self.ptrs[rank], False
+        else:
+            import torch.distributed as dist
+            self.rank = dist.get_rank(group) if rank is None else rank
+            self.world = dist.get_world_size(group) if world is None else world
+            if not 1 <= self.world <= _lib.MAX_PEERS:
+                raise ValueError(f"1..{_lib.MAX_PEERS} ranks are supported, got {self.world}")
+            nbytes = self.lib.lrqk_peer_buffer_bytes(self.world, heads_per_rank, head_dim, _DTYPES[dtype])
+            own, handle = C.c_void_p(), C.create_string_buffer(64)
+            _lib.check(self.lib.lrqk_peer_buffer_create(nbytes, C.byref(own), handle), "lrqk_peer_buffer_create")
+            self.own_ptr, self._owns = own.value, True
+            handles = [None] * self.world
+            dist.all_gather_object(handles, handle.raw, group=group)
+            self.ptrs = []
+            for r in range(self.world):
+                if r == self.rank:
+                    self.ptrs.append(self.own_ptr)
+                else:
+                    p = C.c_void_p()
+                    _lib.check(self.lib.lrqk_peer_buffer_open(handles[r], C.byref(p)), "lrqk_peer_buffer_open")
+                    self.ptrs.append(p.value)
+        self.counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self.status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self.gathered = torch.empty((self.world, heads_per_rank, head_dim), dtype=dtype, device="cuda")
+        g = _lib.PeerGroup()
+        g.world, g.rank, g.heads_per_rank, g.head_dim, g.dtype = self.world, self.rank, heads_per_rank, head_dim, _DTYPES[dtype]
+        for r in range(self.world):
+            g.base[r] = self.ptrs[r]
+        g.local_counter = self.counter.data_ptr()
+        self.c = g
+        self.seq = PushSequence()
+
+    @classmethod
+    def local_group(cls, world: int, heads_per_rank: int, head_dim: int, dtype: torch.dtype) -> List["HeadExchange"]:
+        """``world`` emulated ranks inside this process, all buffers on the current device.  Pushes
+        and waits of the emulated ranks must be issued in an order in which every wait finds its
+        pushes already enqueued on the same stream (kernels that wait on one another must never
+        share a GPU as separate launches)."""
+        from .state import _DTYPES
+        lib = _lib.lib()
+        nbytes = lib.lrqk_peer_buffer_bytes(world, heads_per_rank, head_dim, _DTYPES[dtype])
+        ptrs = []
+        for _ in range(world):
+            p, h = C.c_void_p(), C.create_string_buffer(64)
+            _lib.check(lib.lrqk_peer_buffer_create(nbytes, C.byref(p), h), "lrqk_peer_buffer_create")
+            ptrs.append(p.value)
+        members = [cls(heads_per_rank, head_dim, dtype, rank=r, world=world, local_ptrs=ptrs) for r in range(world)]
+        members[0]._local_all = ptrs  # member 0 frees all buffers on close
+        return members
+
+    def struct_ptr(self) -> int:
+        return C.addressof(self.c)
+
+    def wait(self, copy: bool = True) -> torch.Tensor:
+        """Enqueue the bounded wait for the outstanding push; returns [world, heads_per_rank, d]."""
+        seq = self.seq.next_wait()
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        out = C.c_void_p(self.gathered.data_ptr()) if copy else None
+        _lib.check(self.lib.lrqk_allgather_wait(C.byref(self.c), seq, out, C.c_void_p(self.status.data_ptr()), stream),
+                   "lrqk_allgather_wait")
+        return self.gathered
+
+    def check_status(self) -> None:
+        """Synchronising check of the device status word (call it off the hot path)."""
+        code = int(self.status.item())
+        if code != 0:
+            raise _lib.LrqkError(code, "lrqk_allgather_wait", self.lib.lrqk_strerror(code).decode())
+
+    def close(self):
+        if getattr(self, "ptrs", None):
+            torch.cuda.synchronize()
+            if self._owns:
+                for r, p in enumerate(self.ptrs):
+                    if r != self.rank:
+                        self.lib.lrqk_peer_buffer_close(C.c_void_p(p))
+                self.lib.lrqk_peer_buffer_destroy(C.c_void_p(self.own_ptr))
+            for p in getattr(self, "_local_all", []):
+                self.lib.lrqk_peer_buffer_destroy(C.c_void_p(p))
+            self.ptrs = None
