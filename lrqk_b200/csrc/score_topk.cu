@@ -13,8 +13,9 @@
 // thread owns a contiguous run of keys.  Of equal scores the lower position wins.
 //
 // Summation order of a score (fixed, so results are reproducible): the r columns are split
-// over `lanes = row_bytes / vector_bytes` lanes, each lane sums its run left to right with
-// fused multiply-adds starting from zero, and the lanes are combined by a butterfly
+// over `lanes = max(1, row_bytes / 64)` lanes; each lane sums the even and the odd columns of its
+// run separately, left to right with fused multiply-adds starting from zero (the two sums share
+// one packed fp32x2 instruction), adds the two, and the lanes are combined by a butterfly
 // (partner distance 1, 2, 4, ...).
 #include <cooperative_groups.h>
 
@@ -28,7 +29,6 @@ namespace {
 constexpr int kThreads = 1024;
 constexpr int kWarps = kThreads / 32;
 constexpr int kBins = 2048;          // 11-bit digits for passes 0 and 1, 10 bits for pass 2
-constexpr int kUnroll = 4;
 constexpr int kGranule = 4096;       // segment lengths are multiples of this many rows
 
 template <int VB> struct Vec;
@@ -61,6 +61,11 @@ template <int NW> struct Unpack<float, NW> {
 #pragma unroll
     for (int i = 0; i < NW; ++i) f[i] = __uint_as_float(w[i]);
   }
+  // neighbouring columns as the two halves of one 64-bit register pair
+  __device__ static __forceinline__ void pairs(const uint32_t (&w)[NW], float2 (&f)[NW / 2]) {
+#pragma unroll
+    for (int i = 0; i < NW / 2; ++i) f[i] = make_float2(__uint_as_float(w[2 * i]), __uint_as_float(w[2 * i + 1]));
+  }
 };
 template <int NW> struct Unpack<__nv_bfloat16, NW> {
   static constexpr int kElts = 2 * NW;
@@ -69,6 +74,16 @@ template <int NW> struct Unpack<__nv_bfloat16, NW> {
     for (int i = 0; i < NW; ++i) {
       f[2 * i] = __uint_as_float(w[i] << 16);
       f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+  }
+  // The two bf16 halves of a word become the two halves of one 64-bit value, which the compiler
+  // keeps in an aligned register pair: the form the packed fp32x2 multiply-add takes directly.
+  __device__ static __forceinline__ void pairs(const uint32_t (&w)[NW], float2 (&f)[NW]) {
+#pragma unroll
+    for (int i = 0; i < NW; ++i) {
+      const unsigned long long pk =
+          ((unsigned long long)(w[i] & 0xFFFF0000u) << 32) | (unsigned long long)(w[i] << 16);
+      f[i] = make_float2(__uint_as_float((uint32_t)pk), __uint_as_float((uint32_t)(pk >> 32)));
     }
   }
 };
@@ -140,11 +155,14 @@ __device__ __forceinline__ int key_slot(int i, int V, uint32_t magic) {
 template <typename T, int R>
 __global__ void __launch_bounds__(kThreads, 1) score_topk_kernel(ScoreTopkParams p) {
   constexpr int RB = R * (int)sizeof(T);          // bytes per row
-  constexpr int VB = RB >= 32 ? 32 : 16;          // bytes per lane
-  constexpr int LPR = RB / VB;                    // lanes per row
-  constexpr int NW = VB / 4;                      // 32-bit words per lane
-  constexpr int EPL = Unpack<T, NW>::kElts;       // elements per lane
+  constexpr int VB = RB >= 32 ? 32 : 16;          // bytes per load
+  constexpr int VPL = RB >= 64 ? 2 : 1;           // loads per lane and row: a lane covers up to 64 bytes of a row
+  constexpr int LPR = RB / (VB * VPL);            // lanes per row
+  constexpr int NW = VB / 4;                      // 32-bit words per load
+  constexpr int EPV = Unpack<T, NW>::kElts;       // elements per load
+  constexpr int EPL = EPV * VPL;                  // elements per lane
   constexpr int RPI = kThreads / LPR;             // rows per CTA-wide load
+  constexpr int kUnroll = 4 / VPL;                // rows a thread keeps in flight (128 bytes)
   static_assert(kGranule % (RPI * kUnroll) == 0, "a granule must be a whole number of unrolled loads");
 
   cg::cluster_group cluster = cg::this_cluster();
@@ -158,6 +176,7 @@ __global__ void __launch_bounds__(kThreads, 1) score_topk_kernel(ScoreTopkParams
   uint32_t *hist = keys + p.seg_len;           // [3][kBins] this CTA's histogram of each pass (peers read it)
   uint32_t *scratch = hist + 3 * kBins;          // [2*(kWarps + 1)]
   uint32_t *bcast = scratch + 2 * (kWarps + 1);  // [6]
+  float *qs = reinterpret_cast<float *>(bcast + 6);  // [R] q_hat in fp32 (8-byte aligned: the counts before it are even)
 
   for (int i = tid; i < 3 * kBins; i += kThreads) hist[i] = 0;
   __syncthreads();
@@ -168,34 +187,49 @@ __global__ void __launch_bounds__(kThreads, 1) score_topk_kernel(ScoreTopkParams
   const int64_t seg_begin = (int64_t)rank * p.seg_len;
   const int lane_in_row = tid % LPR;
   const int row_in_iter = tid / LPR;
-  float qf[EPL];
-  {
-    const T *qh = reinterpret_cast<const T *>(p.q_hat) + (int64_t)n * R + lane_in_row * EPL;
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) qf[e] = Elt<T>::to_float(qh[e]);
-  }
-  const char *base = reinterpret_cast<const char *>(p.A_K) + ((int64_t)n * p.a_capacity) * RB + lane_in_row * VB;
+  // q_hat as fp32 pairs in shared memory: every lane of a warp reads the same pair (a broadcast)
+  if (tid < R) qs[tid] = Elt<T>::to_float(reinterpret_cast<const T *>(p.q_hat)[(int64_t)n * R + tid]);
+  __syncthreads();
+  const float4 *q4 = reinterpret_cast<const float4 *>(qs + lane_in_row * EPL);
+  const char *base = reinterpret_cast<const char *>(p.A_K) + ((int64_t)n * p.a_capacity) * RB + lane_in_row * (VB * VPL);
   int64_t seg_rows = p.candidates - seg_begin;   // rows of this segment that hold candidates
   if (seg_rows < 0) seg_rows = 0;
   if (seg_rows > p.seg_len) seg_rows = p.seg_len;
   const int n_iter_rows = (int)((seg_rows + RPI * kUnroll - 1) / (RPI * kUnroll)) * (RPI * kUnroll);
+  // rows past the end of the segment re-read its last row (the result is discarded), so that the
+  // loop body is free of special cases
+  const int last_row = seg_rows > 0 ? (int)seg_rows - 1 : 0;
+  const char *seg_base = seg_rows > 0 ? base + seg_begin * RB : base;  // an empty segment reads (and ignores) row 0
 
+  // Rolling prefetch: a thread keeps kUnroll row pieces in flight; as soon as one has been turned
+  // into a key, the piece kUnroll steps ahead is requested into the same registers, so the loads
+  // never drain while the dot products are formed.
+  Vec<VB> v[kUnroll][VPL];
+#pragma unroll
+  for (int u = 0; u < kUnroll; ++u) {
+    const int local = min(u * RPI + row_in_iter, last_row);
+#pragma unroll
+    for (int w = 0; w < VPL; ++w) v[u][w].load(seg_base + (int64_t)local * RB + w * VB);
+  }
   for (int it = 0; it < n_iter_rows; it += RPI * kUnroll) {
-    Vec<VB> v[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const int local = it + u * RPI + row_in_iter;
-      if (local < seg_rows) v[u].load(base + (seg_begin + local) * RB);
-      else v[u].zero();
-    }
+      const int ahead = min(local + RPI * kUnroll, last_row);
+      float2 acc2 = make_float2(0.0f, 0.0f);  // even and odd columns of the lane's run
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int local = it + u * RPI + row_in_iter;
-      float a[EPL];
-      Unpack<T, NW>::run(v[u].w, a);
-      float acc = 0.0f;
+      for (int w = 0; w < VPL; ++w) {
+        float2 a2[EPV / 2];
+        Unpack<T, NW>::pairs(v[u][w].w, a2);
+        v[u][w].load(seg_base + (int64_t)ahead * RB + w * VB);
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) acc = fmaf(a[e], qf[e], acc);
+        for (int e = 0; e < EPV / 4; ++e) {
+          const float4 qq = q4[w * (EPV / 4) + e];
+          acc2 = __ffma2_rn(a2[2 * e], make_float2(qq.x, qq.y), acc2);
+          acc2 = __ffma2_rn(a2[2 * e + 1], make_float2(qq.z, qq.w), acc2);
+        }
+      }
+      float acc = acc2.x + acc2.y;
 #pragma unroll
       for (int o = 1; o < LPR; o <<= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
       if (lane_in_row == 0) {
@@ -326,7 +360,7 @@ __global__ void __launch_bounds__(kThreads, 1) score_topk_kernel(ScoreTopkParams
 
 template <typename T, int R>
 int launch_score_topk(const ScoreTopkParams &p, int n_heads, int csize, cudaStream_t stream) {
-  const size_t smem = ((size_t)p.seg_len + 3 * kBins + 2 * (kWarps + 1) + 6) * sizeof(uint32_t);
+  const size_t smem = ((size_t)p.seg_len + 3 * kBins + 2 * (kWarps + 1) + 6 + R) * sizeof(uint32_t);
   auto kern = score_topk_kernel<T, R>;
   static size_t smem_set = 0;
   static bool nonportable_set = false;
@@ -371,6 +405,10 @@ int dispatch_rank(int r, const ScoreTopkParams &p, int n_heads, int csize, cudaS
 // One CTA per SM (its keys fill most of the SM's shared memory).  The smallest cluster whose
 // segment fits is grown while the whole grid still fits the SMs in a single, evenly loaded
 // wave and every CTA keeps at least one granule of rows.
+// CTAs of a grid of clusters of `cs` that are resident at once with one CTA per SM: a cluster must
+// fit inside one GPC, and the GPCs of the part hold 16 to 20 usable SMs, so clusters of 8 waste some.
+static int kMaxResident(int cs) { return cs >= 8 ? 15 * 8 : (cs == 4 ? 36 * 4 : kNumSMs); }
+
 int plan_score_topk(int64_t candidates, int n_heads, int *csize_out, int *seg_len_out) {
   const int64_t max_seg = 49152;  // 192 KiB of keys next to the histograms
   int best = -1;
@@ -379,7 +417,7 @@ int plan_score_topk(int64_t candidates, int n_heads, int *csize_out, int *seg_le
     if (seg > max_seg) continue;
     if (best < 0) { best = cs; continue; }  // smallest cluster whose segment fits
     // (clusters of more than 8 CTAs are not grown into: they launch far more slowly)
-    if (cs <= 8 && (int64_t)n_heads * cs <= kNumSMs && ceil_div64(candidates, cs) >= kGranule) best = cs;
+    if (cs <= 8 && (int64_t)n_heads * cs <= kMaxResident(cs) && ceil_div64(candidates, cs) >= kGranule) best = cs;
   }
   if (best < 0) return LRQK_EUNSUPPORTED;
   *csize_out = best;

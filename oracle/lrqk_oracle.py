@@ -249,19 +249,24 @@ def proxy_scores(A_K: torch.Tensor, q_hat: torch.Tensor) -> torch.Tensor:
 
 
 def proxy_scores_lane_order(A_K: torch.Tensor, q_hat: torch.Tensor, lanes: int) -> np.ndarray:
-    """Scores from bf16 operands in a fixed fp32 summation order: the r columns are cut
-    into `lanes` equal runs, each run is summed left to right starting from zero,
-    and the run sums are combined by a butterfly (partner distance 1, 2, 4, ...).
-    Products of two bf16 values are exact in fp32, so this order is reproducible
-    bit for bit on any machine; it is the order the CUDA scoring kernel uses."""
+    """Scores in the fixed fp32 summation order of the CUDA scoring kernel: the r columns are
+    cut into `lanes` equal runs; within a run the even and the odd columns are summed
+    separately, left to right starting from zero, and the two sums are added; the run sums
+    are then combined by a butterfly (partner distance 1, 2, 4, ...).  Products of two bf16
+    values are exact in fp32, and for fp32 operands a fused multiply-add is emulated in
+    float64 (exact product, one rounding), so the order is reproducible bit for bit."""
     a = A_K.to(torch.float32).numpy()
     q = q_hat.to(torch.float32).numpy()
     *lead, c, r = a.shape
     per = r // lanes
-    prod = (a * q).astype(np.float32).reshape(*lead, c, lanes, per)
-    run = np.zeros(prod.shape[:-1], dtype=np.float32)
-    for j in range(per):
-        run = (run + prod[..., j]).astype(np.float32)
+    a64 = a.astype(np.float64).reshape(*lead, c, lanes, per)
+    q64 = np.broadcast_to(q.astype(np.float64), a.shape).reshape(*lead, c, lanes, per)
+    even = np.zeros(a64.shape[:-1], dtype=np.float32)
+    odd = np.zeros(a64.shape[:-1], dtype=np.float32)
+    for j in range(0, per, 2):
+        even = (a64[..., j] * q64[..., j] + even.astype(np.float64)).astype(np.float32)
+        odd = (a64[..., j + 1] * q64[..., j + 1] + odd.astype(np.float64)).astype(np.float32)
+    run = (even + odd).astype(np.float32)
     dist = 1
     while dist < lanes:
         idx = np.arange(lanes) ^ dist
