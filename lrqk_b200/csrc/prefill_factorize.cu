@@ -17,6 +17,7 @@
 //                     last row of A_Q.
 // Arithmetic is fp32 on the stored operands, as in the reference (which up-casts to fp32).
 #include "common.cuh"
+#include "gram_tc.cuh"
 #include "smallmat.cuh"
 
 namespace lrqk {
@@ -34,6 +35,7 @@ struct FactorWs {
   int64_t part;      // [2][N][splits][Wp*Wp]   partial Gram matrices of the two sides
   int64_t head;      // [N][head_stride]        per-head scratch of the algebra kernel
   int64_t sweep;     // [N][sweeps][sweep_stride] per-sweep results
+  int64_t status;    // int32 status word of the tensor-core Gram pass
   int64_t total;
   int32_t splits, Wp, head_stride, sweep_stride;
 };
@@ -49,7 +51,8 @@ __host__ __device__ inline FactorWs factor_ws_layout(int n_heads, int r, int d, 
   w.part = 0;
   w.head = w.part + (int64_t)2 * n_heads * splits * w.Wp * w.Wp;
   w.sweep = w.head + (int64_t)n_heads * w.head_stride;
-  w.total = w.sweep + (int64_t)n_heads * sweeps * w.sweep_stride;
+  w.status = w.sweep + (int64_t)n_heads * sweeps * w.sweep_stride;  // one word (4 reserved)
+  w.total = w.status + 4;
   return w;
 }
 
@@ -355,12 +358,30 @@ int run(const lrqk_layer *L, const void *Q, const void *K, float *A_Q, float *A_
   const int n_heads = L->bsz * L->q_heads;
   const int splits = plan_gram_splits(n_heads, seq_len);
   const FactorWs lay = factor_ws_layout(n_heads, R, D, sweeps, splits);
-  GramParams gp;
-  gp.Q = Q; gp.K = K; gp.A_Q0 = A_Q; gp.A_K0 = A_K_init; gp.part = ws + lay.part;
-  gp.seq_len = seq_len; gp.q_heads = L->q_heads; gp.groups = L->q_heads / L->kv_heads; gp.splits = splits;
-  gp.rows_per_split = (int32_t)(ceil_div64(ceil_div64(seq_len, splits), kGramRows) * kGramRows);
-  gram_pass_kernel<T, R, D><<<dim3(splits, n_heads, 2), kFThreads, 0, stream>>>(gp);
-  LRQK_LAUNCH_CHECK();
+  const int groups = L->q_heads / L->kv_heads;
+  bool on_tensor_cores = false;
+  if constexpr (sizeof(T) == 2 && D == 128) {
+    // bf16 prompts: tcgen05 Gram pass.  It rounds the initial left factors to bf16 (they are a
+    // random or column-sampled starting point; the same rounded values enter every product).
+    GramTcArgs ta;
+    ta.Q = Q; ta.K = K; ta.A_Q0 = A_Q; ta.A_K0 = A_K_init; ta.part = ws + lay.part;
+    ta.status = reinterpret_cast<int32_t *>(ws + lay.status);
+    ta.seq_len = seq_len; ta.bsz = L->bsz; ta.q_heads = L->q_heads; ta.kv_heads = L->kv_heads; ta.head_dim = D; ta.r = R;
+    ta.splits = splits;
+    ta.rows_per_split = (int32_t)(ceil_div64(ceil_div64(seq_len, splits), gram_tc_tile_rows()) * gram_tc_tile_rows());
+    LRQK_CUDA_TRY(cudaMemsetAsync(ta.status, 0, sizeof(int32_t), stream));
+    const int rc = launch_gram_tc(ta, stream);
+    if (rc == LRQK_OK) on_tensor_cores = true;
+    else if (rc != LRQK_EUNSUPPORTED) return rc;
+  }
+  if (!on_tensor_cores) {
+    GramParams gp;
+    gp.Q = Q; gp.K = K; gp.A_Q0 = A_Q; gp.A_K0 = A_K_init; gp.part = ws + lay.part;
+    gp.seq_len = seq_len; gp.q_heads = L->q_heads; gp.groups = groups; gp.splits = splits;
+    gp.rows_per_split = (int32_t)(ceil_div64(ceil_div64(seq_len, splits), kGramRows) * kGramRows);
+    gram_pass_kernel<T, R, D><<<dim3(splits, n_heads, 2), kFThreads, 0, stream>>>(gp);
+    LRQK_LAUNCH_CHECK();
+  }
   AlgebraParams ap;
   ap.ws = ws; ap.lay = lay; ap.n_heads = n_heads; ap.sweeps = sweeps;
   algebra_kernel<R, D><<<n_heads, kFThreads, 0, stream>>>(ap);
@@ -368,7 +389,7 @@ int run(const lrqk_layer *L, const void *Q, const void *K, float *A_Q, float *A_
   ApplyParams pp;
   pp.Q = Q; pp.K = K; pp.A_K = L->A_K; pp.B_Q = L->B_Q; pp.B_K = L->B_K; pp.a_q_last = a_q_last;
   pp.ws = ws; pp.lay = lay; pp.sweeps_out = sweeps_out; pp.seq_len = seq_len; pp.a_capacity = L->a_capacity;
-  pp.q_heads = L->q_heads; pp.groups = gp.groups; pp.n_heads = n_heads; pp.sweeps = sweeps; pp.tol = tol;
+  pp.q_heads = L->q_heads; pp.groups = groups; pp.n_heads = n_heads; pp.sweeps = sweeps; pp.tol = tol;
   apply_kernel<T, R, D><<<dim3((unsigned)ceil_div64(seq_len, kApplyRows), n_heads, 1), kFThreads, 0, stream>>>(pp);
   LRQK_LAUNCH_CHECK();
   return LRQK_OK;
