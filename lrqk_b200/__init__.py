@@ -15,7 +15,17 @@ from .lrqk_attention import (  # noqa: F401
     repeat_kv,
 )
 
+from .hf_models import (  # noqa: F401,E402
+    load_lrqk_model,
+    load_model,
+    load_model_hack,
+    load_tokenizer,
+    lrqk_attention_forward,
+    patch_model,
+)
+
 __all__ = [
+    "load_lrqk_model", "load_model", "load_model_hack", "load_tokenizer", "lrqk_attention_forward", "patch_model",
     "AutoIncreaseTensor", "AutoIncreaseTensorSharedKV", "DynamicLRQKCache", "InitAQAK",
     "LightAttentionIndicesFactory", "LightAttentionIndicesNoHitMiss", "PreAllocatedTensor", "repeat_kv",
 ]

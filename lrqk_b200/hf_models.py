@@ -1,0 +1,182 @@
+"""Hugging Face integration: attention forward for Llama / Qwen2 / Mistral decoder layers that
+routes through ``DynamicLRQKCache``, and the reference's loader functions.
+
+Mirrors the reference's patched attention classes and loaders (paths relative to its checkout):
+
+* ``LRQK_LlamaFlashAttention2.forward``   -- lrqk_attention.py:2222-2335
+* ``LRQK_Qwen2FlashAttention2.forward``   -- lrqk_attention.py:2108-2219
+* ``LRQK_MistralFlashAttention2.forward`` -- lrqk_attention.py:2338-2458
+* ``load_model_hack`` / ``load_tokenizer`` / ``load_lrqk_model`` / ``load_model``
+                                          -- lrqk_attention.py:2595-2743
+
+The reference replaces the ``flash_attention_2`` class of transformers 4.47; the attention
+modules of transformers 5.x are a single class per family with one ``forward(hidden_states,
+position_embeddings, attention_mask, past_key_values, **kwargs)``, so here that bound method is
+replaced on every decoder layer (the reference's second pass does the same, :2661-2665).  The
+three families share the code below: q/k/v projections (Qwen2's carry biases), rotary embedding
+from the family's own ``apply_rotary_pos_emb``, the cache call, the output projection.
+
+What the patched forward does with the cache:
+
+* layer still prefilling (``pending`` / ``collecting``): ``cache.update(q, k, v, layer_idx,
+  attention_mask)`` -- the reference's call (:2284-2286) -- returns the prompt's K, V and
+  exact causal attention over them is taken with ``scaled_dot_product_attention`` (the prompt
+  attention is a dense library operation outside the selection path);
+* layer decoding: ``cache.attend(q, k, v, layer_idx)`` runs the whole per-layer step (ring
+  write, rank-r projection, proxy scoring + top-k, hit/miss, miss fetch, attention over the
+  resident rows) in the CUDA library and returns the attention output directly.
+
+Any other cache type falls through to the family's original forward.
+"""
+from __future__ import annotations
+
+import sys
+import types
+import warnings
+from typing import Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from .lrqk_attention import DynamicLRQKCache
+
+SUPPORTED_FAMILIES = ("qwen", "llama", "mistral")
+
+
+def _causal_attention(q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, scaling: float,
+                      pad_mask: Optional[torch.Tensor]) -> torch.Tensor:
+    """Exact attention of q [B,Hq,L,d] over K, V [B,Hkv,S,d] (S >= L; the queries are the last L
+    positions), causal, optionally with a [B,S] padding mask (1 = token).  Returns [B,L,Hq,d]."""
+    L, S = q.shape[2], K.shape[2]
+    mask = None
+    if pad_mask is not None or (L > 1 and L != S):
+        idx_q = torch.arange(S - L, S, device=q.device)[:, None]
+        idx_k = torch.arange(S, device=q.device)[None, :]
+        mask = (idx_k <= idx_q)[None, None]                      # [1,1,L,S]
+        if pad_mask is not None:
+            mask = mask & pad_mask[:, None, None, -S:].to(torch.bool)
+    out = F.scaled_dot_product_attention(q, K, V, attn_mask=mask, is_causal=(mask is None and L > 1),
+                                         scale=scaling, enable_gqa=K.shape[1] != q.shape[1])
+    return out.transpose(1, 2)
+
+
+def _padding_mask(attention_mask: Optional[torch.Tensor], seq_len: int) -> Optional[torch.Tensor]:
+    """The [B,S] token mask the reference's cache expects (:1901-1903), when one can be recovered."""
+    if attention_mask is None:
+        return None
+    if attention_mask.dim() == 2:
+        return attention_mask[:, -seq_len:]
+    return None  # a 4-D causal mask carries no per-token padding information we rely on
+
+
+def lrqk_attention_forward(self, hidden_states: torch.Tensor,
+                           position_embeddings: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                           attention_mask: Optional[torch.Tensor] = None, past_key_values=None, **kwargs):
+    """Replacement for ``{Llama,Qwen2,Mistral}Attention.forward`` of transformers 5.x."""
+    if not isinstance(past_key_values, DynamicLRQKCache):
+        return self._lrqk_original_forward(hidden_states, position_embeddings=position_embeddings,
+                                           attention_mask=attention_mask, past_key_values=past_key_values, **kwargs)
+    cache: DynamicLRQKCache = past_key_values
+    input_shape = hidden_states.shape[:-1]
+    hidden_shape = (*input_shape, -1, self.head_dim)
+    query_states = self.q_proj(hidden_states).view(hidden_shape).transpose(1, 2)
+    key_states = self.k_proj(hidden_states).view(hidden_shape).transpose(1, 2)
+    value_states = self.v_proj(hidden_states).view(hidden_shape).transpose(1, 2)
+    cos, sin = position_embeddings
+    rope = sys.modules[type(self).__module__].apply_rotary_pos_emb
+    query_states, key_states = rope(query_states, key_states, cos, sin)
+
+    q_len = query_states.shape[2]
+    if cache.is_decoding(self.layer_idx):
+        if q_len != 1:
+            raise NotImplementedError("a decoding LRQK layer takes one new token per call, like the reference's "
+                                      "LightAttentionIndicesFactory.decode")
+        attn_output = cache.attend(query_states, key_states, value_states, self.layer_idx).transpose(1, 2)
+    else:
+        pad = _padding_mask(attention_mask, key_states.shape[2])
+        K, V = cache.update(query_states, key_states.contiguous(), value_states.contiguous(), self.layer_idx,
+                            attention_mask=pad)
+        attn_output = _causal_attention(query_states, K, V, self.scaling, _padding_mask(attention_mask, K.shape[2]))
+    attn_output = attn_output.reshape(*input_shape, -1).contiguous()
+    return self.o_proj(attn_output), None
+
+
+def family_of(model_name: str) -> str:
+    """Model family by substring of the name, in the reference's order (:2611-2632)."""
+    mn = model_name.lower()
+    for fam in SUPPORTED_FAMILIES:
+        if fam in mn:
+            return fam
+    raise ValueError(f"Unknown model name: {model_name}")
+
+
+def patch_model(model) -> int:
+    """Replace ``self_attn.forward`` of every decoder layer; returns the number of layers patched."""
+    n = 0
+    for layer in model.model.layers:
+        attn = getattr(layer, "self_attn", None)
+        if attn is None:
+            continue
+        if not hasattr(attn, "_lrqk_original_forward"):
+            attn._lrqk_original_forward = attn.forward
+            attn.forward = types.MethodType(lrqk_attention_forward, attn)
+        n += 1
+    return n
+
+
+def load_model_hack(model_name: str, device=None, yarn=None, base_model=None):
+    """The model with its ``self_attn.forward`` replaced (lrqk_attention.py:2595-2671).
+
+    - model_name: the model name (also selects the family: qwen / llama / mistral)
+    - device: the device to load the model on (``device_map="auto"`` when None)
+    - yarn: additional keyword arguments for ``from_pretrained``
+    - base_model: use this model instead of loading one
+    """
+    import transformers
+    family_of(model_name)
+    if yarn is None:
+        yarn = {}
+    if base_model is not None:
+        model = base_model
+    else:
+        model = transformers.AutoModelForCausalLM.from_pretrained(
+            model_name, attn_implementation="sdpa", dtype=torch.bfloat16, trust_remote_code=True,
+            device_map="auto" if device is None else device, **yarn)
+    patch_model(model)
+    return model.eval()
+
+
+def load_tokenizer(model_name: str, max_length=None):
+    """Left-padding tokenizer with a pad token (lrqk_attention.py:2674-2685)."""
+    import transformers
+    tokenizer = transformers.AutoTokenizer.from_pretrained(model_name, padding_side="left", max_length=max_length)
+    if tokenizer.pad_token is None:
+        tokenizer.pad_token = tokenizer.eos_token
+        tokenizer.pad_token_id = tokenizer.eos_token_id
+    return tokenizer
+
+
+def load_lrqk_model(model_name: str, max_length=None, device=None, yarn=None, base_model=None):
+    """(model, tokenizer) with the LRQK attention forward (lrqk_attention.py:2687-2699)."""
+    model = load_model_hack(model_name, device, yarn=yarn, base_model=base_model)
+    return model, load_tokenizer(model_name, max_length)
+
+
+def load_model(model_name: str, lrqk=True, max_length=None, device=None, yarn=None, base_model=None):
+    """(model, tokenizer); ``lrqk=False`` loads the plain model (lrqk_attention.py:2702-2743)."""
+    import transformers
+    if yarn is None:
+        yarn = {}
+    if device is None:
+        warnings.warn("When device is None, device_map=auto is used. Only single-GPU placement is tested; "
+                      "specify one device explicitly.")
+    if lrqk:
+        model = load_model_hack(model_name, device, yarn=yarn, base_model=base_model)
+    elif base_model is not None:
+        model = base_model
+    else:
+        model = transformers.AutoModelForCausalLM.from_pretrained(
+            model_name, dtype=torch.bfloat16, trust_remote_code=True, attn_implementation="sdpa",
+            device_map="auto" if device is None else device, **yarn)
+    model = model.eval()
+    return model, load_tokenizer(model_name, max_length)

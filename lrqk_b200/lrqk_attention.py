@@ -374,6 +374,15 @@ class LightAttentionIndicesFactory:
         return LayerState(bsz, hq, hkv, d, self.r, self.attn_topk, self.num_lite_tokens, a_capacity=cap,
                           host_capacity=cap, dtype=dtype, device=device, max_iter=self.max_iter[1])
 
+    _side_streams: Dict[torch.device, "torch.cuda.Stream"] = {}
+
+    @classmethod
+    def _side_stream(cls, device) -> "torch.cuda.Stream":
+        device = torch.device(device)
+        if device not in cls._side_streams:
+            cls._side_streams[device] = torch.cuda.Stream(device=device)
+        return cls._side_streams[device]
+
     @torch.no_grad()
     def prefill(self, query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor):
         bsz, hq, seq_len, d = query_states.shape
@@ -388,6 +397,14 @@ class LightAttentionIndicesFactory:
         v = value_states.contiguous()
         st = self.state = self._new_state(bsz, hq, hkv, d, seq_len, q.dtype, q.device)
         self.prefill_length = self.current_len = seq_len
+        # the prompt's K|V rows go to the page-locked host store on a second stream: that copy is bound
+        # by the host link and overlaps the factorisation, which is bound by HBM and the tensor cores
+        main, side = torch.cuda.current_stream(), self._side_stream(q.device)
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            st.kv_pack_host(k, v, 0)
+        k.record_stream(side)
+        v.record_stream(side)
         aq, ak = self._initial_factors(q, k)
         nb = st.lib.lrqk_prefill_factorize_workspace_bytes(C.byref(st.c), seq_len)
         ws = torch.empty((max(nb, 16),), dtype=torch.uint8, device=q.device)
@@ -395,13 +412,13 @@ class LightAttentionIndicesFactory:
         _lib.check(st.lib.lrqk_prefill_factorize(C.byref(st.c), _ptr(q), _ptr(k), _ptr(aq), _ptr(ak), seq_len,
                                                  self.max_iter[0], self.tol[0], _ptr(a_q_last), None, _ptr(ws),
                                                  _stream()), "lrqk_prefill_factorize")
-        st.kv_pack_host(k, v, 0)
         st.host.current_len = seq_len
         st.score_topk(a_q_last, seq_len - self.num_lite_tokens)       # candidates 0 .. S-m-1, :1471-1474
         st.table.copy_(st.wanted)
         st.fill_resident(k, v)
         self.lite_indices = list(range(seq_len - self.num_lite_tokens, seq_len))
         self.lite_len = 0
+        main.wait_stream(side)                                         # the host store is complete from here on
         del aq, ak, ws
 
     def load_state(self, *, A_K, B_Q, B_K, keys, values, table, dtype=None):

@@ -1,0 +1,69 @@
+"""The patched attention forward inside real Hugging Face decoder stacks (random-init, tiny):
+Llama, Qwen2 (QKV bias) and Mistral.  Checks that the prompt pass is exact attention, that the
+decode steps run through ``DynamicLRQKCache.attend`` (the CUDA path) and stay close to the
+full-attention model when almost every token is resident, and that the loaders' helpers behave
+like the reference's (family by substring, forward replaced on every layer)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _tiny(family: str):
+    import transformers
+    common = dict(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                  num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=4096)
+    if family == "llama":
+        cfg = transformers.LlamaConfig(**common, head_dim=64, rope_theta=500000.0)
+    elif family == "qwen":
+        cfg = transformers.Qwen2Config(**common, rope_theta=1e6)
+    else:
+        cfg = transformers.MistralConfig(**common, head_dim=64, sliding_window=None)
+    cfg._attn_implementation = "sdpa"
+    torch.manual_seed(3)
+    model = transformers.AutoModelForCausalLM.from_config(cfg).to(torch.bfloat16).cuda().eval()
+    return model
+
+
+@pytest.mark.parametrize("family", ["llama", "qwen", "mistral"])
+def test_patched_stack_prefills_exactly_and_decodes_through_the_cuda_path(family):
+    from lrqk_b200 import DynamicLRQKCache, load_model_hack
+    from lrqk_b200.hf_models import family_of
+    model = _tiny(family)
+    assert family_of({"llama": "meta-llama/Llama-3-8B", "qwen": "Qwen/Qwen2.5-7B", "mistral": "mistralai/Mistral-7B"}[family]) == family
+    k, m, S = 256, 16, 290
+    ids = torch.randint(0, 512, (2, S), generator=torch.Generator().manual_seed(1)).cuda()
+    with torch.no_grad():
+        ref_prompt = model(input_ids=ids, use_cache=False).logits
+        nxt = ref_prompt[:, -1].argmax(-1, keepdim=True)
+        ref_step = model(input_ids=torch.cat([ids, nxt], 1), use_cache=False).logits[:, -1]
+    patched = load_model_hack(f"tiny-{family}", base_model=model)
+    assert patched is model and all(hasattr(l.self_attn, "_lrqk_original_forward") for l in model.model.layers)
+    cache = DynamicLRQKCache(r=16, num_active_tokens=k, lite_tokens=m, max_iter=2, tol=1e-2, max_sequence_length=1024,
+                             num_key_value_groups=2, init_aq_ak_method="top")
+    with torch.no_grad():
+        out = model(input_ids=ids, past_key_values=cache, use_cache=True)
+        # the prompt pass is exact attention: same logits as the unpatched path up to bf16 noise
+        assert torch.allclose(out.logits.float(), ref_prompt.float(), atol=3e-2, rtol=3e-2)
+        assert all(cache.is_decoding(i) for i in range(2)) and cache.get_seq_length() == S
+        step = model(input_ids=nxt, past_key_values=cache, use_cache=True).logits[:, -1]
+        assert cache.get_seq_length() == S + 1
+        # 272 of the 291 tokens are resident: the decode logits stay close to full attention
+        cos = torch.nn.functional.cosine_similarity(step.float(), ref_step.float(), dim=-1)
+        assert torch.isfinite(step).all() and float(cos.min()) > 0.97, cos
+        tok = step.argmax(-1, keepdim=True)
+        for _ in range(20):                                      # ring wraps once (m = 16)
+            tok = model(input_ids=tok, past_key_values=cache, use_cache=True).logits[:, -1].argmax(-1, keepdim=True)
+        assert cache.get_seq_length() == S + 21
+    # any other cache type takes the family's own forward
+    with torch.no_grad():
+        plain = model(input_ids=ids, use_cache=True).logits
+    assert torch.allclose(plain.float(), ref_prompt.float(), atol=3e-2, rtol=3e-2)
+    for fac in cache.lwattn.values():
+        fac.close()
+
+
+def test_unknown_family_is_rejected_like_the_reference():
+    from lrqk_b200.hf_models import family_of
+    with pytest.raises(ValueError):
+        family_of("gpt2")
