@@ -41,8 +41,14 @@ WORKLOADS = {
     # name: bsz, q heads, kv heads, head dim, prompt length, r, k, m, max_iter, tol
     "cfg2-layer": dict(bsz=1, hq=32, hkv=8, d=128, seq=131072, r=32, k=2048, m=64, max_iter=(2, 2), tol=1e-2),
     "cfg1-layer": dict(bsz=4, hq=32, hkv=8, d=128, seq=32768, r=32, k=2048, m=64, max_iter=(2, 2), tol=1e-2),
+    "cfg3-layer": dict(bsz=8, hq=28, hkv=4, d=128, seq=65536, r=16, k=1024, m=32, max_iter=(1, 1), tol=1e-2),
+    "cfg4-layer": dict(bsz=1, hq=40, hkv=8, d=128, seq=262144, r=64, k=4096, m=128, max_iter=(4, 4), tol=1e-2),
     "cfg0": dict(bsz=1, hq=8, hkv=2, d=128, seq=4096, r=16, k=256, m=16, max_iter=(2, 2), tol=1e-2),
 }
+# dram__bytes (read + write) of one launch from the ncu capture summarised in
+# profiles/path_kernels_cfg2_ncu_sections.md (1 GPU, cfg2-layer)
+NCU_TRAFFIC_CFG2 = {"score_topk": 271.6e6, "flash_decode": 35.2e6, "project_update": 27.2e6, "slot_diff": 0.5e6,
+                    "miss_gather": 0.8e6, "lite_append": 0.0}
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -291,7 +297,8 @@ def run_ours(args):
             slot, position, flush_rows, host_row, cand = fac._step_counters()
             cand_seen = cand
             marks = [torch.cuda.Event(enable_timing=True) for _ in range(7)]
-            marks[0].record()
+            torch.cuda._sleep(400_000)   # ~0.2 ms of GPU idle spin: the host queues the six launches behind it,
+            marks[0].record()            # so the event deltas are device time, not host launch time
             st.lite_append(k, v, slot, position, flush_rows, host_row); marks[1].record()
             st.project_update(q, k, w["max_iter"][1], w["tol"], position); marks[2].record()
             st.score_topk(st.q_hat, cand); marks[3].record()
@@ -323,10 +330,11 @@ def run_ours(args):
         bound = "host_link" if n == "miss_gather" else "hbm"
         peak = link_peak if n == "miss_gather" else hbm_peak
         per_kernel[n] = {"us": round(stage_us[n], 2), "bytes": int(bytes_[n]), "bound": bound,
-                         "achieved": round(gbs, 1), "peak": round(peak, 1), "unit": "GB/s", "frac": round(gbs / peak, 4)}
+                         "achieved": round(gbs, 1), "peak": round(peak, 1), "unit": "GB/s", "frac": round(gbs / peak, 4),
+                         "traffic": (NCU_TRAFFIC_CFG2.get(n) if args.workload == "cfg2-layer" and world == 1 else None)}
     dominant = max(names, key=lambda n: stage_us[n])
     roof = dict(per_kernel[dominant])
-    roof.update({"kernel": dominant, "traffic": None,
+    roof.update({"kernel": dominant,
                  "peak_source": ("MEASURED_PEAKS.json hbm_gbs" if peak_kind == "measured" else "fallback 6650 GB/s")
                  if dominant != "miss_gather" else "pinned host->device cudaMemcpy measured in this run"})
     hbm_kernel = max((n for n in names if n != "miss_gather"), key=lambda n: stage_us[n])
