@@ -177,9 +177,10 @@ int lrqk_flash_decode(const lrqk_layer *L, const void *q, void *out, int32_t row
  * The scratch is an array compiled into the library (lrqk_flash_decode_static_capacity_bytes(),
  * 4 MiB, resident on every GPU that loads the library until the process exits).  This entry and
  * everything it calls allocate nothing.
- *   - Limit: B*Hq heads times the split count chosen for `rows` must fit the array (about 240
- *     heads at head_dim 128); larger shapes return LRQK_ECAPACITY and lrqk_last_cuda_error()
- *     says how many bytes were needed.
+ *   - Limit: B*Hq heads times the split count chosen for `rows` (one split per 32 KiB of keys)
+ *     times 520 bytes must fit the array: 470 heads at 2112 bf16 rows of head_dim 128, 240 heads at
+ *     4224 rows; larger shapes return LRQK_ECAPACITY and lrqk_last_cuda_error() says how many
+ *     bytes were needed.
  *   - The first call on a device looks up the array's device address (once per device, with that
  *     device current); make that first call outside any stream capture.
  *   - All calls share the one array and it keeps the previous call's contents; the entry clears
