@@ -24,7 +24,18 @@ from .hf_models import (  # noqa: F401,E402
     patch_model,
 )
 
+from .extras import (  # noqa: F401,E402
+    FullOffloadCache,
+    HitRateCounter,
+    LightAttentionIndicesOffloadPrefill,
+    WrapForwardTimer,
+    run_task,
+    tps_estimate,
+)
+
 __all__ = [
+    "FullOffloadCache", "HitRateCounter", "LightAttentionIndicesOffloadPrefill", "WrapForwardTimer", "run_task",
+    "tps_estimate",
     "load_lrqk_model", "load_model", "load_model_hack", "load_tokenizer", "lrqk_attention_forward", "patch_model",
     "AutoIncreaseTensor", "AutoIncreaseTensorSharedKV", "DynamicLRQKCache", "InitAQAK",
     "LightAttentionIndicesFactory", "LightAttentionIndicesNoHitMiss", "PreAllocatedTensor", "repeat_kv",
