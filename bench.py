@@ -208,6 +208,8 @@ def run_ours(args):
     assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    from lrqk_b200 import sharding as _sharding
+    numa_cpus = _sharding.bind_host_to_gpu_numa(local_rank)   # the host K|V store is allocated after this
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
@@ -349,6 +351,7 @@ def run_ours(args):
         "data": "synthetic",
         "config": {"workload": args.workload, **{k2: (list(v2) if isinstance(v2, tuple) else v2) for k2, v2 in w.items()},
                    "layers_cycled": layers, "query_rho": args.rho, "sharding": f"kv-heads/{world}",
+                   "host_numa": ("process bound to %d CPUs next to the GPU" % len(numa_cpus)) if numa_cpus else "topology not visible, unbound",
                    "exchange": ("none" if world == 1 else
                                 "attention epilogue pushes rows to every rank over NVLink (peer stores + arrival words)"
                                 if exchange is not None else "nccl all_gather_into_tensor"),

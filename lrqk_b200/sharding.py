@@ -26,6 +26,53 @@ import torch
 from . import _lib
 
 
+def _parse_cpulist(text: str) -> List[int]:
+    cpus: List[int] = []
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        cpus.extend(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+def gpu_numa_cpus(device_index: int, sysfs: str = "/sys") -> Optional[List[int]]:
+    """CPUs of the NUMA node the GPU's PCIe slot hangs off, from sysfs; None when it cannot be told
+    (no sysfs entry, node -1 on single-node machines)."""
+    import os
+    try:
+        props = torch.cuda.get_device_properties(device_index)
+        bus = "%04x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+        with open(os.path.join(sysfs, "bus/pci/devices", bus, "numa_node")) as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open(os.path.join(sysfs, "devices/system/node", f"node{node}", "cpulist")) as f:
+            cpus = _parse_cpulist(f.read())
+        return cpus or None
+    except Exception:
+        return None
+
+
+def bind_host_to_gpu_numa(device_index: int) -> Optional[List[int]]:
+    """Restrict this process to the CPUs next to the GPU, so that the page-locked K|V store it
+    allocates afterwards (first touch) lands in the memory the GPU's host link reaches without
+    crossing sockets -- the rows of every miss travel that path.  Returns the CPUs used, or None if
+    the topology is not visible (nothing is changed then).  Call it before the first allocation."""
+    import os
+    cpus = gpu_numa_cpus(device_index)
+    if not cpus:
+        return None
+    try:
+        allowed = sorted(set(cpus) & set(os.sched_getaffinity(0)))
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return allowed
+    except Exception:
+        return None
+
+
 @dataclass(frozen=True)
 class Shard:
     """The units [unit_begin, unit_end) of the row-major (batch, KV head) grid owned by a rank."""

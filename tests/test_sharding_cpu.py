@@ -88,3 +88,10 @@ def test_two_ranks_over_gloo_assemble_the_unsharded_result(tmp_path):
     mp.spawn(_rank_main, args=(world, port, str(tmp_path)), nprocs=world, join=True)
     for r in range(world):
         assert (tmp_path / f"rank{r}.txt").read_text() == "ok"
+
+
+def test_cpulist_parsing_and_missing_topology(tmp_path):
+    assert sharding._parse_cpulist("0-3,8,10-11\n") == [0, 1, 2, 3, 8, 10, 11]
+    assert sharding._parse_cpulist("") == []
+    # no CUDA device / no sysfs entry: the helpers report "unknown" and change nothing
+    assert sharding.gpu_numa_cpus(0, sysfs=str(tmp_path)) is None
