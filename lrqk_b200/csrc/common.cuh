@@ -82,6 +82,48 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
+// ---- programmatic dependent launch -------------------------------------------------------------
+// The kernels of a decode step depend on one another in stream order.  Each is launched with the
+// programmatic-stream-serialization attribute, calls pdl_launch_dependents() first thing and
+// pdl_wait() before it touches global memory: the next kernel's CTAs are then placed, and run
+// their set-up (shared-memory clears, barrier initialisation), while the previous kernel is still
+// finishing, and block in pdl_wait() until that kernel has completed and its writes are visible.
+// Launched without the attribute both calls do nothing, so the same kernels serve the
+// stage-by-stage entry points.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// cudaLaunchKernelEx with the programmatic attribute and, if cluster_x > 1, a cluster dimension.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    int cluster_x, Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[n].val.programmaticStreamSerializationAllowed = 1;
+  ++n;
+  if (cluster_x > 0) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = (unsigned)cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// lrqk_score_topk with one extra duty for the fused step: *clear_word = 0 (the miss-list length the
+// next kernel appends to), which saves a memset node between two dependent kernels.
+int score_topk_enqueue(const lrqk_layer *L, const void *q_hat, int64_t candidates, int32_t *wanted, float *scores_out,
+                       int64_t scores_stride, int32_t *clear_word, cudaStream_t stream);
+
 // Dispatch on the element type of a layer.
 #define LRQK_DISPATCH_DTYPE(dtype, T, ...)                       \
   do {                                                           \

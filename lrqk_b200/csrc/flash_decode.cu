@@ -82,11 +82,13 @@ __global__ void __launch_bounds__(kAThreads, 4) flash_decode_kernel(AttnParams p
   const char *Kg = reinterpret_cast<const char *>(p.K_res) + ((int64_t)n * p.slots) * ROW_BYTES;
   const char *Vg = reinterpret_cast<const char *>(p.V_res) + ((int64_t)n * p.slots) * ROW_BYTES + lir * 16;
 
+  pdl_launch_dependents();
   if (tid == 0) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(bar)));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  pdl_wait();  // the rows this kernel reads are written by the kernels before it
 
   float m_run = -INFINITY, l_run = 0.0f;
   float2 acc[EPV / 2], qf[EPV / 2];  // pairs of neighbouring dimensions: two fused multiply-adds per instruction
@@ -319,7 +321,7 @@ int launch_flash_decode(const lrqk_layer *L, const void *q, void *out, int32_t r
       LRQK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem)); \
       attr_set = true;                                                                                      \
     }                                                                                                       \
-    kern<<<grid, kAThreads, kAttnSmem, s>>>(p);                                                             \
+    LRQK_CUDA_TRY(launch_dependent(kern, grid, dim3(kAThreads), kAttnSmem, s, 0, p));                       \
   } while (0)
   if (L->head_dim == 128) {
     LRQK_DISPATCH_DTYPE(L->dtype, T, LRQK_ATTN_LAUNCH(T, 128));
@@ -329,7 +331,6 @@ int launch_flash_decode(const lrqk_layer *L, const void *q, void *out, int32_t r
     return LRQK_EUNSUPPORTED;
   }
 #undef LRQK_ATTN_LAUNCH
-  LRQK_LAUNCH_CHECK();
   return LRQK_OK;
 }
 

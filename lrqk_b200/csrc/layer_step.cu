@@ -15,9 +15,8 @@ extern "C" int lrqk_layer_step(const lrqk_layer *L, const lrqk_step_args *a, lrq
   rc = lrqk_decode_project_update(L, a->q, a->k_new, a->max_iter, a->tol, a->position, a->q_hat, a->counters + 2,
                                   a->project_workspace, stream);
   if (rc != LRQK_OK) return rc;
-  rc = lrqk_score_topk(L, a->q_hat, a->candidates, a->wanted, nullptr, 0, stream);
+  rc = score_topk_enqueue(L, a->q_hat, a->candidates, a->wanted, nullptr, 0, a->counters, as_stream(stream));
   if (rc != LRQK_OK) return rc;
-  LRQK_CUDA_TRY(cudaMemsetAsync(a->counters, 0, sizeof(int32_t), as_stream(stream)));
   rc = lrqk_slot_diff(L, a->wanted, a->mask, a->miss_count, a->miss_list, a->counters, a->counters + 1, stream);
   if (rc != LRQK_OK) return rc;
   rc = lrqk_miss_gather(L, a->miss_list, a->counters, stream);

@@ -17,6 +17,8 @@ struct LiteParams {
 
 __global__ void __launch_bounds__(128) lite_append_kernel(LiteParams p) {
   // one CTA per (batch, kv head)
+  pdl_launch_dependents();
+  pdl_wait();
   const int g = blockIdx.x;  // b * kv_heads + kvh
   const int kv_heads = p.q_heads / p.groups;
   const int b = g / kv_heads, kvh = g % kv_heads;
@@ -77,7 +79,6 @@ extern "C" int lrqk_lite_append(const lrqk_layer *L, const void *k_new, const vo
   p.lite_slot = lite_slot;
   p.position = position;
   p.flush_rows = flush_rows;
-  lite_append_kernel<<<L->bsz * L->kv_heads, 128, 0, as_stream(stream)>>>(p);
-  LRQK_LAUNCH_CHECK();
+  LRQK_CUDA_TRY(launch_dependent(lite_append_kernel, dim3(L->bsz * L->kv_heads), dim3(128), 0, as_stream(stream), 0, p));
   return LRQK_OK;
 }

@@ -42,6 +42,8 @@ struct GatherParams {
 };
 
 __global__ void __launch_bounds__(kGThreads) miss_gather_kernel(GatherParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int warp_global = (blockIdx.x * kGThreads + threadIdx.x) >> 5;
   const int n_warps = (gridDim.x * kGThreads) >> 5;
@@ -242,8 +244,7 @@ extern "C" int lrqk_miss_gather(const lrqk_layer *L, const lrqk_miss *list, cons
   // the list length is only known on the device: size the grid for the worst case (every slot missed)
   const int64_t worst = (int64_t)L->bsz * L->q_heads * L->k;
   const int grid = grid_for_rows(worst, kRowsInFlight);
-  miss_gather_kernel<<<grid, kGThreads, 0, as_stream(stream)>>>(p);
-  LRQK_LAUNCH_CHECK();
+  LRQK_CUDA_TRY(launch_dependent(miss_gather_kernel, dim3(grid), dim3(kGThreads), 0, as_stream(stream), 0, p));
   return LRQK_OK;
 }
 

@@ -22,6 +22,8 @@ struct WaitParams {
 
 __global__ void __launch_bounds__(256) allgather_wait_kernel(WaitParams p) {
   __shared__ int ok;
+  pdl_launch_dependents();
+  pdl_wait();
   if (threadIdx.x == 0) ok = 1;
   __syncthreads();
   if ((int)threadIdx.x < p.world) {
@@ -130,7 +132,6 @@ extern "C" int lrqk_allgather_wait(const lrqk_peer_group *g, int32_t seq, void *
   p.seq = seq;
   p.vecs = (int32_t)(half / 16);
   p.polls = g_peer_wait_polls;
-  allgather_wait_kernel<<<1, 256, 0, as_stream(stream)>>>(p);
-  LRQK_LAUNCH_CHECK();
+  LRQK_CUDA_TRY(launch_dependent(allgather_wait_kernel, dim3(1), dim3(256), 0, as_stream(stream), 0, p));
   return LRQK_OK;
 }

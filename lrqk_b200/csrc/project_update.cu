@@ -246,6 +246,8 @@ __global__ void __launch_bounds__(kPThreads, 2) project_kernel(ProjectParams p) 
   float *qrhs = vec, *kbk = vec + R, *khat = vec + 2 * R, *qhat = vec + 3 * R, *knew = vec + 4 * R;
   float *rhs = vec + 5 * R, *tmpv = vec + 6 * R;
 
+  pdl_launch_dependents();
+  pdl_wait();
   const T *qg = reinterpret_cast<const T *>(p.q) + (int64_t)n * D;
   const T *kg = reinterpret_cast<const T *>(p.k_new) + ((int64_t)b_idx * kv_heads + kvh) * D;
   for (int e = tid; e < D; e += kPThreads) {
@@ -434,6 +436,8 @@ __global__ void __launch_bounds__(D) update_kernel(UpdateParams p) {
   __shared__ float hat[2][R];
   __shared__ float red[2][4][D / 32];
   __shared__ int chosen;
+  pdl_launch_dependents();
+  pdl_wait();
 
   // common stopping iteration: mean over all heads of the squared change of k_hat
   for (int it = warp; it < p.max_iter && it < 8; it += D / 32) {
@@ -532,20 +536,8 @@ int launch(const lrqk_layer *L, ProjectParams pp, const UpdateParams &up, cudaSt
     LRQK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     smem_set = smem;
   }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(csize, n_heads, 1);
-  cfg.blockDim = dim3(kPThreads, 1, 1);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = csize;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  LRQK_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, pp));
-  update_kernel<T, R, D><<<n_heads, D, 0, stream>>>(up);
+  LRQK_CUDA_TRY(launch_dependent(kern, dim3(csize, n_heads, 1), dim3(kPThreads), smem, stream, csize, pp));
+  LRQK_CUDA_TRY(launch_dependent(update_kernel<T, R, D>, dim3(n_heads), dim3(D), 0, stream, 0, up));
   LRQK_LAUNCH_CHECK();
   return LRQK_OK;
 }

@@ -9,8 +9,9 @@
 // per pass each CTA reads its peers' histograms through distributed shared memory, so that it
 // knows both the cluster totals (which digit holds the k-th key) and how many of the larger
 // keys sit in lower-ranked CTAs (where its own output starts).  No further exchange is needed:
-// the selected positions are written in ascending order by an ordered compaction in which every
-// thread owns a contiguous run of keys.  Of equal scores the lower position wins.
+// every thread owns a contiguous run of keys, walks it once after the first pass (two bit masks:
+// "above the digit", "equal to it"), and the later passes and the ordered, ascending compaction
+// only revisit the marked keys.  Of equal scores the lower position wins.
 //
 // Summation order of a score (fixed, so results are reproducible): the r columns are split
 // over `lanes = max(1, row_bytes / 64)` lanes; each lane sums the even and the odd columns of its
@@ -29,7 +30,7 @@ namespace {
 constexpr int kThreads = 1024;
 constexpr int kWarps = kThreads / 32;
 constexpr int kBins = 2048;          // 11-bit digits for passes 0 and 1, 10 bits for pass 2
-constexpr int kGranule = 4096;       // segment lengths are multiples of this many rows
+constexpr int kGranule = 4096;       // segment lengths are multiples of this many rows (4 per thread)
 
 template <int VB> struct Vec;
 template <> struct Vec<32> {
@@ -99,6 +100,7 @@ struct ScoreTopkParams {
   int32_t *wanted;      // [N, k]
   float *scores_out;    // optional [N, scores_stride]
   int64_t scores_stride;
+  int32_t *clear_word;  // optional: set to zero by the kernel
 };
 
 // Inclusive block scan of NV 32-bit values per thread at once (kThreads threads).  The values are
@@ -178,8 +180,11 @@ __global__ void __launch_bounds__(kThreads, 1) score_topk_kernel(ScoreTopkParams
   uint32_t *bcast = scratch + 2 * (kWarps + 1);  // [6]
   float *qs = reinterpret_cast<float *>(bcast + 6);  // [R] q_hat in fp32 (8-byte aligned: the counts before it are even)
 
+  pdl_launch_dependents();
   for (int i = tid; i < 3 * kBins; i += kThreads) hist[i] = 0;
   __syncthreads();
+  pdl_wait();  // everything above touched shared memory only
+  if (p.clear_word && n == 0 && rank == 0 && tid == 0) *p.clear_word = 0;
   const int V = p.seg_len / (4 * kThreads);  // 16-byte key vectors per thread
   const uint32_t magic = p.seg_magic;
 
@@ -255,22 +260,45 @@ __global__ void __launch_bounds__(kThreads, 1) score_topk_kernel(ScoreTopkParams
   uint32_t need = (uint32_t)p.k;
   uint32_t out_base = 0;  // selected keys held by lower-ranked CTAs
   uint32_t quota = 0;     // how many keys equal to the threshold this CTA contributes
+  unsigned long long sel = 0ull, und = 0ull;  // this thread's keys: surely selected / still undecided (bit = position in its run)
 #pragma unroll 1
   for (int pass = 0; pass < 3; ++pass) {
-    const int shift = pass == 0 ? 21 : (pass == 1 ? 10 : 0);
     const int bits = pass == 2 ? 10 : 11;
     const uint32_t dmask = (1u << bits) - 1;
     uint32_t *hl = hist + pass * kBins;
-    if (pass > 0) {
-      // histogram of the next digit among the keys that match the prefix so far; four keys per load
+    if (pass == 1) {
+      // The only pass over all keys after the stream: every thread sorts the keys of its own run
+      // into "above the chosen digit" (sel) and "equal to it" (und: undecided), one bit per key,
+      // and histograms the next digit of the undecided ones.  Later passes only walk those bits.
       const uint4 *k4 = reinterpret_cast<const uint4 *>(keys);
-      const int pshift = shift + bits;
-      for (int i = tid; i < (p.seg_len >> 2); i += kThreads) {
-        const uint4 v = k4[i];
-        if ((v.x >> pshift) == prefix) atomicAdd(&hl[(v.x >> shift) & dmask], 1u);
-        if ((v.y >> pshift) == prefix) atomicAdd(&hl[(v.y >> shift) & dmask], 1u);
-        if ((v.z >> pshift) == prefix) atomicAdd(&hl[(v.z >> shift) & dmask], 1u);
-        if ((v.w >> pshift) == prefix) atomicAdd(&hl[(v.w >> shift) & dmask], 1u);
+      for (int j = 0; j < V; ++j) {
+        const uint4 v = k4[j * kThreads + tid];
+        const uint32_t kk[4] = {v.x, v.y, v.z, v.w};
+        uint32_t above = 0u, equal = 0u;  // one bit per key of this group of four
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const uint32_t top = kk[c] >> 21;
+          above |= (uint32_t)(top > prefix) << c;
+          if (top == prefix) {
+            equal |= 1u << c;
+            atomicAdd(&hl[(kk[c] >> 10) & dmask], 1u);
+          }
+        }
+        sel |= (unsigned long long)above << (4 * j);
+        und |= (unsigned long long)equal << (4 * j);
+      }
+      __syncthreads();
+    } else if (pass == 2) {
+      unsigned long long m = und;
+      while (m) {
+        const int i = __ffsll((long long)m) - 1;
+        m &= m - 1;
+        const uint32_t key = keys[(((i >> 2) * kThreads + tid) << 2) | (i & 3)];
+        const uint32_t digit = (key >> 10) & 0x7FFu;
+        const uint32_t chosen = prefix & 0x7FFu;  // the digit pass 1 settled on
+        if (digit != chosen) und &= ~(1ull << i);
+        if (digit > chosen) sel |= 1ull << i;
+        if (digit == chosen) atomicAdd(&hl[key & dmask], 1u);
       }
       __syncthreads();
     }
@@ -317,42 +345,39 @@ __global__ void __launch_bounds__(kThreads, 1) score_topk_kernel(ScoreTopkParams
   const uint32_t T_key = prefix;  // the k-th largest key
 
   // ---- ordered compaction: every thread owns 4*V consecutive rows -----------------------------
-  // Selected keys are rare, so a group of four keys is looked at closely only if its largest
-  // reaches the threshold.  Counts travel as one word: keys above the threshold in the low half,
-  // equal keys in the high half.
-  const uint4 *k4 = reinterpret_cast<const uint4 *>(keys);
-  uint32_t cnt[1] = {0u};
-  for (int j = 0; j < V; ++j) {
-    const uint4 v = k4[j * kThreads + tid];
-    if (max(max(v.x, v.y), max(v.z, v.w)) >= T_key) {
-      cnt[0] += (uint32_t)(v.x > T_key) + (uint32_t)(v.y > T_key) + (uint32_t)(v.z > T_key) + (uint32_t)(v.w > T_key) +
-                (((uint32_t)(v.x == T_key) + (uint32_t)(v.y == T_key) + (uint32_t)(v.z == T_key) +
-                  (uint32_t)(v.w == T_key)) << 16);
+  // The undecided keys (a handful per cluster by now) are settled against the threshold; the
+  // selected keys of a thread are then the set bits of two masks.  Counts travel as one word:
+  // keys above the threshold in the low half, equal keys in the high half.
+  unsigned long long tie = 0ull;
+  {
+    unsigned long long m = und;
+    while (m) {
+      const int i = __ffsll((long long)m) - 1;
+      m &= m - 1;
+      const uint32_t key = keys[(((i >> 2) * kThreads + tid) << 2) | (i & 3)];
+      if (key > T_key) sel |= 1ull << i;
+      if (key == T_key) tie |= 1ull << i;
     }
   }
-  const uint32_t own = cnt[0];
-  uint32_t cta_total[1];
+  const uint32_t own = (uint32_t)__popcll(sel) | ((uint32_t)__popcll(tie) << 16);
+  uint32_t cnt[1] = {own}, cta_total[1];
   block_inclusive_scan<1>(cnt, scratch, cta_total);
   if (own != 0u) {
     const uint32_t at = cnt[0] - own;
     uint32_t g_at = at & 0xFFFFu, e_at = at >> 16;
     int32_t *out = p.wanted + (int64_t)n * p.k;
     const int32_t first = (int32_t)seg_begin + tid * 4 * V;
-    for (int j = 0; j < V; ++j) {
-      const uint4 v = k4[j * kThreads + tid];
-      if (max(max(v.x, v.y), max(v.z, v.w)) >= T_key) {
-        const uint32_t kk[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const bool is_g = kk[t] > T_key, is_e = kk[t] == T_key;
-          if (is_g || (is_e && e_at < quota)) {
-            const uint32_t pos = out_base + g_at + (e_at < quota ? e_at : quota);
-            if (pos < (uint32_t)p.k) out[pos] = first + 4 * j + t;
-          }
-          g_at += is_g;
-          e_at += is_e;
-        }
+    unsigned long long m = sel | tie;
+    while (m) {  // ascending bit = ascending position
+      const int i = __ffsll((long long)m) - 1;
+      m &= m - 1;
+      const bool is_e = (tie >> i) & 1ull;
+      if (!is_e || e_at < quota) {
+        const uint32_t pos = out_base + g_at + (e_at < quota ? e_at : quota);
+        if (pos < (uint32_t)p.k) out[pos] = first + i;
       }
+      g_at += is_e ? 0u : 1u;
+      e_at += is_e ? 1u : 0u;
     }
   }
   cluster.barrier_wait();  // peers may still be reading this CTA's histograms
@@ -372,19 +397,7 @@ int launch_score_topk(const ScoreTopkParams &p, int n_heads, int csize, cudaStre
     LRQK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
     nonportable_set = true;
   }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(csize, n_heads, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = csize;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  LRQK_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p));
+  LRQK_CUDA_TRY(launch_dependent(kern, dim3(csize, n_heads, 1), dim3(kThreads), smem, stream, csize, p));
   return LRQK_OK;
 }
 
@@ -429,7 +442,12 @@ int plan_score_topk(int64_t candidates, int n_heads, int *csize_out, int *seg_le
 
 extern "C" int lrqk_score_topk(const lrqk_layer *L, const void *q_hat, int64_t candidates, int32_t *wanted,
                                float *scores_out, int64_t scores_stride, lrqk_stream_t stream) {
-  using namespace lrqk;
+  return lrqk::score_topk_enqueue(L, q_hat, candidates, wanted, scores_out, scores_stride, nullptr,
+                                  lrqk::as_stream(stream));
+}
+
+int lrqk::score_topk_enqueue(const lrqk_layer *L, const void *q_hat, int64_t candidates, int32_t *wanted,
+                             float *scores_out, int64_t scores_stride, int32_t *clear_word, cudaStream_t stream) {
   int rc = check_device();
   if (rc != LRQK_OK) return rc;
   rc = check_layer(L);
@@ -449,6 +467,7 @@ extern "C" int lrqk_score_topk(const lrqk_layer *L, const void *q_hat, int64_t c
   p.wanted = wanted;
   p.scores_out = scores_out;
   p.scores_stride = scores_stride;
+  p.clear_word = clear_word;
   int csize = 1, seg_len = 0;
   rc = plan_score_topk(candidates, n_heads, &csize, &seg_len);
   if (rc != LRQK_OK) return rc;
@@ -457,6 +476,6 @@ extern "C" int lrqk_score_topk(const lrqk_layer *L, const void *q_hat, int64_t c
     const uint32_t v = (uint32_t)(seg_len / kGranule);
     p.seg_magic = (uint32_t)((0x100000000ull + v - 1) / v);
   }
-  LRQK_DISPATCH_DTYPE(L->dtype, T, return dispatch_rank<T>(L->r, p, n_heads, csize, as_stream(stream)));
+  LRQK_DISPATCH_DTYPE(L->dtype, T, return dispatch_rank<T>(L->r, p, n_heads, csize, stream));
   return LRQK_EUNSUPPORTED;
 }

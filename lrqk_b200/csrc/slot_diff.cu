@@ -47,6 +47,8 @@ __global__ void __launch_bounds__(kDThreads) slot_diff_kernel(int32_t *table, co
   __shared__ int32_t list_base;
 
   const int n = blockIdx.x, tid = threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   int32_t *tab = table + (int64_t)n * k;
   const int32_t *wg = wanted + (int64_t)n * k;
   for (int i = tid; i < k; i += kDThreads) { w[i] = wg[i]; resident[i] = 0; }
@@ -119,8 +121,7 @@ extern "C" int lrqk_slot_diff(const lrqk_layer *L, const int32_t *wanted, uint8_
     LRQK_CUDA_TRY(cudaFuncSetAttribute(slot_diff_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     smem_set = smem;
   }
-  slot_diff_kernel<<<L->bsz * L->q_heads, kDThreads, smem, as_stream(stream)>>>(L->table, wanted, mask, miss_count,
-                                                                              list, list_len, status, L->k);
-  LRQK_LAUNCH_CHECK();
+  LRQK_CUDA_TRY(launch_dependent(slot_diff_kernel, dim3(L->bsz * L->q_heads), dim3(kDThreads), smem, as_stream(stream), 0,
+                                 L->table, wanted, mask, miss_count, list, list_len, status, (int)L->k));
   return LRQK_OK;
 }
