@@ -22,7 +22,9 @@ import sys
 import sysconfig
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-DEFAULT_REFERENCE = os.environ.get("LRQK_REFERENCE_DIR", "/root/reference")
+# a checkout of the reference project: LRQK_REFERENCE_DIR, else a directory "reference" beside this repository
+DEFAULT_REFERENCE = os.environ.get("LRQK_REFERENCE_DIR",
+                                   os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 
 
 def build_c_oracle(verbose: bool = False) -> str:

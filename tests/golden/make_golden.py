@@ -136,7 +136,9 @@ def run_case(ref, name: str, c: dict) -> dict:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("LRQK_REFERENCE_DIR", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get(
+        "LRQK_REFERENCE_DIR", os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference")),
+        help="checkout of the reference project (default: a directory \"reference\" beside this repository)")
     ap.add_argument("--cases", nargs="*", default=list(CASES))
     a = ap.parse_args()
     ref = import_reference(a.reference)
