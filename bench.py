@@ -237,7 +237,7 @@ def run_ours(args):
             exchange.wait()
         else:
             out = fac.decode_attend(q, k, v)
-            if world > 1:
+            if world > 1 and args.collective == "nccl":
                 dist.all_gather_into_tensor(gathered, out.squeeze(2))
         return out
 
@@ -260,8 +260,10 @@ def run_ours(args):
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
+    t_host = time.perf_counter()
     for _ in range(args.steps):
         token(tcur); tcur += 1
+    host_issue_us = (time.perf_counter() - t_host) * 1e6 / (args.steps * layers)   # host time to enqueue one layer-step
     e1.record()
     barrier()
     ms_dev = e0.elapsed_time(e1)
@@ -354,13 +356,15 @@ def run_ours(args):
                    "host_numa": ("process bound to %d CPUs next to the GPU" % len(numa_cpus)) if numa_cpus else "topology not visible, unbound",
                    "exchange": ("none" if world == 1 else
                                 "attention epilogue pushes rows to every rank over NVLink (peer stores + arrival words)"
-                                if exchange is not None else "nccl all_gather_into_tensor"),
+                                if exchange is not None else
+                                "nccl all_gather_into_tensor" if args.collective == "nccl" else "skipped (diagnostic run)"),
                    "l2": "inputs larger than L2: each layer's A_K is %.0f MB and %d layer states are cycled"
                          % (w["bsz"] * hq_l * w["seq"] * w["r"] * 2 / 1e6, layers)},
         "tokens_per_s_8b_equiv": round(1e6 / (us_per_layer * 32), 2),
         "miss_rate": round(miss_rate, 4), "setup_s": round(setup_s, 1), "prefill_ms_per_layer": round(prefill_ms, 2),
         "e2e": {"value": round(us_per_layer_e2e, 2), "unit": "us/layer/step", "h2d_bytes_per_step": int(h2d),
                 "d2h_bytes_per_step": int(d2h)},
+        "host_issue_us_per_layer_step": round(host_issue_us, 1),
         "gpu_launches": int(args.steps * layers * (7 + (1 if exchange is not None else 0))),
         "roofline": roof, "roofline_hbm": roof_hbm, "kernels": per_kernel,
         "host_link_peak_gbs": round(link_peak, 1), "clocks": clocks,
@@ -480,7 +484,7 @@ def main():
     ap.add_argument("--rho", type=float, default=0.0)
     ap.add_argument("--seed", type=int, default=2024)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--collective", default="push", choices=["push", "nccl"],
+    ap.add_argument("--collective", default="push", choices=["push", "nccl", "none"],
                     help="N > 1: how the attention rows of all heads reach every rank")
     args = ap.parse_args()
     if args.warmup < 3:

@@ -352,24 +352,30 @@ def test_layer_step_replay_against_oracle_and_golden(name):
     st.close()
 
 
-def test_layer_step_free_running_bf16():
+@pytest.mark.parametrize("c", [
+    dict(seed=3, bsz=2, hq=8, hkv=2, seq=3000, d=128, r=32, k=256, m=8, steps=20, max_iter=2),
+    # head structure, rank and ring length of the Qwen2.5-7B configuration (28/4 heads, r=16, m=32, one alternation)
+    dict(seed=4, bsz=2, hq=14, hkv=2, seq=2500, d=128, r=16, k=128, m=32, steps=36, max_iter=1),
+    # ... and of the Qwen2.5-32B configuration (40/8 heads, r=64, m=128, four alternations)
+    dict(seed=5, bsz=1, hq=10, hkv=2, seq=6000, d=128, r=64, k=512, m=128, steps=10, max_iter=4),
+], ids=["llama-like", "qwen7b-like", "qwen32b-like"])
+def test_layer_step_free_running_bf16(c):
     """bf16, many steps without resynchronising from the oracle.  After each step the oracle
     adopts the device's rounded factors, so both sides start every step from the same bits: the
     projected query must agree within tolerance, and the integer stages -- recomputed by the
     oracle from the device's own q_hat -- must agree exactly."""
     from gpu_util import bookkeeping, squeeze_step, state_from_oracle
-    c = dict(seed=3, bsz=2, hq=8, hkv=2, seq=3000, d=128, r=32, k=256, m=8, steps=20)
     grp = c["hq"] // c["hkv"]
     Q, K, V = orc.make_prompt(c["seed"], c["bsz"], c["hq"], c["hkv"], c["seq"], c["d"], dtype=torch.bfloat16)
-    lay = orc.OracleLayer(c["r"], c["k"], c["m"], grp, (2, 2), (1e-2, 1e-2), capacity=c["seq"] + 64, init="top")
+    lay = orc.OracleLayer(c["r"], c["k"], c["m"], grp, (2, c["max_iter"]), (1e-2, 1e-2), capacity=c["seq"] + 64, init="top")
     lay.prefill(Q, K, V)
-    st = state_from_oracle(lay, c["hkv"])
+    st = state_from_oracle(lay, c["hkv"], max_iter=c["max_iter"])
     total_miss = 0
     for s in range(c["steps"]):
         q, k, v = orc.make_step(c["seed"], s, c["bsz"], c["hq"], c["hkv"], c["d"], dtype=torch.bfloat16)
         bk = bookkeeping(lay)
         dq, dk, dv = squeeze_step(q, k, v)
-        st.layer_step(st.make_step_args(dq, dk, dv, max_iter=2, tol=1e-2, **bk))
+        st.layer_step(st.make_step_args(dq, dk, dv, max_iter=c["max_iter"], tol=1e-2, **bk))
         torch.cuda.synchronize()
         table_before = lay.table.copy()
         lay.decode(q, k, v, want_attention=False)
