@@ -371,8 +371,11 @@ class LightAttentionIndicesFactory:
 
     def _new_state(self, bsz, hq, hkv, d, seq_len, dtype, device) -> LayerState:
         cap = max(self.capacity, int(seq_len * self.scaling_ratio))   # first allocation, :880
-        return LayerState(bsz, hq, hkv, d, self.r, self.attn_topk, self.num_lite_tokens, a_capacity=cap,
-                          host_capacity=cap, dtype=dtype, device=device, max_iter=self.max_iter[1])
+        # the first seq_len rows of the host store are written by the prompt copy: clear only the rest
+        st = LayerState(bsz, hq, hkv, d, self.r, self.attn_topk, self.num_lite_tokens, a_capacity=cap,
+                        host_capacity=cap, dtype=dtype, device=device, max_iter=self.max_iter[1], zero_host=False)
+        st.host.zero_rows_from(seq_len)
+        return st
 
     _side_streams: Dict[torch.device, "torch.cuda.Stream"] = {}
 

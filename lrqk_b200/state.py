@@ -28,35 +28,74 @@ def _stream():
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+# Page-locked buffers released by closed stores, kept for the next store of the same size: pinning
+# half a gigabyte takes a fifth of a second, far longer than the prompt kernels of a layer.
+_HOST_POOL: dict = {}
+_HOST_POOL_BYTES = 0
+HOST_POOL_LIMIT_BYTES = 64 << 30
+
+
+def release_host_pool() -> None:
+    """Give the pooled page-locked buffers back to the system."""
+    global _HOST_POOL_BYTES
+    for bufs in _HOST_POOL.values():
+        for ptr in bufs:
+            _lib.lib().lrqk_host_free(C.c_void_p(ptr))
+    _HOST_POOL.clear()
+    _HOST_POOL_BYTES = 0
+
+
 class HostStore:
     """Page-locked, device-mapped host buffer [B, Hkv, capacity, 2d] holding K|V rows
-    (the reference's pinned AutoIncreaseTensorSharedKV, lrqk_attention.py:959-963, :1088-1094)."""
+    (the reference's pinned AutoIncreaseTensorSharedKV, lrqk_attention.py:959-963, :1088-1094).
 
-    def __init__(self, bsz: int, kv_heads: int, capacity: int, head_dim: int, dtype: torch.dtype):
+    The reference's store is zero-initialised (:888).  ``zero=True`` clears the whole buffer on the
+    host; a caller that is about to overwrite the first rows anyway passes ``zero=False`` and clears
+    only the rest with :meth:`zero_rows_from` (clearing 0.5 GB on one core costs more than every
+    prompt kernel of the layer together)."""
+
+    def __init__(self, bsz: int, kv_heads: int, capacity: int, head_dim: int, dtype: torch.dtype, zero: bool = True):
+        global _HOST_POOL_BYTES
         self.shape = (bsz, kv_heads, capacity, 2 * head_dim)
         self.dtype = dtype
         self.nbytes = int(np.prod(self.shape)) * torch.empty((), dtype=dtype).element_size()
-        hp = C.c_void_p()
-        _lib.check(_lib.lib().lrqk_host_alloc(C.byref(hp), self.nbytes), "lrqk_host_alloc")
-        self.host_ptr = hp.value
+        pooled = _HOST_POOL.get(self.nbytes)
+        if pooled:
+            self.host_ptr = pooled.pop()
+            _HOST_POOL_BYTES -= self.nbytes
+        else:
+            hp = C.c_void_p()
+            _lib.check(_lib.lib().lrqk_host_alloc(C.byref(hp), self.nbytes), "lrqk_host_alloc")
+            self.host_ptr = hp.value
         dp = C.c_void_p()
-        _lib.check(_lib.lib().lrqk_host_device_ptr(hp, C.byref(dp)), "lrqk_host_device_ptr")
+        _lib.check(_lib.lib().lrqk_host_device_ptr(C.c_void_p(self.host_ptr), C.byref(dp)), "lrqk_host_device_ptr")
         self.device_ptr = dp.value
         raw = (C.c_uint8 * self.nbytes).from_address(self.host_ptr)
         self._raw = raw
         self.data = torch.frombuffer(raw, dtype=torch.uint8).view(dtype).view(self.shape)
-        self.data.zero_()  # the reference's store is zero-initialised (:888); cudaHostAlloc memory is not
+        if zero:
+            self.data.zero_()  # cudaHostAlloc memory (and a pooled buffer) is not zero
         self.current_len = 0
+
+    def zero_rows_from(self, row: int) -> None:
+        """Clear rows [row, capacity) of every (batch, KV head) on the host."""
+        if row < self.capacity:
+            self.data[:, :, row:].zero_()
 
     @property
     def capacity(self) -> int:
         return self.shape[2]
 
     def close(self):
+        global _HOST_POOL_BYTES
         if getattr(self, "host_ptr", None):
             self.data = None
             self._raw = None
-            _lib.lib().lrqk_host_free(C.c_void_p(self.host_ptr))
+            if _HOST_POOL_BYTES + self.nbytes <= HOST_POOL_LIMIT_BYTES:
+                _HOST_POOL.setdefault(self.nbytes, []).append(self.host_ptr)
+                _HOST_POOL_BYTES += self.nbytes
+            else:
+                _lib.lib().lrqk_host_free(C.c_void_p(self.host_ptr))
             self.host_ptr = None
 
     def __del__(self):
@@ -69,7 +108,7 @@ class HostStore:
 class LayerState:
     def __init__(self, bsz: int, q_heads: int, kv_heads: int, head_dim: int, r: int, k: int, m: int,
                  a_capacity: int, host_capacity: int, dtype: torch.dtype, device="cuda", max_iter: int = 2,
-                 with_host: bool = True):
+                 with_host: bool = True, zero_host: bool = True):
         if dtype not in _DTYPES:
             raise ValueError(f"unsupported dtype {dtype}: the kernels take float32 or bfloat16")
         if not torch.cuda.is_available():
@@ -87,7 +126,7 @@ class LayerState:
         self.V_res = torch.zeros((bsz, q_heads, k + m, head_dim), **z)
         self.table = torch.zeros((bsz, q_heads, k), dtype=torch.int32, device=self.device)
         self.lite_pos = torch.full((m,), -1, dtype=torch.int32, device=self.device)
-        self.host = HostStore(bsz, kv_heads, host_capacity, head_dim, dtype) if with_host else None
+        self.host = HostStore(bsz, kv_heads, host_capacity, head_dim, dtype, zero=zero_host) if with_host else None
         # per-step outputs and scratch
         self.q_hat = torch.zeros((bsz, q_heads, r), **z)
         self.wanted = torch.zeros((bsz, q_heads, k), dtype=torch.int32, device=self.device)
