@@ -473,6 +473,89 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------------------------------------------------------------
+# whole-model run (optional): a random-init decoder stack of a named architecture through the
+# patched Hugging Face forward -- prompt pass, then greedy decoding through DynamicLRQKCache
+# ------------------------------------------------------------------------------------------------
+MODELS = {
+    # Llama-3-8B architecture, the settings of the 128K configuration
+    "llama3-8b": dict(family="llama", vocab_size=128256, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32,
+                      num_attention_heads=32, num_key_value_heads=8, head_dim=128, rope_theta=500000.0,
+                      r=32, k=2048, m=64, max_iter=(2, 2), batch=1, prompt=131072, decode=256),
+    # Qwen2.5-7B architecture (QKV bias), the settings of the batch-8 64K configuration
+    "qwen2.5-7b": dict(family="qwen", vocab_size=152064, hidden_size=3584, intermediate_size=18944, num_hidden_layers=28,
+                       num_attention_heads=28, num_key_value_heads=4, rope_theta=1e6,
+                       r=16, k=1024, m=32, max_iter=(1, 1), batch=8, prompt=65536, decode=128),
+}
+
+
+def run_model(args):
+    import transformers
+    from lrqk_b200 import DynamicLRQKCache, patch_model
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
+    spec = dict(MODELS[args.model])
+    family = spec.pop("family")
+    r, k, m, max_iter = spec.pop("r"), spec.pop("k"), spec.pop("m"), spec.pop("max_iter")
+    prompt = args.prompt or spec.pop("prompt")
+    spec.pop("prompt", None)
+    n_decode = args.decode or spec.pop("decode")
+    spec.pop("decode", None)
+    batch = args.batch or spec.pop("batch")
+    spec.pop("batch", None)
+    if args.model_layers:
+        spec["num_hidden_layers"] = args.model_layers
+    cfg_cls = transformers.LlamaConfig if family == "llama" else transformers.Qwen2Config
+    cfg = cfg_cls(max_position_embeddings=prompt + n_decode + 64, **spec)
+    cfg._attn_implementation = "sdpa"
+    torch.cuda.set_device(0)
+    torch.manual_seed(args.seed)
+    t0 = time.time()
+    with torch.device("cuda"):
+        model = transformers.AutoModelForCausalLM.from_config(cfg, dtype=torch.bfloat16)
+    model.eval()
+    patch_model(model)
+    build_s = time.time() - t0
+    groups = cfg.num_attention_heads // cfg.num_key_value_heads
+    ids = torch.randint(0, cfg.vocab_size, (batch, prompt), generator=torch.Generator().manual_seed(args.seed)).cuda()
+    cache = DynamicLRQKCache(r=r, num_active_tokens=k, lite_tokens=m, max_iter=max_iter, tol=1e-2,
+                             max_sequence_length=prompt + n_decode + 2 * m + 64, num_key_value_groups=groups)
+    sampler = ClockSampler(0)
+    with torch.no_grad():
+        torch.cuda.synchronize()
+        t1 = time.time()
+        out = model(input_ids=ids, past_key_values=cache, use_cache=True, logits_to_keep=1)
+        torch.cuda.synchronize()
+        prefill_s = time.time() - t1
+        tok = out.logits[:, -1].argmax(-1, keepdim=True)
+        for _ in range(args.warmup):
+            tok = model(input_ids=tok, past_key_values=cache, use_cache=True).logits[:, -1].argmax(-1, keepdim=True)
+        torch.cuda.synchronize()
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n_decode):
+            tok = model(input_ids=tok, past_key_values=cache, use_cache=True).logits[:, -1].argmax(-1, keepdim=True)
+        e1.record()
+        torch.cuda.synchronize()
+        clocks = sampler.stop()
+    ms = e0.elapsed_time(e1)
+    miss = float(torch.stack([f.state.miss_count.float().mean() for f in cache.lwattn.values()]).mean()) / k
+    line = {
+        "metric": "decode_tokens_per_s", "value": round(batch * n_decode / (ms * 1e-3), 2), "unit": "tokens/s", "n_gpus": 1,
+        "steps": n_decode, "warmup": args.warmup, "ms_per_step": round(ms / n_decode, 3), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{args.model} architecture, random init, {cfg.num_hidden_layers} layers, batch {batch}, "
+                               f"{prompt}-token uniform-random prompt, greedy decode", "r": r, "k": k, "m": m,
+                   "max_iter": list(max_iter), "dense_parts": "transformers modules (library GEMMs, SDPA for the prompt pass)"},
+        "us_per_layer_step_including_dense": round(ms * 1e3 / (n_decode * cfg.num_hidden_layers), 1),
+        "prefill_s": round(prefill_s, 2), "prefill_tokens_per_s": round(batch * prompt / prefill_s, 1),
+        "model_build_s": round(build_s, 1), "last_step_miss_rate": round(miss, 4), "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+    for f in cache.lwattn.values():
+        f.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -486,9 +569,17 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--collective", default="push", choices=["push", "nccl", "none"],
                     help="N > 1: how the attention rows of all heads reach every rank")
+    ap.add_argument("--model", default=None, choices=sorted(MODELS),
+                    help="run a whole random-init decoder stack instead of the per-layer workload (1 GPU)")
+    ap.add_argument("--prompt", type=int, default=0, help="--model: prompt length (default: the configuration's)")
+    ap.add_argument("--decode", type=int, default=0, help="--model: tokens to decode (default: the configuration's)")
+    ap.add_argument("--batch", type=int, default=0, help="--model: sequences (default: the configuration's)")
+    ap.add_argument("--model-layers", type=int, default=0, help="--model: fewer decoder layers, for a quick look")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
+    if args.model is not None:
+        return run_model(args)
     if args.impl == "reference":
         run_reference(args)
     else:
