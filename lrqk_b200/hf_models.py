@@ -44,12 +44,16 @@ SUPPORTED_FAMILIES = ("qwen", "llama", "mistral")
 
 
 def _causal_attention(q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, scaling: float,
-                      pad_mask: Optional[torch.Tensor]) -> torch.Tensor:
+                      pad_mask: Optional[torch.Tensor], mask4d: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Exact attention of q [B,Hq,L,d] over K, V [B,Hkv,S,d] (S >= L; the queries are the last L
-    positions), causal, optionally with a [B,S] padding mask (1 = token).  Returns [B,L,Hq,d]."""
+    positions), causal.  ``mask4d`` -- the [B,1,L,S] mask transformers built for this call, boolean
+    or additive -- is used as it is when its shape fits; otherwise the causal pattern is rebuilt
+    here, combined with the [B,S] padding mask (1 = token) if there is one.  Returns [B,L,Hq,d]."""
     L, S = q.shape[2], K.shape[2]
     mask = None
-    if pad_mask is not None or (L > 1 and L != S):
+    if mask4d is not None and mask4d.dim() == 4 and mask4d.shape[-2] == L and mask4d.shape[-1] == S:
+        mask = mask4d if mask4d.dtype == torch.bool else mask4d.to(q.dtype)
+    elif pad_mask is not None or (L > 1 and L != S):
         idx_q = torch.arange(S - L, S, device=q.device)[:, None]
         idx_k = torch.arange(S, device=q.device)[None, :]
         mask = (idx_k <= idx_q)[None, None]                      # [1,1,L,S]
@@ -61,12 +65,17 @@ def _causal_attention(q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, scaling
 
 
 def _padding_mask(attention_mask: Optional[torch.Tensor], seq_len: int) -> Optional[torch.Tensor]:
-    """The [B,S] token mask the reference's cache expects (:1901-1903), when one can be recovered."""
+    """The [B,S] token mask the reference's cache expects (:1901-1903).  transformers 5.x hands the
+    attention modules a [B,1,L,S] mask (or none at all when nothing is padded): its last query row
+    tells which keys are real tokens."""
     if attention_mask is None:
         return None
     if attention_mask.dim() == 2:
-        return attention_mask[:, -seq_len:]
-    return None  # a 4-D causal mask carries no per-token padding information we rely on
+        return attention_mask[:, -seq_len:].to(torch.bool)
+    if attention_mask.dim() == 4 and attention_mask.shape[-1] >= seq_len:
+        row = attention_mask[:, 0, -1, -seq_len:]
+        return row if row.dtype == torch.bool else (row == 0)
+    return None
 
 
 def lrqk_attention_forward(self, hidden_states: torch.Tensor,
@@ -95,8 +104,9 @@ def lrqk_attention_forward(self, hidden_states: torch.Tensor,
     else:
         pad = _padding_mask(attention_mask, key_states.shape[2])
         K, V = cache.update(query_states, key_states.contiguous(), value_states.contiguous(), self.layer_idx,
-                            attention_mask=pad)
-        attn_output = _causal_attention(query_states, K, V, self.scaling, _padding_mask(attention_mask, K.shape[2]))
+                            attention_mask=None if pad is None else pad.to(key_states.dtype))
+        attn_output = _causal_attention(query_states, K, V, self.scaling, _padding_mask(attention_mask, K.shape[2]),
+                                        mask4d=attention_mask)
     attn_output = attn_output.reshape(*input_shape, -1).contiguous()
     return self.o_proj(attn_output), None
 

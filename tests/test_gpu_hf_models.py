@@ -63,6 +63,38 @@ def test_patched_stack_prefills_exactly_and_decodes_through_the_cuda_path(family
         fac.close()
 
 
+def test_generate_and_left_padded_prompts():
+    """``model.generate(..., past_key_values=DynamicLRQKCache(...))`` -- the reference's usage -- and a
+    left-padded batch: the prompt pass honours the mask transformers builds (same logits as the
+    unpatched model on the real tokens) and the padded keys and values are zeroed in the cache,
+    as the reference does (lrqk_attention.py:1901-1903)."""
+    from lrqk_b200 import DynamicLRQKCache, patch_model
+    model = _tiny("llama")
+    S, pad = 300, 7
+    ids = torch.randint(1, 512, (2, S), generator=torch.Generator().manual_seed(2)).cuda()
+    mask = torch.ones_like(ids)
+    mask[1, :pad] = 0                                           # second sequence is left-padded
+    with torch.no_grad():
+        ref = model(input_ids=ids, attention_mask=mask, use_cache=False).logits
+    patch_model(model)
+    mk = lambda: DynamicLRQKCache(r=16, num_active_tokens=256, lite_tokens=16, max_sequence_length=1024,  # noqa: E731
+                                  num_key_value_groups=2, init_aq_ak_method="top")
+    cache = mk()
+    with torch.no_grad():
+        out = model(input_ids=ids, attention_mask=mask, past_key_values=cache, use_cache=True).logits
+    assert torch.allclose(out[0].float(), ref[0].float(), atol=3e-2, rtol=3e-2)
+    assert torch.allclose(out[1, pad:].float(), ref[1, pad:].float(), atol=3e-2, rtol=3e-2)
+    host = cache.lwattn[0].KVcpu.data
+    assert not host[1, :, :pad].any() and host[1, :, pad:S].any() and host[0, :, :pad].any()
+    cache2 = mk()
+    gen = model.generate(input_ids=ids, attention_mask=mask, past_key_values=cache2, max_new_tokens=12, do_sample=False,
+                         pad_token_id=0)
+    assert gen.shape == (2, S + 12) and cache2.get_seq_length() == S + 11
+    for c in (cache, cache2):
+        for fac in c.lwattn.values():
+            fac.close()
+
+
 def test_unknown_family_is_rejected_like_the_reference():
     from lrqk_b200.hf_models import family_of
     with pytest.raises(ValueError):
