@@ -121,8 +121,22 @@ inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 bl
 
 // lrqk_score_topk with one extra duty for the fused step: *clear_word = 0 (the miss-list length the
 // next kernel appends to), which saves a memset node between two dependent kernels.
+// With `diff`, the kernel also runs the hit/miss difference of every head against L->table right
+// after its selection (what lrqk_slot_diff does as a kernel of its own); *diff->list_len must be
+// zero before the kernel starts.
+struct FusedDiff {
+  uint8_t *mask;
+  int32_t *miss_count;
+  lrqk_miss *list;
+  int32_t *list_len, *status;
+};
 int score_topk_enqueue(const lrqk_layer *L, const void *q_hat, int64_t candidates, int32_t *wanted, float *scores_out,
-                       int64_t scores_stride, int32_t *clear_word, cudaStream_t stream);
+                       int64_t scores_stride, int32_t *clear_word, cudaStream_t stream, const FusedDiff *diff = nullptr);
+
+// lrqk_decode_project_update with one extra duty for the fused step: *clear_word = 0 at the end.
+int project_update_enqueue(const lrqk_layer *L, const void *q, const void *k_new, int32_t max_iter, float tol,
+                           int64_t append_row, void *q_hat, int32_t *iters_out, void *workspace, int32_t *clear_word,
+                           cudaStream_t stream);
 
 // Dispatch on the element type of a layer.
 #define LRQK_DISPATCH_DTYPE(dtype, T, ...)                       \

@@ -12,12 +12,15 @@ extern "C" int lrqk_layer_step(const lrqk_layer *L, const lrqk_step_args *a, lrq
   if ((a->attn_out || a->peers) && !a->attn_workspace) return LRQK_EINVAL;
   int rc = lrqk_lite_append(L, a->k_new, a->v_new, a->lite_slot, a->position, a->flush_rows, a->host_row, stream);
   if (rc != LRQK_OK) return rc;
-  rc = lrqk_decode_project_update(L, a->q, a->k_new, a->max_iter, a->tol, a->position, a->q_hat, a->counters + 2,
-                                  a->project_workspace, stream);
+  // the miss-list length is cleared by the projection's second kernel, the hit/miss difference runs
+  // as the tail of the scoring kernel: five launches per step instead of seven plus a memset
+  rc = project_update_enqueue(L, a->q, a->k_new, a->max_iter, a->tol, a->position, a->q_hat, a->counters + 2,
+                              a->project_workspace, a->counters, as_stream(stream));
   if (rc != LRQK_OK) return rc;
-  rc = score_topk_enqueue(L, a->q_hat, a->candidates, a->wanted, nullptr, 0, a->counters, as_stream(stream));
-  if (rc != LRQK_OK) return rc;
-  rc = lrqk_slot_diff(L, a->wanted, a->mask, a->miss_count, a->miss_list, a->counters, a->counters + 1, stream);
+  FusedDiff diff;
+  diff.mask = a->mask; diff.miss_count = a->miss_count; diff.list = a->miss_list;
+  diff.list_len = a->counters; diff.status = a->counters + 1;
+  rc = score_topk_enqueue(L, a->q_hat, a->candidates, a->wanted, nullptr, 0, nullptr, as_stream(stream), &diff);
   if (rc != LRQK_OK) return rc;
   rc = lrqk_miss_gather(L, a->miss_list, a->counters, stream);
   if (rc != LRQK_OK) return rc;

@@ -424,6 +424,7 @@ struct UpdateParams {
   int64_t a_capacity, append_row;
   int32_t q_heads, groups, max_iter, n_heads;
   float tol;
+  int32_t *clear_word;  // optional: set to zero by the kernel
 };
 
 template <typename T, int R, int D>
@@ -454,6 +455,7 @@ __global__ void __launch_bounds__(D) update_kernel(UpdateParams p) {
     }
     chosen = c;
     if (n == 0 && p.iters_out) *p.iters_out = c + 1;
+    if (n == 0 && p.clear_word) *p.clear_word = 0;
   }
   __syncthreads();
   const float *w = p.ws + ((int64_t)n * p.max_iter + chosen) * W;
@@ -565,7 +567,13 @@ extern "C" size_t lrqk_decode_project_update_workspace_bytes(const lrqk_layer *L
 extern "C" int lrqk_decode_project_update(const lrqk_layer *L, const void *q, const void *k_new, int32_t max_iter,
                                           float tol, int64_t append_row, void *q_hat, int32_t *iters_out,
                                           void *workspace, lrqk_stream_t stream) {
-  using namespace lrqk;
+  return lrqk::project_update_enqueue(L, q, k_new, max_iter, tol, append_row, q_hat, iters_out, workspace, nullptr,
+                                      lrqk::as_stream(stream));
+}
+
+int lrqk::project_update_enqueue(const lrqk_layer *L, const void *q, const void *k_new, int32_t max_iter, float tol,
+                                 int64_t append_row, void *q_hat, int32_t *iters_out, void *workspace,
+                                 int32_t *clear_word, cudaStream_t s) {
   int rc = check_device();
   if (rc != LRQK_OK) return rc;
   rc = check_layer(L);
@@ -589,7 +597,7 @@ extern "C" int lrqk_decode_project_update(const lrqk_layer *L, const void *q, co
   up.a_capacity = L->a_capacity; up.append_row = append_row;
   up.q_heads = L->q_heads; up.groups = pp.groups; up.max_iter = max_iter; up.n_heads = pp.n_heads;
   up.tol = tol;
-  cudaStream_t s = as_stream(stream);
+  up.clear_word = clear_word;
   if (L->head_dim == 128) {
     LRQK_DISPATCH_DTYPE(L->dtype, T, return (dispatch_r<T, 128>(L, pp, up, s)));
   } else if (L->head_dim == 64) {

@@ -21,6 +21,7 @@
 #include <cooperative_groups.h>
 
 #include "common.cuh"
+#include "slot_diff.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -101,6 +102,13 @@ struct ScoreTopkParams {
   float *scores_out;    // optional [N, scores_stride]
   int64_t scores_stride;
   int32_t *clear_word;  // optional: set to zero by the kernel
+  // optional fused hit/miss difference (table != nullptr): after the selection, the first CTA of
+  // every cluster runs slot_diff_head for its head
+  int32_t *table;
+  uint8_t *mask;
+  int32_t *miss_count;
+  lrqk_miss *miss_list;
+  int32_t *list_len, *diff_status;
 };
 
 // Inclusive block scan of NV 32-bit values per thread at once (kThreads threads).  The values are
@@ -381,11 +389,22 @@ __global__ void __launch_bounds__(kThreads, 1) score_topk_kernel(ScoreTopkParams
     }
   }
   cluster.barrier_wait();  // peers may still be reading this CTA's histograms
+  if (p.table != nullptr) {
+    // fused hit/miss difference: once every CTA of the cluster has written its part of `wanted`
+    // (release/acquire through the cluster barrier), the first CTA diffs the head's wanted set
+    // against the slot table; the keys' shared memory is free by now
+    __threadfence();
+    cluster.sync();
+    if (rank == 0)
+      slot_diff_head(n, p.table, p.wanted, p.mask, p.miss_count, p.miss_list, p.list_len, p.diff_status, p.k,
+                     reinterpret_cast<unsigned char *>(smem));
+  }
 }
 
 template <typename T, int R>
 int launch_score_topk(const ScoreTopkParams &p, int n_heads, int csize, cudaStream_t stream) {
-  const size_t smem = ((size_t)p.seg_len + 3 * kBins + 2 * (kWarps + 1) + 6 + R) * sizeof(uint32_t);
+  size_t smem = ((size_t)p.seg_len + 3 * kBins + 2 * (kWarps + 1) + 6 + R) * sizeof(uint32_t);
+  if (p.table != nullptr && slot_diff_smem_bytes(p.k) > smem) smem = slot_diff_smem_bytes(p.k);
   auto kern = score_topk_kernel<T, R>;
   static size_t smem_set = 0;
   static bool nonportable_set = false;
@@ -447,7 +466,8 @@ extern "C" int lrqk_score_topk(const lrqk_layer *L, const void *q_hat, int64_t c
 }
 
 int lrqk::score_topk_enqueue(const lrqk_layer *L, const void *q_hat, int64_t candidates, int32_t *wanted,
-                             float *scores_out, int64_t scores_stride, int32_t *clear_word, cudaStream_t stream) {
+                             float *scores_out, int64_t scores_stride, int32_t *clear_word, cudaStream_t stream,
+                             const FusedDiff *diff) {
   int rc = check_device();
   if (rc != LRQK_OK) return rc;
   rc = check_layer(L);
@@ -468,6 +488,13 @@ int lrqk::score_topk_enqueue(const lrqk_layer *L, const void *q_hat, int64_t can
   p.scores_out = scores_out;
   p.scores_stride = scores_stride;
   p.clear_word = clear_word;
+  p.table = nullptr; p.mask = nullptr; p.miss_count = nullptr; p.miss_list = nullptr; p.list_len = nullptr; p.diff_status = nullptr;
+  if (diff) {
+    if (!L->table || !diff->mask || !diff->miss_count || !diff->list || !diff->list_len || !diff->status) return LRQK_EINVAL;
+    if (slot_diff_smem_bytes(L->k) > 200 * 1024) return LRQK_EUNSUPPORTED;
+    p.table = L->table; p.mask = diff->mask; p.miss_count = diff->miss_count; p.miss_list = diff->list;
+    p.list_len = diff->list_len; p.diff_status = diff->status;
+  }
   int csize = 1, seg_len = 0;
   rc = plan_score_topk(candidates, n_heads, &csize, &seg_len);
   if (rc != LRQK_OK) return rc;

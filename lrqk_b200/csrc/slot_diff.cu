@@ -1,106 +1,17 @@
-// Hit/miss difference of the wanted set against the resident slot table.
-//
-// One CTA per (batch, query head).  `wanted` is ascending, so membership of a resident entry
-// is a binary search in shared memory; the search also flags the wanted entry as resident.
-// Two ordered block scans then pair the i-th evicted slot (ascending slot number) with the
-// i-th wanted position that is not resident (ascending).  The table is updated in place, the
-// mask and per-head miss count are written, and the (head, slot, position) triples of the
-// misses are appended to a global list with one atomic reservation per CTA.
-#include "common.cuh"
+// Hit/miss difference of the wanted set against the resident slot table: one CTA per
+// (batch, query head) runs slot_diff_head (slot_diff.cuh).
+#include "slot_diff.cuh"
 
 namespace lrqk {
 namespace {
 
-constexpr int kDThreads = 1024;
-
-__device__ __forceinline__ uint32_t block_scan(uint32_t v, uint32_t *scratch, uint32_t &total) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  uint32_t inc = v;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    uint32_t t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
-    if (lane >= o) inc += t;
-  }
-  if (lane == 31) scratch[warp] = inc;
-  __syncthreads();
-  uint32_t off = 0, tot = 0;
-#pragma unroll
-  for (int w = 0; w < kDThreads / 32; ++w) {
-    const uint32_t s = scratch[w];
-    if (w < warp) off += s;
-    tot += s;
-  }
-  __syncthreads();
-  total = tot;
-  return off + inc - v;
-}
-
 __global__ void __launch_bounds__(kDThreads) slot_diff_kernel(int32_t *table, const int32_t *wanted, uint8_t *mask,
                                                              int32_t *miss_count, lrqk_miss *list, int32_t *list_len,
                                                              int32_t *status, int k) {
-  extern __shared__ __align__(16) int32_t sh[];
-  int32_t *w = sh;                                        // [k] wanted, ascending
-  int32_t *missing = w + k;                               // [k] wanted-but-not-resident, ascending
-  uint8_t *resident = reinterpret_cast<uint8_t *>(missing + k);  // [k] wanted entry already resident
-  uint8_t *evict = resident + k;                          // [k] slot entry no longer wanted
-  __shared__ uint32_t scratch[kDThreads / 32];
-  __shared__ int32_t list_base;
-
-  const int n = blockIdx.x, tid = threadIdx.x;
+  extern __shared__ __align__(16) unsigned char sh[];
   pdl_launch_dependents();
   pdl_wait();
-  int32_t *tab = table + (int64_t)n * k;
-  const int32_t *wg = wanted + (int64_t)n * k;
-  for (int i = tid; i < k; i += kDThreads) { w[i] = wg[i]; resident[i] = 0; }
-  __syncthreads();
-  for (int i = tid; i < k; i += kDThreads) {
-    const int32_t v = tab[i];
-    int lo = 0, hi = k;
-    while (lo < hi) {
-      const int mid = (lo + hi) >> 1;
-      if (w[mid] < v) lo = mid + 1; else hi = mid;
-    }
-    const bool hit = lo < k && w[lo] == v;
-    if (hit) resident[lo] = 1;
-    evict[i] = hit ? 0 : 1;
-  }
-  __syncthreads();
-  // ordered compaction of the missing wanted entries; each thread owns a contiguous run
-  const int per = (k + kDThreads - 1) / kDThreads;
-  const int begin = min(k, tid * per), end = min(k, begin + per);
-  uint32_t cnt = 0;
-  for (int i = begin; i < end; ++i) cnt += resident[i] == 0;
-  uint32_t n_missing;
-  uint32_t off = block_scan(cnt, scratch, n_missing);
-  for (int i = begin; i < end; ++i)
-    if (resident[i] == 0) missing[off++] = w[i];
-  // ordered scan over the evicted slots
-  cnt = 0;
-  for (int i = begin; i < end; ++i) cnt += evict[i];
-  uint32_t n_evict;
-  off = block_scan(cnt, scratch, n_evict);  // the barrier inside also publishes missing[]
-  if (tid == 0) {
-    list_base = n_evict ? atomicAdd(list_len, (int32_t)n_evict) : 0;
-    miss_count[n] = (int32_t)n_evict;
-    if (n_evict != n_missing) atomicExch(status, 1);
-  }
-  __syncthreads();
-  const uint32_t usable = n_evict < n_missing ? n_evict : n_missing;
-  for (int i = begin; i < end; ++i) {
-    uint8_t mk = 0;
-    if (evict[i]) {
-      if (off < usable) {
-        const int32_t pos = missing[off];
-        tab[i] = pos;
-        lrqk_miss e;
-        e.head = n; e.slot = i; e.pos = pos;
-        list[list_base + off] = e;
-        mk = 1;
-      }
-      ++off;
-    }
-    mask[(int64_t)n * k + i] = mk;
-  }
+  slot_diff_head(blockIdx.x, table, wanted, mask, miss_count, list, list_len, status, k, sh);
 }
 
 }  // namespace
@@ -114,7 +25,7 @@ extern "C" int lrqk_slot_diff(const lrqk_layer *L, const int32_t *wanted, uint8_
   rc = check_layer(L);
   if (rc != LRQK_OK) return rc;
   if (!wanted || !mask || !miss_count || !list || !list_len || !status || !L->table) return LRQK_EINVAL;
-  const size_t smem = (size_t)L->k * (2 * sizeof(int32_t) + 2);
+  const size_t smem = slot_diff_smem_bytes(L->k);
   if (smem > 200 * 1024) return LRQK_EUNSUPPORTED;
   static size_t smem_set = 48 * 1024;
   if (smem > smem_set) {
