@@ -227,6 +227,7 @@ def test_lite_append_and_flush(dtype):
 @pytest.mark.parametrize("dtype,d,rows,bsz,hq", [
     (torch.bfloat16, 128, 2112, 1, 32), (torch.bfloat16, 128, 272, 2, 8), (torch.float32, 128, 272, 1, 8),
     (torch.bfloat16, 64, 100, 1, 3), (torch.float32, 64, 33, 2, 2), (torch.bfloat16, 128, 5, 1, 2),
+    (torch.bfloat16, 128, 9000, 1, 2), (torch.float32, 128, 5000, 1, 1),   # more rows than 64 splits of one staging round
 ])
 def test_flash_decode_matches_oracle(dtype, d, rows, bsz, hq):
     g = torch.Generator().manual_seed(rows)

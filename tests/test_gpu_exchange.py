@@ -51,6 +51,24 @@ def test_emulated_ranks_push_and_wait(dtype, world, hq, d):
         ex.close()
 
 
+def test_push_without_a_local_output_buffer():
+    """`out` may be NULL: the rows then only exist in the exchange buffers."""
+    from lrqk_b200 import _lib, sharding
+    lib = _lib.lib()
+    group = sharding.HeadExchange.local_group(1, 4, 128, torch.bfloat16)
+    st, q = _mk_state(3, 1, 4, 128, 200, torch.bfloat16)
+    expect = st.flash_decode(q).clone()
+    seq = group[0].seq.next_push()
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    _lib.check(lib.lrqk_flash_decode_push(C.byref(st.c), C.c_void_p(q.data_ptr()), None, st.k + st.m, 128 ** -0.5,
+                                          C.c_void_p(st.attn_ws.data_ptr()), C.byref(group[0].c), seq, stream), "push")
+    got = group[0].wait().clone()
+    torch.cuda.synchronize()
+    group[0].check_status()
+    assert torch.equal(got[0], expect[0])
+    group[0].close()
+
+
 def test_wait_runs_out_and_reports_without_hanging():
     from lrqk_b200 import _lib, sharding
     lib = _lib.lib()

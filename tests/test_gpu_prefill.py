@@ -45,6 +45,8 @@ def _factorize(Q, K, aq, ak, r, sweeps, tol, groups):
     (torch.float32, 16, 1, 4, 2, 2048, 4, 50.0),    # leaves after the second sweep (change < tol)
     (torch.bfloat16, 32, 1, 8, 2, 4096, 2, 1e-9),
     (torch.bfloat16, 64, 1, 2, 1, 3000, 1, 1e-9),
+    (torch.bfloat16, 16, 2, 4, 2, 2500, 2, 1e-9),   # tensor-core Gram pass at r=16, ragged tail tile, batch 2
+    (torch.bfloat16, 8, 1, 2, 2, 1111, 2, 1e-9),    # ... and r=8
     (torch.float32, 32, 1, 2, 1, 1000, 2, 1e-9),
 ])
 def test_prefill_factorize_matches_reference_algorithm(dtype, r, b, hq, hkv, s, sweeps, tol):
