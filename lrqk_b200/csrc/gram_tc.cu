@@ -20,89 +20,20 @@
 // split in the layout the algebra kernel sums.  Stages are recycled through mbarriers; the MMA
 // warp releases a stage with tcgen05.commit.  Every wait is bounded: if one runs out the CTA
 // raises the status word, stops issuing work, and still frees its TMEM.
-#include <cuda.h>
-
 #include "common.cuh"
 #include "gram_tc.cuh"
+#include "tc_common.cuh"
 
 namespace lrqk {
 namespace {
+
+using namespace tc;
 
 constexpr int kTileRows = 64;                       // prompt rows per stage
 constexpr int kGroupBytes = kTileRows * 128;        // one 64-column group of a stage
 template <int R> __host__ __device__ constexpr int stage_count() { return R >= 64 ? 5 : 6; }  // 160 to 200 KiB of stages
 constexpr int kTcThreads = 192;                     // 6 warps
-constexpr uint32_t kTcWaitLimit = 1u << 22;
 constexpr int kTmemCols = 256;
-
-__device__ __forceinline__ uint32_t saddr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ bool wait_bounded(uint64_t *bar, uint32_t parity) {
-  const uint32_t a = saddr(bar);
-  for (uint32_t i = 0; i < kTcWaitLimit; ++i) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done) : "r"(a), "r"(parity) : "memory");
-    if (done) return true;
-  }
-  return false;
-}
-
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(saddr(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(saddr(bar)) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(saddr(bar)), "r"(bytes) : "memory");
-}
-
-// Shared-memory matrix descriptor of an MN-major operand in the 128-byte swizzle: 64-element
-// groups `lbo` bytes apart along M/N, 8-row atoms `sbo` bytes apart along K.
-__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_byte_addr, uint32_t lbo, uint32_t sbo) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_byte_addr >> 4) & 0x3FFF);
-  d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
-  d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
-  d |= (uint64_t)1 << 46;   // descriptor version of this architecture
-  d |= (uint64_t)2 << 61;   // 128-byte swizzle
-  return d;
-}
-
-// Instruction descriptor: bf16 x bf16 -> fp32, both operands MN-major, M x N.
-__host__ __device__ constexpr uint32_t umma_idesc_bf16_mn(int M, int N) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) | ((uint32_t)(N >> 3) << 17) |
-         ((uint32_t)(M >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-
-__device__ __forceinline__ void umma_commit(uint64_t *bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(saddr(bar)) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
 
 struct GramTcParams {
   const float *A_Q0, *A_K0;   // [N][S][R] fp32
@@ -280,38 +211,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) gram_tc_kernel(const __grid_con
   }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void *sym = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess ||
-        qres != cudaDriverEntryPointSuccess)
-      return nullptr;
-    fn = reinterpret_cast<EncodeTiledFn>(sym);
-  }
-  return fn;
-}
-
-// [heads][S][128] bf16 as a 3-D tensor; a box is 64 columns x kTileRows rows of one head.
-int make_prompt_map(CUtensorMap *map, const void *base, int64_t heads, int64_t seq_len) {
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (!fn) { note_error_text("cuTensorMapEncodeTiled is not available from the driver"); return LRQK_ELAUNCH; }
-  const cuuint64_t dims[3] = {128, (cuuint64_t)seq_len, (cuuint64_t)heads};
-  const cuuint64_t strides[2] = {256, (cuuint64_t)seq_len * 256};
-  const cuuint32_t box[3] = {64, (cuuint32_t)kTileRows, 1};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) { note_error_text("cuTensorMapEncodeTiled failed for the prompt tensor"); return LRQK_ELAUNCH; }
-  return LRQK_OK;
-}
-
 template <int R>
 int launch_r(const GramTcArgs &a, cudaStream_t stream) {
   constexpr int kRawBytes = kTileRows * R * 4;
@@ -324,9 +223,9 @@ int launch_r(const GramTcArgs &a, cudaStream_t stream) {
     attr_set = true;
   }
   CUtensorMap mq, mk;
-  int rc = make_prompt_map(&mq, a.Q, (int64_t)a.bsz * a.q_heads, a.seq_len);
+  int rc = make_prompt_map(&mq, a.Q, (int64_t)a.bsz * a.q_heads, a.seq_len, kTileRows);
   if (rc != LRQK_OK) return rc;
-  rc = make_prompt_map(&mk, a.K, (int64_t)a.bsz * a.kv_heads, a.seq_len);
+  rc = make_prompt_map(&mk, a.K, (int64_t)a.bsz * a.kv_heads, a.seq_len, kTileRows);
   if (rc != LRQK_OK) return rc;
   GramTcParams p;
   p.A_Q0 = a.A_Q0; p.A_K0 = a.A_K0; p.part = a.part; p.status = a.status;

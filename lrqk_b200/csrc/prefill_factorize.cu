@@ -16,6 +16,7 @@
 //                     A_K = K X_K is written in the storage dtype, together with B_Q, B_K and the
 //                     last row of A_Q.
 // Arithmetic is fp32 on the stored operands, as in the reference (which up-casts to fp32).
+#include "apply_tc.cuh"
 #include "common.cuh"
 #include "gram_tc.cuh"
 #include "smallmat.cuh"
@@ -267,6 +268,7 @@ struct ApplyParams {
   int64_t seq_len, a_capacity;
   int32_t q_heads, groups, n_heads, sweeps;
   float tol;
+  int32_t rows_elsewhere;  // non-zero: the rows of A_K are written by the tensor-core apply pass
 };
 
 template <typename T, int R, int D>
@@ -306,7 +308,7 @@ __global__ void __launch_bounds__(kFThreads) apply_kernel(ApplyParams p) {
   T *AKh = reinterpret_cast<T *>(p.A_K) + (int64_t)n * p.a_capacity * R;
   const int64_t row = (int64_t)tile * kApplyRows + tid / 2;
   const int c0 = (tid % 2) * CPT;
-  if (row < p.seq_len) {
+  if (row < p.seq_len && !p.rows_elsewhere) {
     float acc[CPT];
 #pragma unroll
     for (int c = 0; c < CPT; ++c) acc[c] = 0.0f;
@@ -390,7 +392,23 @@ int run(const lrqk_layer *L, const void *Q, const void *K, float *A_Q, float *A_
   pp.Q = Q; pp.K = K; pp.A_K = L->A_K; pp.B_Q = L->B_Q; pp.B_K = L->B_K; pp.a_q_last = a_q_last;
   pp.ws = ws; pp.lay = lay; pp.sweeps_out = sweeps_out; pp.seq_len = seq_len; pp.a_capacity = L->a_capacity;
   pp.q_heads = L->q_heads; pp.groups = groups; pp.n_heads = n_heads; pp.sweeps = sweeps; pp.tol = tol;
-  apply_kernel<T, R, D><<<dim3((unsigned)ceil_div64(seq_len, kApplyRows), n_heads, 1), kFThreads, 0, stream>>>(pp);
+  pp.rows_elsewhere = 0;
+  if constexpr (sizeof(T) == 2 && D == 128) {
+    // bf16 prompts: A_K = K X_K on the tensor cores (X_K rounded to bf16); the SIMT kernel then only
+    // writes B_Q, B_K and the last row of A_Q
+    if (on_tensor_cores) {
+      ApplyTcArgs aa;
+      aa.K = K; aa.A_K = L->A_K; aa.ws = ws; aa.status = reinterpret_cast<int32_t *>(ws + lay.status);
+      aa.seq_len = seq_len; aa.a_capacity = L->a_capacity; aa.sweep_base = lay.sweep; aa.sweep_stride = lay.sweep_stride;
+      aa.sweeps = sweeps; aa.bsz = L->bsz; aa.q_heads = L->q_heads; aa.kv_heads = L->kv_heads; aa.head_dim = D; aa.r = R;
+      aa.tol = tol;
+      const int rc = launch_apply_tc(aa, stream);
+      if (rc == LRQK_OK) pp.rows_elsewhere = 1;
+      else if (rc != LRQK_EUNSUPPORTED) return rc;
+    }
+  }
+  const unsigned apply_tiles = pp.rows_elsewhere ? 1u : (unsigned)ceil_div64(seq_len, kApplyRows);
+  apply_kernel<T, R, D><<<dim3(apply_tiles, n_heads, 1), kFThreads, 0, stream>>>(pp);
   LRQK_LAUNCH_CHECK();
   return LRQK_OK;
 }
