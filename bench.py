@@ -386,7 +386,19 @@ def run_ours(args):
 # ------------------------------------------------------------------------------------------------
 # CPU legs (the only code here that may touch oracle/)
 # ------------------------------------------------------------------------------------------------
+def _use_all_host_threads() -> int:
+    """The CPU legs run on every core this process may use (torchrun pins OMP_NUM_THREADS to 1)."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    os.environ["OMP_NUM_THREADS"] = str(n)      # read by the C oracle's OpenMP runtime when it is loaded
+    torch.set_num_threads(n)
+    return n
+
+
 def _oracle():
+    _use_all_host_threads()
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import lrqk_oracle
     return lrqk_oracle
