@@ -57,7 +57,10 @@ const char *lrqk_last_cuda_error(void);
 /* ------------------------------------------------------------------------------------
  * Page-locked, device-mapped host memory for the K|V store.
  * Stands in for torch.empty(..., pin_memory=True) of AutoIncreaseTensorSharedKV
- * (lrqk_attention.py:883-888, :1088-1094).  The only entries that allocate.
+ * (lrqk_attention.py:883-888, :1088-1094).  The memory is zero-filled, portable across devices and
+ * addressable by kernels through lrqk_host_device_ptr.  (Anonymous huge-page memory registered with
+ * the driver where that works -- about three times quicker to obtain than cudaHostAlloc -- else
+ * cudaHostAlloc.)  These and lrqk_peer_buffer_create are the only entries that allocate.
  * ---------------------------------------------------------------------------------- */
 int lrqk_host_alloc(void **host_ptr, size_t bytes);
 int lrqk_host_free(void *host_ptr);
