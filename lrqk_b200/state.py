@@ -60,26 +60,28 @@ class HostStore:
         self.dtype = dtype
         self.nbytes = int(np.prod(self.shape)) * torch.empty((), dtype=dtype).element_size()
         pooled = _HOST_POOL.get(self.nbytes)
+        fresh = not pooled
         if pooled:
             self.host_ptr = pooled.pop()
             _HOST_POOL_BYTES -= self.nbytes
         else:
             hp = C.c_void_p()
             _lib.check(_lib.lib().lrqk_host_alloc(C.byref(hp), self.nbytes), "lrqk_host_alloc")
-            self.host_ptr = hp.value
+            self.host_ptr = hp.value                   # comes zero-filled
         dp = C.c_void_p()
         _lib.check(_lib.lib().lrqk_host_device_ptr(C.c_void_p(self.host_ptr), C.byref(dp)), "lrqk_host_device_ptr")
         self.device_ptr = dp.value
         raw = (C.c_uint8 * self.nbytes).from_address(self.host_ptr)
         self._raw = raw
         self.data = torch.frombuffer(raw, dtype=torch.uint8).view(dtype).view(self.shape)
-        if zero:
-            self.data.zero_()  # cudaHostAlloc memory (and a pooled buffer) is not zero
+        self._fresh = fresh
+        if zero and not fresh:
+            self.data.zero_()  # a pooled buffer still holds its previous contents
         self.current_len = 0
 
     def zero_rows_from(self, row: int) -> None:
         """Clear rows [row, capacity) of every (batch, KV head) on the host."""
-        if row < self.capacity:
+        if row < self.capacity and not self._fresh:
             self.data[:, :, row:].zero_()
 
     @property
