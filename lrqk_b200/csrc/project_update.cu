@@ -371,10 +371,15 @@ __global__ void __launch_bounds__(kPThreads, 2) project_kernel(ProjectParams p) 
     return;
   }
   const int first_rank = csize == 1 ? 0 : 1;
-  for (int i = tid; i < R * R; i += kPThreads) {
-    float s = 0.0f;
-    for (int c = first_rank; c < csize; ++c) s += cluster.map_shared_rank(Gp, c)[i];
-    GQ[i] += s;  // B_Q B_Q^T + A^T A
+  for (int i = tid; i < R * R / 4; i += kPThreads) {  // 16-byte remote loads, all peers in flight at once
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int c = first_rank; c < csize; ++c) {
+      const float4 v = reinterpret_cast<const float4 *>(cluster.map_shared_rank(Gp, c))[i];
+      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    }
+    float4 g = reinterpret_cast<float4 *>(GQ)[i];
+    g.x += s.x; g.y += s.y; g.z += s.z; g.w += s.w;
+    reinterpret_cast<float4 *>(GQ)[i] = g;  // B_Q B_Q^T + A^T A
   }
   if (tid < R) {
     float s = 0.0f;
