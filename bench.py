@@ -371,7 +371,9 @@ def run_ours(args):
         "e2e": {"value": round(us_per_layer_e2e, 2), "unit": "us/layer/step", "h2d_bytes_per_step": int(h2d),
                 "d2h_bytes_per_step": int(d2h)},
         "host_issue_us_per_layer_step": round(host_issue_us, 1),
-        "gpu_launches": int(args.steps * layers * (6 + (1 if exchange is not None else 0))),
+        # per layer-step: projection, update, scoring(+diff), miss fetch, attention (+ exchange wait);
+        # plus one ring-flush kernel per layer every m steps
+        "gpu_launches": int(args.steps * layers * (5 + (1 if exchange is not None else 0)) + layers * (args.steps // w["m"])),
         "roofline": roof, "roofline_hbm": roof_hbm, "roofline_step": roof_step, "kernels": per_kernel,
         "host_link_peak_gbs": round(link_peak, 1), "clocks": clocks,
     }

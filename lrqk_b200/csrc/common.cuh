@@ -133,10 +133,14 @@ struct FusedDiff {
 int score_topk_enqueue(const lrqk_layer *L, const void *q_hat, int64_t candidates, int32_t *wanted, float *scores_out,
                        int64_t scores_stride, int32_t *clear_word, cudaStream_t stream, const FusedDiff *diff = nullptr);
 
-// lrqk_decode_project_update with one extra duty for the fused step: *clear_word = 0 at the end.
+// lrqk_decode_project_update with extra duties for the fused step: *clear_word = 0 at the end, and --
+// when v_new is given -- the ring write of the step's key/value into lite slot `lite_slot` (position
+// append_row), so that no separate ring-write kernel is needed unless the ring is flushed.
 int project_update_enqueue(const lrqk_layer *L, const void *q, const void *k_new, int32_t max_iter, float tol,
                            int64_t append_row, void *q_hat, int32_t *iters_out, void *workspace, int32_t *clear_word,
-                           cudaStream_t stream);
+                           cudaStream_t stream, const void *v_new, int32_t lite_slot);
+// The flush half of lrqk_lite_append alone: the ring of every KV head to host rows [host_row, host_row + m).
+int lite_flush_enqueue(const lrqk_layer *L, int64_t host_row, cudaStream_t stream);
 
 // Dispatch on the element type of a layer.
 #define LRQK_DISPATCH_DTYPE(dtype, T, ...)                       \

@@ -10,13 +10,19 @@ extern "C" int lrqk_layer_step(const lrqk_layer *L, const lrqk_step_args *a, lrq
       !a->counters || !a->project_workspace)
     return LRQK_EINVAL;
   if ((a->attn_out || a->peers) && !a->attn_workspace) return LRQK_EINVAL;
-  int rc = lrqk_lite_append(L, a->k_new, a->v_new, a->lite_slot, a->position, a->flush_rows, a->host_row, stream);
+  // The ring write is done by the projection kernel (its solver CTAs store the step's key/value, the
+  // streaming CTAs take that row from k_new); a ring-write kernel only runs on the steps that flush
+  // the ring to the host store.  The miss-list length is cleared by the projection's second kernel,
+  // the hit/miss difference runs as the tail of the scoring kernel: five launches per step.
+  if (a->lite_slot < 0 || a->lite_slot >= L->m) return LRQK_ECAPACITY;
+  if (a->flush_rows != 0 && a->flush_rows != L->m) return LRQK_EINVAL;
+  int rc = project_update_enqueue(L, a->q, a->k_new, a->max_iter, a->tol, a->position, a->q_hat, a->counters + 2,
+                                  a->project_workspace, a->counters, as_stream(stream), a->v_new, a->lite_slot);
   if (rc != LRQK_OK) return rc;
-  // the miss-list length is cleared by the projection's second kernel, the hit/miss difference runs
-  // as the tail of the scoring kernel: five launches per step instead of seven plus a memset
-  rc = project_update_enqueue(L, a->q, a->k_new, a->max_iter, a->tol, a->position, a->q_hat, a->counters + 2,
-                              a->project_workspace, a->counters, as_stream(stream));
-  if (rc != LRQK_OK) return rc;
+  if (a->flush_rows) {
+    rc = lite_flush_enqueue(L, a->host_row, as_stream(stream));
+    if (rc != LRQK_OK) return rc;
+  }
   FusedDiff diff;
   diff.mask = a->mask; diff.miss_count = a->miss_count; diff.list = a->miss_list;
   diff.list_len = a->counters; diff.status = a->counters + 1;

@@ -69,6 +69,13 @@ struct ProjectParams {
   int32_t q_heads, groups, k, m, max_iter, n_heads;
   int32_t tile_rows;  // rows a streaming CTA handles per pass over its buffers
   float *ws;          // [N][max_iter][2R+2]
+  // fused ring write (fuse_row >= 0): this kernel also stores the step's key/value into slot
+  // fuse_row of the resident rows (and its position into lite_pos), which the ring-write kernel
+  // does otherwise; the streaming CTAs take that row from k_new instead of from K_res
+  const void *v_new;
+  void *K_res_w, *V_res_w;
+  int32_t *lite_pos_w;
+  int32_t fuse_row, position;
 };
 
 // Rows of the streaming buffers (bounded so that the buffers stay near 40 KiB).
@@ -274,7 +281,7 @@ __global__ void __launch_bounds__(kPThreads, 2) project_kernel(ProjectParams p) 
       const int rows = max(0, min(p.tile_rows, j_end - t0));
       for (int i = tid; i < rows; i += kPThreads) {
         const int j = t0 + i;
-        pos_s[i] = j < p.k ? tab[j] : p.lite_pos[j - p.k];
+        pos_s[i] = j == p.fuse_row ? p.position : (j < p.k ? tab[j] : p.lite_pos[j - p.k]);
       }
       __syncthreads();
       // rank-r rows of the tile's tokens: 16-byte pieces, gathered by all threads
@@ -300,8 +307,11 @@ __global__ void __launch_bounds__(kPThreads, 2) project_kernel(ProjectParams p) 
           const int row = r0 + u * kPWarps;
           float acc = 0.0f;
           if (row < rows) {
+            // the step's own key is not in K_res yet when the ring write is fused (what was loaded for
+            // that slot is the ring's previous occupant): take it from k_new
+            const bool own = t0 + row == p.fuse_row;
 #pragma unroll
-            for (int e = 0; e < EL; ++e) acc = fmaf(kv[u][e], qf[e], acc);
+            for (int e = 0; e < EL; ++e) acc = fmaf(own ? ks[lane * EL + e] : kv[u][e], qf[e], acc);
           }
           acc = warp_sum(acc);
           if (lane == 0 && row < rows) S[row] = acc;
@@ -315,6 +325,15 @@ __global__ void __launch_bounds__(kPThreads, 2) project_kernel(ProjectParams p) 
   }
 
   // ---- solver CTA: everything that does not depend on the active rows ----------------------------
+  if (solver && p.fuse_row >= 0) {  // fused ring write: 16-byte copies of the step's key and value
+    constexpr int CH = D * (int)sizeof(T) / 16;
+    const int64_t dst = ((int64_t)n * (p.k + p.m) + p.fuse_row) * D * (int64_t)sizeof(T);
+    const int64_t src = ((int64_t)b_idx * kv_heads + kvh) * D * (int64_t)sizeof(T);
+    if (tid < CH) st16(reinterpret_cast<char *>(p.K_res_w) + dst + tid * 16, ld16(reinterpret_cast<const char *>(p.k_new) + src + tid * 16));
+    else if (tid < 2 * CH) st16(reinterpret_cast<char *>(p.V_res_w) + dst + (tid - CH) * 16,
+                                ld16(reinterpret_cast<const char *>(p.v_new) + src + (tid - CH) * 16));
+    if (n == 0 && tid == 2 * CH) p.lite_pos_w[p.fuse_row - p.k] = p.position;
+  }
   if (solver) {
     const T *BQg = reinterpret_cast<const T *>(p.B_Q) + (int64_t)n * R * D;
     const T *BKg = reinterpret_cast<const T *>(p.B_K) + (int64_t)n * R * D;
@@ -573,12 +592,12 @@ extern "C" int lrqk_decode_project_update(const lrqk_layer *L, const void *q, co
                                           float tol, int64_t append_row, void *q_hat, int32_t *iters_out,
                                           void *workspace, lrqk_stream_t stream) {
   return lrqk::project_update_enqueue(L, q, k_new, max_iter, tol, append_row, q_hat, iters_out, workspace, nullptr,
-                                      lrqk::as_stream(stream));
+                                      lrqk::as_stream(stream), nullptr, -1);
 }
 
 int lrqk::project_update_enqueue(const lrqk_layer *L, const void *q, const void *k_new, int32_t max_iter, float tol,
                                  int64_t append_row, void *q_hat, int32_t *iters_out, void *workspace,
-                                 int32_t *clear_word, cudaStream_t s) {
+                                 int32_t *clear_word, cudaStream_t s, const void *v_new, int32_t lite_slot) {
   int rc = check_device();
   if (rc != LRQK_OK) return rc;
   rc = check_layer(L);
@@ -596,6 +615,12 @@ int lrqk::project_update_enqueue(const lrqk_layer *L, const void *q, const void 
   pp.max_iter = max_iter; pp.n_heads = L->bsz * L->q_heads;
   pp.tile_rows = 0;
   pp.ws = reinterpret_cast<float *>(workspace);
+  pp.v_new = v_new; pp.K_res_w = L->K_res; pp.V_res_w = L->V_res; pp.lite_pos_w = L->lite_pos;
+  pp.fuse_row = -1; pp.position = (int32_t)append_row;
+  if (v_new) {
+    if (lite_slot < 0 || lite_slot >= L->m || !L->V_res) return LRQK_EINVAL;
+    pp.fuse_row = L->k + lite_slot;
+  }
   UpdateParams up;
   up.A_K = L->A_K; up.B_Q = L->B_Q; up.B_K = L->B_K; up.q = q; up.k_new = k_new;
   up.ws = pp.ws; up.q_hat = q_hat; up.iters_out = iters_out;
