@@ -47,7 +47,7 @@ WORKLOADS = {
 }
 # dram__bytes (read + write) of one launch from the ncu capture summarised in
 # profiles/path_kernels_cfg2_ncu_sections.md (1 GPU, cfg2-layer)
-NCU_TRAFFIC_CFG2 = {"score_topk": 272.5e6, "flash_decode": 35.2e6, "project_update": 27.2e6, "slot_diff": 0.5e6,
+NCU_TRAFFIC_CFG2 = {"score_topk": 272.8e6, "flash_decode": 35.2e6, "project_update": 27.2e6, "slot_diff": 0.5e6,
                     "miss_gather": 0.8e6, "lite_append": 0.0}
 FALLBACK_HBM_GBS = 6650.0
 
