@@ -527,8 +527,16 @@ def run_model(args):
     cfg_cls = transformers.LlamaConfig if family == "llama" else transformers.Qwen2Config
     cfg = cfg_cls(max_position_embeddings=prompt + n_decode + 64, **spec)
     cfg._attn_implementation = "sdpa"
-    torch.cuda.set_device(0)
-    torch.manual_seed(args.seed)
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    from lrqk_b200 import sharding as _sharding
+    _sharding.bind_host_to_gpu_numa(local_rank)                # the host K|V stores are allocated after this
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    torch.manual_seed(args.seed)                               # every rank builds the same weights
     t0 = time.time()
     with torch.device("cuda"):
         model = transformers.AutoModelForCausalLM.from_config(cfg, dtype=torch.bfloat16)
@@ -539,41 +547,69 @@ def run_model(args):
     ids = torch.randint(0, cfg.vocab_size, (batch, prompt), generator=torch.Generator().manual_seed(args.seed)).cuda()
     cache = DynamicLRQKCache(r=r, num_active_tokens=k, lite_tokens=m, max_iter=max_iter, tol=1e-2,
                              max_sequence_length=prompt + n_decode + 2 * m + 64, num_key_value_groups=groups)
-    sampler = ClockSampler(0)
-    with torch.no_grad():
+    if world > 1:
+        cache.shard_heads()            # this rank keeps 1/world of every layer's (batch x KV head) units
+
+    def barrier():
         torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def step(tok):
+        tok = model(input_ids=tok, past_key_values=cache, use_cache=True).logits[:, -1].argmax(-1, keepdim=True)
+        if world > 1:
+            dist.broadcast(tok, 0)     # the ranks compute the same logits; this keeps them on one token regardless
+        return tok
+
+    sampler = ClockSampler(local_rank)
+    with torch.no_grad():
+        barrier()
         t1 = time.time()
         out = model(input_ids=ids, past_key_values=cache, use_cache=True, logits_to_keep=1)
-        torch.cuda.synchronize()
+        barrier()
         prefill_s = time.time() - t1
         tok = out.logits[:, -1].argmax(-1, keepdim=True)
+        if world > 1:
+            dist.broadcast(tok, 0)
         for _ in range(args.warmup):
-            tok = model(input_ids=tok, past_key_values=cache, use_cache=True).logits[:, -1].argmax(-1, keepdim=True)
-        torch.cuda.synchronize()
+            tok = step(tok)
+        barrier()
         sampler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(n_decode):
-            tok = model(input_ids=tok, past_key_values=cache, use_cache=True).logits[:, -1].argmax(-1, keepdim=True)
+            tok = step(tok)
         e1.record()
-        torch.cuda.synchronize()
+        barrier()
         clocks = sampler.stop()
+        if cache.sharding is not None and cache.sharding._exchange is not None:
+            cache.sharding._exchange.check_status()
     ms = e0.elapsed_time(e1)
     miss = float(torch.stack([f.state.miss_count.float().mean() for f in cache.lwattn.values()]).mean()) / k
+    if world > 1:
+        t = torch.tensor([ms, prefill_s], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)               # the slowest rank's device time counts
+        ms, prefill_s = float(t[0]), float(t[1])
     line = {
-        "metric": "decode_tokens_per_s", "value": round(batch * n_decode / (ms * 1e-3), 2), "unit": "tokens/s", "n_gpus": 1,
-        "steps": n_decode, "warmup": args.warmup, "ms_per_step": round(ms / n_decode, 3), "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "metric": "decode_tokens_per_s", "value": round(batch * n_decode / (ms * 1e-3), 2), "unit": "tokens/s",
+        "n_gpus": world, "steps": n_decode, "warmup": args.warmup, "ms_per_step": round(ms / n_decode, 3),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"{args.model} architecture, random init, {cfg.num_hidden_layers} layers, batch {batch}, "
                                f"{prompt}-token uniform-random prompt, greedy decode", "r": r, "k": k, "m": m,
-                   "max_iter": list(max_iter), "dense_parts": "transformers modules (library GEMMs, SDPA for the prompt pass)"},
+                   "max_iter": list(max_iter), "dense_parts": "transformers modules (library GEMMs, SDPA for the prompt pass)"
+                   + (", replicated on every rank" if world > 1 else ""),
+                   "parallelism": f"(batch x KV head) units over {world} ranks, attention rows pushed over NVLink"
+                   if world > 1 else "single GPU"},
         "us_per_layer_step_including_dense": round(ms * 1e3 / (n_decode * cfg.num_hidden_layers), 1),
         "prefill_s": round(prefill_s, 2), "prefill_tokens_per_s": round(batch * prompt / prefill_s, 1),
         "model_build_s": round(build_s, 1), "last_step_miss_rate": round(miss, 4), "clocks": clocks,
     }
-    print(json.dumps(line), flush=True)
-    for f in cache.lwattn.values():
-        f.close()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    cache.close()
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def main():
@@ -590,7 +626,7 @@ def main():
     ap.add_argument("--collective", default="push", choices=["push", "nccl", "none"],
                     help="N > 1: how the attention rows of all heads reach every rank")
     ap.add_argument("--model", default=None, choices=sorted(MODELS),
-                    help="run a whole random-init decoder stack instead of the per-layer workload (1 GPU)")
+                    help="run a whole random-init decoder stack instead of the per-layer workload")
     ap.add_argument("--prompt", type=int, default=0, help="--model: prompt length (default: the configuration's)")
     ap.add_argument("--decode", type=int, default=0, help="--model: tokens to decode (default: the configuration's)")
     ap.add_argument("--batch", type=int, default=0, help="--model: sequences (default: the configuration's)")

@@ -26,6 +26,11 @@ What the patched forward does with the cache:
   write, rank-r projection, proxy scoring + top-k, hit/miss, miss fetch, attention over the
   resident rows) in the CUDA library and returns the attention output directly.
 
+With ``cache.shard_heads()`` (one process per GPU) the dense parts run replicated on every rank,
+each rank's cache holds its share of the (batch x KV head) units, the prompt's attention is taken
+for those heads only and all-gathered, and ``cache.attend`` returns all heads' rows through the
+exchange fused into the attention kernel.
+
 Any other cache type falls through to the family's original forward.
 """
 from __future__ import annotations
@@ -105,8 +110,18 @@ def lrqk_attention_forward(self, hidden_states: torch.Tensor,
         pad = _padding_mask(attention_mask, key_states.shape[2])
         K, V = cache.update(query_states, key_states.contiguous(), value_states.contiguous(), self.layer_idx,
                             attention_mask=None if pad is None else pad.to(key_states.dtype))
-        attn_output = _causal_attention(query_states, K, V, self.scaling, _padding_mask(attention_mask, K.shape[2]),
-                                        mask4d=attention_mask)
+        pad_all, sh = _padding_mask(attention_mask, K.shape[2]), getattr(cache, "sharding", None)
+        if sh is None:
+            attn_output = _causal_attention(query_states, K, V, self.scaling, pad_all, mask4d=attention_mask)
+        else:
+            # head-sharded cache: K, V are this rank's; attend for its query heads, then every rank
+            # receives the rows of all heads
+            hkv, mask4d = key_states.shape[1], attention_mask
+            if mask4d is not None and mask4d.dim() == 4 and mask4d.shape[0] == query_states.shape[0]:
+                mask4d = sh.local_rows(mask4d, hkv)
+            local = _causal_attention(sh.local(query_states, hkv), K, V, self.scaling, sh.local_rows(pad_all, hkv),
+                                      mask4d=mask4d)
+            attn_output = sh.gather_prompt(local, query_states.shape[0], hkv, query_states.shape[1])
     attn_output = attn_output.reshape(*input_shape, -1).contiguous()
     return self.o_proj(attn_output), None
 

@@ -603,6 +603,24 @@ class DynamicLRQKCache(_CacheBase):
             r=r, max_iter=max_iter, tol=tol, capacity=max_sequence_length, init_aq_ak_method=init_aq_ak_method))
         self.temp_buff_cache_qkv: Dict[int, _CacheQKV] = defaultdict(lambda: _CacheQKV(num_active_tokens, 2))
         self.sequence_state = defaultdict(lambda: DynamicLRQKCache.State.pending)
+        self.sharding = None
+
+    def shard_heads(self, group=None, sharding=None):
+        """Run every layer for this rank's share of the (batch x KV head) units only (one process per
+        GPU, ``group`` = the ranks taking part, default the whole process group).  ``update`` and
+        ``attend`` keep taking the full [B, H, L, d] tensors, identical on every rank; ``attend``
+        still returns the rows of ALL heads (the attention kernel stores them into every rank's
+        exchange buffer), ``update`` returns this rank's K, V.  The reference is single-GPU."""
+        from .sharding import HeadSharding
+        if self.sequence_state:
+            raise RuntimeError("shard_heads() must be called before the first layer sees a prompt")
+        self.sharding = sharding if sharding is not None else HeadSharding(group)
+        return self.sharding
+
+    def _local(self, query_states, key_states, value_states, attention_mask=None):
+        sh, hkv = self.sharding, key_states.shape[1]
+        q, k, v = (sh.local(x, hkv).contiguous() for x in (query_states, key_states, value_states))
+        return q, k, v, sh.local_rows(attention_mask, hkv)
 
     def __getitem__(self, layer_idx: int):
         raise NotImplementedError("DynamicLRQKCache does not support indexing")
@@ -654,6 +672,9 @@ class DynamicLRQKCache(_CacheBase):
                layer_idx: int, attention_mask: Optional[torch.Tensor] = None):
         if any(c is None for c in (query_states, key_states, value_states)):
             raise ValueError("None of query_states, key_states, and value_states can be None")
+        if self.sharding is not None:
+            query_states, key_states, value_states, attention_mask = self._local(query_states, key_states,
+                                                                                 value_states, attention_mask)
         if self.sequence_state[layer_idx] != self.State.decoding:
             return self._prefill_states(query_states, key_states, value_states, layer_idx, attention_mask)
         return self.lwattn[layer_idx].decode(query_states, key_states, value_states)
@@ -663,4 +684,18 @@ class DynamicLRQKCache(_CacheBase):
         """Decode-state only: one step plus attention, returns [B,Hq,1,d]."""
         if self.sequence_state[layer_idx] != self.State.decoding:
             raise RuntimeError("attend() is only valid once the layer is decoding; use update() before")
-        return self.lwattn[layer_idx].decode_attend(query_states, key_states, value_states)
+        fac = self.lwattn[layer_idx]
+        if self.sharding is None:
+            return fac.decode_attend(query_states, key_states, value_states)
+        bsz, hq, hkv = query_states.shape[0], query_states.shape[1], key_states.shape[1]
+        q, k, v, _ = self._local(query_states, key_states, value_states)
+        exchange = self.sharding.exchange(q.shape[0] * q.shape[1], q.shape[-1], fac.state.dtype)
+        fac.decode_attend_push(q, k, v, exchange)
+        return self.sharding.gather_step(bsz, hkv, hq).unsqueeze(2)
+
+    def close(self):
+        """Free every layer's device and page-locked host memory and the exchange buffers."""
+        for fac in self.lwattn.values():
+            fac.close()
+        if self.sharding is not None:
+            self.sharding.close()

@@ -125,6 +125,91 @@ def assemble(gathered: torch.Tensor, shards: Sequence[Shard], bsz: int, q_heads:
     return out
 
 
+class HeadSharding:
+    """Runs a whole decoder stack with every layer's (batch, KV head) units split over the ranks of a
+    process group: the dense parts of the model are replicated, each rank keeps the LRQK state of its
+    units only, and after the attention of a layer every rank receives the rows of all heads --
+    through ``HeadExchange`` while decoding (one row per head, latency-bound), through the group's
+    all-gather for the prompt pass (the prompt's rows of all heads, bandwidth-bound).
+
+    ``DynamicLRQKCache.shard_heads`` attaches one of these to a cache; the patched attention forward
+    then hands the cache full [B, H, L, d] tensors and this object cuts and reassembles them."""
+
+    def __init__(self, group=None, rank: Optional[int] = None, world: Optional[int] = None):
+        if rank is None or world is None:
+            import torch.distributed as dist
+            rank, world = dist.get_rank(group), dist.get_world_size(group)
+        self.group, self.rank, self.world = group, rank, world
+        self._plans = {}
+        self._exchange: Optional[HeadExchange] = None
+
+    def plan(self, bsz: int, kv_heads: int) -> List[Shard]:
+        key = (bsz, kv_heads)
+        if key not in self._plans:
+            self._plans[key] = plan_shards(bsz, kv_heads, self.world)
+        return self._plans[key]
+
+    def shard(self, bsz: int, kv_heads: int) -> Shard:
+        return self.plan(bsz, kv_heads)[self.rank]
+
+    def local(self, x: torch.Tensor, kv_heads: int) -> torch.Tensor:
+        """This rank's part of a [B, H, ...] tensor of query heads (H = kv_heads * groups) or KV heads."""
+        return slice_for_shard(x, self.shard(x.shape[0], kv_heads), x.shape[1] // kv_heads)
+
+    def local_rows(self, x: Optional[torch.Tensor], kv_heads: int) -> Optional[torch.Tensor]:
+        """This rank's batch entries of a per-sequence tensor [B, ...] (a padding mask)."""
+        if x is None:
+            return None
+        s = self.shard(x.shape[0], kv_heads)
+        return x[s.b0:s.b0 + s.bsz]
+
+    def _assemble(self, gathered: torch.Tensor, bsz: int, kv_heads: int, q_heads: int) -> torch.Tensor:
+        """[world, b_local, hq_local, ...] -> [B, Hq, ...] in model order."""
+        plan = self.plan(bsz, kv_heads)
+        if plan[0].bsz == bsz:                                  # only heads are split: one permuting copy
+            order = (1, 0, 2) + tuple(range(3, gathered.dim()))
+            return gathered.permute(*order).reshape((bsz, q_heads) + tuple(gathered.shape[3:]))
+        return assemble(gathered, plan, bsz, q_heads, q_heads // kv_heads)
+
+    def gather_prompt(self, out_local: torch.Tensor, bsz: int, kv_heads: int, q_heads: int) -> torch.Tensor:
+        """All ranks' prompt attention rows: [b_local, L, hq_local, d] -> [B, L, Hq, d]."""
+        import torch.distributed as dist
+        out_local = out_local.contiguous()
+        gathered = out_local.new_empty((self.world,) + tuple(out_local.shape))
+        dist.all_gather_into_tensor(gathered.view((-1,) + tuple(out_local.shape[1:])), out_local, group=self.group)
+        plan = self.plan(bsz, kv_heads)
+        seq_len, d = out_local.shape[1], out_local.shape[3]
+        if plan[0].bsz == bsz:                                  # only heads are split: one permuting copy
+            return gathered.permute(1, 2, 0, 3, 4).reshape(bsz, seq_len, q_heads, d)
+        out = out_local.new_empty((bsz, seq_len, q_heads, d))
+        g = q_heads // kv_heads
+        for s in plan:
+            out[s.b0:s.b0 + s.bsz, :, s.h0 * g:(s.h0 + s.kv_heads) * g].copy_(gathered[s.rank])
+        return out
+
+    def exchange(self, heads_per_rank: int, head_dim: int, dtype: torch.dtype) -> HeadExchange:
+        """The exchange buffers of the decode steps (created collectively at the first step; every
+        layer uses the same ones, a push being waited for before the next layer pushes)."""
+        ex = self._exchange
+        if ex is None:
+            ex = self._exchange = HeadExchange(heads_per_rank, head_dim, dtype, group=self.group)
+        elif (ex.heads_per_rank, ex.head_dim, ex.dtype) != (heads_per_rank, head_dim, dtype):
+            raise ValueError("the layers of one cache must share head count, head size and dtype")
+        return ex
+
+    def gather_step(self, bsz: int, kv_heads: int, q_heads: int) -> torch.Tensor:
+        """Wait for the outstanding push of this layer; returns the rows of all heads [B, Hq, d]."""
+        ex = self._exchange
+        rows = ex.wait()
+        s = self.shard(bsz, kv_heads)
+        return self._assemble(rows.view(self.world, s.bsz, -1, ex.head_dim), bsz, kv_heads, q_heads)
+
+    def close(self):
+        if self._exchange is not None:
+            self._exchange.close()
+            self._exchange = None
+
+
 class PushSequence:
     """Sequence numbers of the pushes of one exchange buffer: 1, 2, 3, ...; push ``seq`` uses half
     ``seq & 1`` of the buffer, so a rank may issue push seq + 1 only after it has waited for push

@@ -99,3 +99,68 @@ def test_unknown_family_is_rejected_like_the_reference():
     from lrqk_b200.hf_models import family_of
     with pytest.raises(ValueError):
         family_of("gpt2")
+
+
+def _sharded_rank(rank, world, port, out_dir):
+    """One rank of a head-sharded tiny Llama stack; rank 0 also runs the unsharded cache on the same
+    weights and compares prompt logits and a run of decode logits."""
+    import os
+    import torch.distributed as dist
+    from lrqk_b200 import DynamicLRQKCache, patch_model
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        model = _tiny("llama")                                   # same seed: same weights on every rank
+        patch_model(model)
+        S, n_steps = 290, 20
+        ids = torch.randint(0, 512, (2, S), generator=torch.Generator().manual_seed(1)).cuda()
+        mk = lambda: DynamicLRQKCache(r=16, num_active_tokens=256, lite_tokens=16, max_iter=2, tol=1e-2,  # noqa: E731
+                                      max_sequence_length=1024, num_key_value_groups=2, init_aq_ak_method="top")
+
+        def run(cache):
+            logits = []
+            with torch.no_grad():
+                out = model(input_ids=ids, past_key_values=cache, use_cache=True).logits
+                logits.append(out[:, -1].float())
+                tok = out[:, -1].argmax(-1, keepdim=True)
+                for _ in range(n_steps):
+                    if cache.sharding is not None:
+                        dist.broadcast(tok, 0)
+                    step = model(input_ids=tok, past_key_values=cache, use_cache=True).logits[:, -1]
+                    logits.append(step.float())
+                    tok = step.argmax(-1, keepdim=True)
+            return torch.stack(logits)
+
+        sharded = mk()
+        sharded.shard_heads()
+        got = run(sharded)
+        mine = sharded.sharding.shard(2, 2)
+        ok = sharded.lwattn[0].state.kv_heads == mine.kv_heads == 1 and sharded.get_seq_length() == S + n_steps
+        sharded.sharding._exchange.check_status()
+        sharded.close()
+        if rank == 0:
+            plain = mk()
+            want = run(plain)
+            plain.close()
+            cos = torch.nn.functional.cosine_similarity(got, want, dim=-1)
+            ok = ok and bool(torch.isfinite(got).all()) and float(cos.min()) > 0.995
+            detail = f"cos_min={float(cos.min()):.5f} max_abs={float((got - want).abs().max()):.4f}"
+        else:
+            detail = ""
+        with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
+            f.write(("ok " if ok else "mismatch ") + detail)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_head_sharded_stack_on_two_gpus_matches_the_unsharded_one(tmp_path):
+    import socket
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_sharded_rank, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        assert (tmp_path / f"rank{r}.txt").read_text().startswith("ok"), (tmp_path / f"rank{r}.txt").read_text()

@@ -90,6 +90,64 @@ def test_two_ranks_over_gloo_assemble_the_unsharded_result(tmp_path):
         assert (tmp_path / f"rank{r}.txt").read_text() == "ok"
 
 
+def _prompt_rank_main(rank: int, world: int, port: int, out_dir: str):
+    """The prompt pass of a head-sharded decoder layer as the patched forward runs it: attention of
+    this rank's heads, all-gather, model order -- for heads-only and batch-x-heads splits, with a
+    left-padded sequence."""
+    from lrqk_b200.hf_models import _causal_attention
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        ok = True
+        for bsz, hq, hkv in ((2, 8, 4), (2, 3, 1)):                # second: ranks outnumber KV heads
+            S, d = 24, 16
+            g = torch.Generator().manual_seed(7)
+            q = torch.randn(bsz, hq, S, d, generator=g)
+            K = torch.randn(bsz, hkv, S, d, generator=g)
+            V = torch.randn(bsz, hkv, S, d, generator=g)
+            pad = torch.ones(bsz, S, dtype=torch.bool)
+            pad[1, :5] = False
+            sh = sharding.HeadSharding()
+            assert (sh.rank, sh.world) == (rank, world)
+            local = _causal_attention(sh.local(q, hkv), sh.local(K, hkv), sh.local(V, hkv), d ** -0.5,
+                                      sh.local_rows(pad, hkv))
+            full = sh.gather_prompt(local, bsz, hkv, hq)
+            ref = _causal_attention(q, K, V, d ** -0.5, pad)
+            real = pad[:, :, None, None].expand_as(ref)               # rows of padded queries are undefined
+            ok = ok and full.shape == ref.shape and torch.allclose(full[real], ref[real], atol=1e-5)
+            # one decode row per head through the same assembly
+            rows = torch.randn(bsz, hq, d, generator=g)
+            mine = sh.local(rows, hkv).contiguous()
+            parts = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(parts, mine)
+            ok = ok and torch.equal(sh._assemble(torch.stack(parts), bsz, hkv, hq), rows)
+        with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
+            f.write("ok" if ok else "mismatch")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_head_sharded_prompt_pass_over_gloo(tmp_path):
+    world, port = 2, _free_port()
+    mp.spawn(_prompt_rank_main, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        assert (tmp_path / f"rank{r}.txt").read_text() == "ok"
+
+
+def test_cache_refuses_to_shard_after_the_first_prompt():
+    from lrqk_b200 import DynamicLRQKCache
+    cache = DynamicLRQKCache(num_key_value_groups=2)
+    cache.sequence_state[0] = cache.State.decoding
+    with pytest.raises(RuntimeError):
+        cache.shard_heads(sharding=sharding.HeadSharding(rank=0, world=2))
+    fresh = DynamicLRQKCache(num_key_value_groups=2)
+    sh = fresh.shard_heads(sharding=sharding.HeadSharding(rank=1, world=2))
+    assert fresh.sharding is sh and sh.shard(1, 8).h0 == 4
+    x = torch.arange(2 * 8 * 3 * 4.0).reshape(2, 8, 3, 4)
+    q, k, v, mask = fresh._local(x, x[:, :4], x[:, :4], torch.ones(2, 3))
+    assert torch.equal(q, x[:, 4:]) and torch.equal(k, x[:, 2:4]) and mask.shape == (2, 3)
+
+
 def test_cpulist_parsing_and_missing_topology(tmp_path):
     assert sharding._parse_cpulist("0-3,8,10-11\n") == [0, 1, 2, 3, 8, 10, 11]
     assert sharding._parse_cpulist("") == []
