@@ -506,6 +506,11 @@ MODELS = {
     "qwen2.5-7b": dict(family="qwen", vocab_size=152064, hidden_size=3584, intermediate_size=18944, num_hidden_layers=28,
                        num_attention_heads=28, num_key_value_heads=4, rope_theta=1e6,
                        r=16, k=1024, m=32, max_iter=(1, 1), batch=8, prompt=65536, decode=128),
+    # Qwen2.5-32B architecture, the settings of the 256K configuration (all 64 layers need several GPUs:
+    # the rank-r key factors alone are 1.3 GB per layer per 262144 tokens, beside 65 GB of weights)
+    "qwen2.5-32b": dict(family="qwen", vocab_size=152064, hidden_size=5120, intermediate_size=27648, num_hidden_layers=64,
+                        num_attention_heads=40, num_key_value_heads=8, rope_theta=1e6,
+                        r=64, k=4096, m=128, max_iter=(4, 4), batch=1, prompt=262144, decode=64),
 }
 
 
@@ -574,12 +579,17 @@ def run_model(args):
             dist.broadcast(tok, 0)
         for _ in range(args.warmup):
             tok = step(tok)
+        facs = [cache.lwattn[i] for i in range(cfg.num_hidden_layers)]
+        watched = [facs[0], facs[len(facs) // 2], facs[-1]]
+        miss_log = torch.zeros((n_decode, len(watched)), dtype=torch.float32, device="cuda")
         barrier()
         sampler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(n_decode):
+        for t in range(n_decode):
             tok = step(tok)
+            for j, f in enumerate(watched):                    # refilled slots of three layers, no host sync
+                miss_log[t, j] = f.state.miss_count.sum()
         e1.record()
         barrier()
         clocks = sampler.stop()
@@ -587,6 +597,11 @@ def run_model(args):
             cache.sharding._exchange.check_status()
     ms = e0.elapsed_time(e1)
     miss = float(torch.stack([f.state.miss_count.float().mean() for f in cache.lwattn.values()]).mean()) / k
+    st0 = facs[0].state
+    slots = st0.bsz * st0.q_heads * k                          # selected rows per layer-step on this rank
+    hit_per_step = (1.0 - miss_log.mean(dim=1) / slots).cpu()
+    row_bytes = 2 * st0.head_dim * 2                            # one K|V row, bf16
+    fetched = float(miss_log.mean()) * cfg.num_hidden_layers * n_decode * row_bytes
     if world > 1:
         t = torch.tensor([ms, prefill_s], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)               # the slowest rank's device time counts
@@ -603,7 +618,14 @@ def run_model(args):
                    if world > 1 else "single GPU"},
         "us_per_layer_step_including_dense": round(ms * 1e3 / (n_decode * cfg.num_hidden_layers), 1),
         "prefill_s": round(prefill_s, 2), "prefill_tokens_per_s": round(batch * prompt / prefill_s, 1),
-        "model_build_s": round(build_s, 1), "last_step_miss_rate": round(miss, 4), "clocks": clocks,
+        "model_build_s": round(build_s, 1), "last_step_miss_rate": round(miss, 4),
+        "hit_rate_per_step": {"first": round(float(hit_per_step[0]), 4), "min": round(float(hit_per_step.min()), 4),
+                              "mean": round(float(hit_per_step.mean()), 4), "max": round(float(hit_per_step.max()), 4),
+                              "of": "layers 0, L/2, L-1 of rank 0"},
+        # bytes the miss fetch moved over this rank's host link, spread over the WHOLE decode time (dense
+        # parts included): a floor of the link rate while the fetch kernel runs
+        "miss_fetch_host_link_gbs_over_whole_step": round(fetched / (ms * 1e-3) / 1e9, 2),
+        "clocks": clocks,
     }
     if rank == 0:
         print(json.dumps(line), flush=True)
