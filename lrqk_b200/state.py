@@ -143,6 +143,7 @@ class LayerState:
         self.project_ws = torch.zeros((max(nb, 16),), dtype=torch.uint8, device=self.device)
         nb = self.lib.lrqk_flash_decode_workspace_bytes(C.byref(self.c), k + m)
         self.attn_ws = torch.zeros((max(nb, 16),), dtype=torch.uint8, device=self.device)
+        self._step_args = None
 
     def _rebuild_struct(self):
         c = _lib.Layer()
@@ -213,16 +214,20 @@ class LayerState:
     def make_step_args(self, q, k_new, v_new, lite_slot: int, position: int, flush_rows: int, host_row: int,
                        candidates: int, max_iter: int, tol: float, scale: Optional[float] = None,
                        attention: bool = True) -> _lib.StepArgs:
-        a = _lib.StepArgs()
+        a = self._step_args
+        if a is None:                      # the buffers below live as long as the state: fill them in once
+            a = self._step_args = _lib.StepArgs()
+            a.q_hat, a.wanted, a.mask = self.q_hat.data_ptr(), self.wanted.data_ptr(), self.mask.data_ptr()
+            a.miss_count, a.miss_list = self.miss_count.data_ptr(), self.miss_list.data_ptr()
+            a.counters = self.counters.data_ptr()
+            a.project_workspace, a.attn_workspace = self.project_ws.data_ptr(), self.attn_ws.data_ptr()
+            self._attn_out_ptr, self._default_scale = self.attn_out.data_ptr(), self.head_dim ** -0.5
         a.q, a.k_new, a.v_new = q.data_ptr(), k_new.data_ptr(), v_new.data_ptr()
-        a.attn_out = self.attn_out.data_ptr() if attention else None
+        a.attn_out = self._attn_out_ptr if attention else None
         a.lite_slot, a.position, a.flush_rows, a.host_row = lite_slot, position, flush_rows, host_row
         a.candidates, a.max_iter, a.tol = candidates, max_iter, tol
-        a.scale = self.head_dim ** -0.5 if scale is None else scale
-        a.q_hat, a.wanted, a.mask = self.q_hat.data_ptr(), self.wanted.data_ptr(), self.mask.data_ptr()
-        a.miss_count, a.miss_list = self.miss_count.data_ptr(), self.miss_list.data_ptr()
-        a.counters = self.counters.data_ptr()
-        a.project_workspace, a.attn_workspace = self.project_ws.data_ptr(), self.attn_ws.data_ptr()
+        a.scale = self._default_scale if scale is None else scale
+        a.peers, a.push_seq = None, 0
         return a
 
     def layer_step(self, args: _lib.StepArgs):
