@@ -586,11 +586,13 @@ def run_model(args):
         sampler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
+        h0 = time.perf_counter()
         for t in range(n_decode):
             tok = step(tok)
             for j, f in enumerate(watched):                    # refilled slots of three layers, no host sync
                 miss_log[t, j] = f.state.miss_count.sum()
         e1.record()
+        host_issue_ms = (time.perf_counter() - h0) * 1e3        # host time to ENQUEUE the steps (no sync inside)
         barrier()
         clocks = sampler.stop()
         if cache.sharding is not None and cache.sharding._exchange is not None:
@@ -619,6 +621,8 @@ def run_model(args):
         "us_per_layer_step_including_dense": round(ms * 1e3 / (n_decode * cfg.num_hidden_layers), 1),
         "prefill_s": round(prefill_s, 2), "prefill_tokens_per_s": round(batch * prompt / prefill_s, 1),
         "model_build_s": round(build_s, 1), "last_step_miss_rate": round(miss, 4),
+        # close to ms_per_step: the host's launch rate bounds the step (dense parts are ~40 eager launches a layer)
+        "host_issue_ms_per_step": round(host_issue_ms / n_decode, 3),
         "hit_rate_per_step": {"first": round(float(hit_per_step[0]), 4), "min": round(float(hit_per_step.min()), 4),
                               "mean": round(float(hit_per_step.mean()), 4), "max": round(float(hit_per_step.max()), 4),
                               "of": "layers 0, L/2, L-1 of rank 0"},

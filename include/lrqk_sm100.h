@@ -296,6 +296,22 @@ int lrqk_take_along_dim_with_mask(void *dst, const void *src, const int64_t *ind
                                   void *workspace, lrqk_stream_t stream);
 
 /* ------------------------------------------------------------------------------------
+ * The patched attention forward's decode-time preamble (lrqk_attention.py:2254-2275: q_proj,
+ * k_proj, v_proj -> view/transpose -> apply_rotary_pos_emb), after ONE fused projection: from
+ * qkv [bsz, (q_heads + 2 kv_heads) * head_dim] (one new token per sequence; q heads, then k
+ * heads, then v heads) and the position's cos, sin [cos_rows, head_dim] (cos_rows = bsz, or 1 when
+ * all sequences are at the same position), writes the rotated q
+ * [b_count, kvh_count * G, head_dim], rotated k and plain v [b_count, kvh_count, head_dim] of
+ * batch entries b0 .. b0+b_count-1 and KV heads kvh0 .. kvh0+kvh_count-1 (a rank's shard; the
+ * whole tensor with 0, bsz, 0, kv_heads).  Rotate-half form, x*cos + rotate_half(x)*sin, rounded
+ * to `dtype` after each product and after the sum like the eager tensor operations.
+ * ---------------------------------------------------------------------------------- */
+int lrqk_rope_qkv(const void *qkv, const void *cos, const void *sin, int32_t cos_rows, int32_t dtype,
+                  int32_t bsz, int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t b0, int32_t b_count,
+                  int32_t kvh0, int32_t kvh_count, void *q_out, void *k_out, void *v_out,
+                  lrqk_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
  * Prompt-time helpers of LightAttentionIndicesFactory.prefill (lrqk_attention.py:1385-1504).
  * ---------------------------------------------------------------------------------- */
 /* K|V rows of the prompt into the host store (KVcpu.append, :1469, :959-963):

@@ -104,6 +104,9 @@ _SIGNATURES = {
     "lrqk_take_along_dim_with_mask": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
                                                 C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_void_p,
                                                 C.c_void_p, C.c_void_p]),
+    "lrqk_rope_qkv": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
+                                C.c_void_p]),
     "lrqk_kv_pack_host": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
     "lrqk_prefill_fill_resident": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "lrqk_prefill_factorize_workspace_bytes": (C.c_size_t, [C.POINTER(Layer), C.c_int64]),

@@ -83,6 +83,35 @@ def _padding_mask(attention_mask: Optional[torch.Tensor], seq_len: int) -> Optio
     return None
 
 
+def _fused_qkv(attn):
+    """(weight [(Hq + 2 Hkv) d, hidden], bias or None) of one projection that yields q|k|v, or None when the
+    module's projections are not three plain ``nn.Linear`` of one dtype.  Built once: the three weights are
+    concatenated and each projection's parameter is re-pointed to its rows of the fused tensor, so no memory is
+    added and the separate projections keep working."""
+    f = getattr(attn, "_lrqk_qkv", None)
+    if f is not None:
+        if f is False or attn.q_proj.weight.data_ptr() == f[0].data_ptr():
+            return f or None
+    projs = (attn.q_proj, attn.k_proj, attn.v_proj)
+    ok = (all(type(p) is torch.nn.Linear for p in projs)
+          and len({(p.weight.dtype, p.weight.device, p.in_features, p.bias is None) for p in projs}) == 1)
+    if not ok:
+        attn._lrqk_qkv = False
+        return None
+    with torch.no_grad():
+        w = torch.cat([p.weight.data for p in projs], 0)
+        b = None if projs[0].bias is None else torch.cat([p.bias.data for p in projs], 0)
+        off = 0
+        for p in projs:
+            n = p.out_features
+            p.weight.data = w[off:off + n]
+            if b is not None:
+                p.bias.data = b[off:off + n]
+            off += n
+    attn._lrqk_qkv = (w, b)
+    return attn._lrqk_qkv
+
+
 def lrqk_attention_forward(self, hidden_states: torch.Tensor,
                            position_embeddings: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
                            attention_mask: Optional[torch.Tensor] = None, past_key_values=None, **kwargs):
@@ -93,6 +122,20 @@ def lrqk_attention_forward(self, hidden_states: torch.Tensor,
     cache: DynamicLRQKCache = past_key_values
     input_shape = hidden_states.shape[:-1]
     hidden_shape = (*input_shape, -1, self.head_dim)
+    if hidden_states.shape[1] == 1 and cache.is_decoding(self.layer_idx):
+        # decode step: one fused projection, then one kernel that rotates q and k and hands this rank's heads
+        # to the layer step (instead of three projections and the dozen element-wise launches of the rotary op)
+        fused = _fused_qkv(self)
+        cos, sin = position_embeddings
+        state = cache.lwattn[self.layer_idx].state
+        if (fused is not None and hidden_states.dtype == fused[0].dtype == state.dtype == cos.dtype
+                and cos.shape[-1] == self.head_dim):
+            qkv = F.linear(hidden_states, fused[0], fused[1])
+            kv_heads = self.k_proj.out_features // self.head_dim
+            q_heads = self.q_proj.out_features // self.head_dim
+            attn_output = cache.attend_qkv(qkv, cos.contiguous(), sin.contiguous(), self.layer_idx, q_heads, kv_heads)
+            attn_output = attn_output.transpose(1, 2).reshape(*input_shape, -1).contiguous()
+            return self.o_proj(attn_output), None
     query_states = self.q_proj(hidden_states).view(hidden_shape).transpose(1, 2)
     key_states = self.k_proj(hidden_states).view(hidden_shape).transpose(1, 2)
     value_states = self.v_proj(hidden_states).view(hidden_shape).transpose(1, 2)

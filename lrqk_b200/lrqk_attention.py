@@ -693,6 +693,23 @@ class DynamicLRQKCache(_CacheBase):
         fac.decode_attend_push(q, k, v, exchange)
         return self.sharding.gather_step(bsz, hkv, hq).unsqueeze(2)
 
+    def attend_qkv(self, qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, layer_idx: int, q_heads: int,
+                   kv_heads: int) -> torch.Tensor:
+        """``attend`` from the fused projection of the new token: qkv [B, 1, (q_heads + 2 kv_heads) d] holds the
+        un-rotated q, k and v heads of the whole model, cos / sin [B or 1, 1, d] the position's rotary factors.
+        One kernel rotates q and k and cuts out this rank's heads; returns the rows of all heads [B,Hq,1,d]."""
+        if self.sequence_state[layer_idx] != self.State.decoding:
+            raise RuntimeError("attend_qkv() is only valid once the layer is decoding; use update() before")
+        fac, bsz = self.lwattn[layer_idx], qkv.shape[0]
+        if self.sharding is None:
+            q, k, v = fac.state.rope_qkv(qkv, cos, sin, bsz, q_heads, kv_heads)
+            return fac.decode_attend(q, k, v)
+        mine = self.sharding.shard(bsz, kv_heads)
+        q, k, v = fac.state.rope_qkv(qkv, cos, sin, bsz, q_heads, kv_heads, b0=mine.b0, kvh0=mine.h0)
+        exchange = self.sharding.exchange(q.shape[0] * q.shape[1], q.shape[-1], fac.state.dtype)
+        fac.decode_attend_push(q, k, v, exchange)
+        return self.sharding.gather_step(bsz, kv_heads, q_heads).unsqueeze(2)
+
     def close(self):
         """Free every layer's device and page-locked host memory and the exchange buffers."""
         for fac in self.lwattn.values():

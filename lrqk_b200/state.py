@@ -144,6 +144,7 @@ class LayerState:
         nb = self.lib.lrqk_flash_decode_workspace_bytes(C.byref(self.c), k + m)
         self.attn_ws = torch.zeros((max(nb, 16),), dtype=torch.uint8, device=self.device)
         self._step_args = None
+        self._qkv_in = None
 
     def _rebuild_struct(self):
         c = _lib.Layer()
@@ -232,6 +233,27 @@ class LayerState:
 
     def layer_step(self, args: _lib.StepArgs):
         _lib.check(self.lib.lrqk_layer_step(C.byref(self.c), C.byref(args), _stream()), "lrqk_layer_step")
+
+    def rope_qkv(self, qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, bsz: int, q_heads: int, kv_heads: int,
+                 b0: int = 0, kvh0: int = 0):
+        """Split the fused projection of one new token per sequence (qkv [bsz, 1, (q_heads + 2 kv_heads) d] of
+        the WHOLE model) into this state's heads -- batch entries b0.., KV heads kvh0.. -- and rotate q and k by
+        cos, sin ([bsz or 1, 1, d]).  Returns views [B,Hq,1,d], [B,Hkv,1,d], [B,Hkv,1,d] of buffers that the next
+        call overwrites."""
+        d = self.head_dim
+        if self._qkv_in is None:
+            z = dict(dtype=self.dtype, device=self.device)
+            self._qkv_in = (torch.empty((self.bsz, self.q_heads, d), **z), torch.empty((self.bsz, self.kv_heads, d), **z),
+                            torch.empty((self.bsz, self.kv_heads, d), **z))
+        self._chk(qkv, (bsz, 1, (q_heads + 2 * kv_heads) * d), "qkv")
+        rows = cos.shape[0]
+        self._chk(cos, (rows, 1, d), "cos")
+        self._chk(sin, (rows, 1, d), "sin")
+        q, k, v = self._qkv_in
+        _lib.check(self.lib.lrqk_rope_qkv(_ptr(qkv), _ptr(cos), _ptr(sin), rows, _DTYPES[self.dtype], bsz, q_heads, kv_heads,
+                                          d, b0, self.bsz, kvh0, self.kv_heads, _ptr(q), _ptr(k), _ptr(v), _stream()),
+                   "lrqk_rope_qkv")
+        return q.unsqueeze(2), k.unsqueeze(2), v.unsqueeze(2)
 
     def kv_pack_host(self, keys, values, host_row: int = 0):
         s = keys.shape[2]

@@ -164,3 +164,46 @@ def test_head_sharded_stack_on_two_gpus_matches_the_unsharded_one(tmp_path):
     mp.spawn(_sharded_rank, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     for r in range(2):
         assert (tmp_path / f"rank{r}.txt").read_text().startswith("ok"), (tmp_path / f"rank{r}.txt").read_text()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shared_position", [False, True])
+def test_rope_qkv_kernel_equals_the_eager_rotary_chain_bit_for_bit(dtype, shared_position):
+    """One launch = split of the fused projection into heads + rotate-half rotary embedding + cut-out of a
+    (batch, KV head) shard; compared with transformers' apply_rotary_pos_emb on the separate tensors."""
+    from transformers.models.llama.modeling_llama import apply_rotary_pos_emb
+    from lrqk_b200.state import LayerState
+    B, Hq, Hkv, d = 4, 8, 2, 128
+    g = torch.Generator().manual_seed(11)
+    qkv = torch.randn(B, 1, (Hq + 2 * Hkv) * d, generator=g).to(dtype).cuda()
+    rows = 1 if shared_position else B
+    ang = torch.rand(rows, 1, d // 2, generator=g) * 6.28
+    cos = torch.cat([ang.cos(), ang.cos()], -1).to(dtype).cuda()
+    sin = torch.cat([ang.sin(), ang.sin()], -1).to(dtype).cuda()
+    q, k, v = qkv.split([Hq * d, Hkv * d, Hkv * d], dim=-1)
+    q, k, v = (t.view(B, 1, -1, d).transpose(1, 2) for t in (q, k, v))
+    q_ref, k_ref = apply_rotary_pos_emb(q, k, cos, sin)
+    for b0, bc, h0, hc in ((0, B, 0, Hkv), (2, 2, 1, 1), (0, 4, 1, 1)):
+        st = LayerState(bc, hc * (Hq // Hkv), hc, d, 16, 64, 16, a_capacity=128, host_capacity=128, dtype=dtype,
+                        device="cuda", with_host=False)
+        qo, ko, vo = st.rope_qkv(qkv, cos, sin, B, Hq, Hkv, b0=b0, kvh0=h0)
+        G = Hq // Hkv
+        assert torch.equal(qo, q_ref[b0:b0 + bc, h0 * G:(h0 + hc) * G])
+        assert torch.equal(ko, k_ref[b0:b0 + bc, h0:h0 + hc])
+        assert torch.equal(vo, v[b0:b0 + bc, h0:h0 + hc])
+
+
+def test_fused_projection_shares_storage_with_the_separate_ones():
+    from lrqk_b200.hf_models import _fused_qkv
+    model = _tiny("qwen")                                     # QKV bias
+    attn = model.model.layers[0].self_attn
+    before = [p.weight.detach().clone() for p in (attn.q_proj, attn.k_proj, attn.v_proj)]
+    w, b = _fused_qkv(attn)
+    assert b is not None and w.shape[0] == sum(t.shape[0] for t in before)
+    assert attn.q_proj.weight.data_ptr() == w.data_ptr() and _fused_qkv(attn)[0] is w      # built once
+    x = torch.randn(2, 1, w.shape[1], device="cuda", dtype=w.dtype)
+    fused = torch.nn.functional.linear(x, w, b)
+    sep = torch.cat([attn.q_proj(x), attn.k_proj(x), attn.v_proj(x)], -1)
+    assert torch.allclose(fused.float(), sep.float(), atol=2e-2, rtol=2e-2)
+    for p, t in zip((attn.q_proj, attn.k_proj, attn.v_proj), before):
+        assert torch.equal(p.weight, t)
