@@ -317,6 +317,29 @@ def run_ours(args):
     misses_per_step = float(miss_acc.item()) / len(evs)
     miss_rate = misses_per_step / (w["bsz"] * hq_l * w["k"])
 
+    # ---- self-check, outside every timed region: one more step per layer state, issued stage by stage and
+    # fused from the same starting state; every output must be bit-identical and the diff status clear ----
+    from lrqk_b200 import selfcheck
+    problems = []
+    for li, fac in enumerate(facs):
+        bad = selfcheck.compare_factory_step(fac, q_all[tcur, li], k_all[tcur, li], v_all[tcur, li])
+        if bad:
+            problems.append({"rank": rank, "layer": li, "differs": bad})
+    tcur += 1
+    if exchange is not None:    # the rows the push delivered against a library all-gather of the same outputs
+        out = facs[0].decode_attend_push(q_all[tcur, 0], k_all[tcur, 0], v_all[tcur, 0], exchange)
+        rows = exchange.wait().clone()
+        ref = torch.empty_like(rows)
+        dist.all_gather_into_tensor(ref, out.reshape(-1, w["d"]).contiguous())
+        torch.cuda.synchronize()
+        if not torch.equal(rows, ref):
+            problems.append({"rank": rank, "exchange": "pushed rows differ from all_gather_into_tensor"})
+        tcur += 1
+    if world > 1:
+        everyone = [None] * world
+        dist.all_gather_object(everyone, problems)
+        problems = [p for ps in everyone for p in ps]
+
     # max over ranks
     vals = torch.tensor([ms_dev, ms_e2e], dtype=torch.float64, device=device)
     if world > 1:
@@ -376,6 +399,7 @@ def run_ours(args):
         "gpu_launches": int(args.steps * layers * (5 + (1 if exchange is not None else 0)) + layers * (args.steps // w["m"])),
         "roofline": roof, "roofline_hbm": roof_hbm, "roofline_step": roof_step, "kernels": per_kernel,
         "host_link_peak_gbs": round(link_peak, 1), "clocks": clocks,
+        "selfcheck": "ok" if not problems else problems,
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline_from_state(facs[0], w, q_all, k_all, v_all, tcur, n_steps=5)
