@@ -6,10 +6,11 @@
   the GPU at once.
 * ``FullOffloadCache``                    -- lrqk_attention.py:1973-2026: the "keep everything on the
   host, bring everything back every step" baseline of the reference's throughput table.
-* ``WrapForwardTimer``                    -- lrqk_attention.py:2031-2105: wall-clock prompt / decode
-  tokens per second around a model's ``forward``.
+* ``WrapForwardTimer``                    -- lrqk_attention.py:2031-2105: prompt / decode tokens per
+  second around a model's ``forward`` (CUDA events here, wall clock there).
 * ``HitRateCounter``                      -- wikitext_hitrate.py:36-51: a factory that records the miss
-  rate of every step through the overridable ``only_indices_in_cpu`` hook.
+  rate of every step (from the device-side miss counts of the fused step here, through an
+  ``only_indices_in_cpu`` override there; that override hook keeps working too).
 * ``tps_estimate`` / ``run_task``         -- tps_estimate.py:41-142: the throughput driver; prompts are
   synthetic token ids of the requested lengths (the reference reads RULER prompts from disk).
 
@@ -19,15 +20,12 @@ set-up / baseline traffic, not part of the per-step selection path.
 from __future__ import annotations
 
 import json
-import time
-from collections import defaultdict
 from typing import Callable, Dict, Optional
 
-import numpy as np
 import torch
 
-from .lrqk_attention import (AutoIncreaseTensorSharedKV, DynamicLRQKCache, LightAttentionIndicesFactory,
-                             LightAttentionIndicesNoHitMiss, _CacheBase)
+from .lrqk_attention import (DynamicLRQKCache, LightAttentionIndicesFactory, LightAttentionIndicesNoHitMiss,
+                             _CacheBase)
 
 
 class LightAttentionIndicesOffloadPrefill(LightAttentionIndicesFactory):
@@ -66,125 +64,211 @@ class LightAttentionIndicesOffloadPrefill(LightAttentionIndicesFactory):
         return super()._decode(*args, **kwargs)
 
 
-class FullOffloadCache(_CacheBase):
-    """Every layer's K|V lives in page-locked host memory; ``update`` appends the new rows and returns
-    the whole K and V on the device (lrqk_attention.py:1973-2026)."""
+class _HostKV:
+    """K and V of one layer in two page-locked host buffers [B, Hkv, capacity, d], grown by half when full."""
 
-    def __init__(self) -> None:
+    def __init__(self, like: torch.Tensor, first_rows: int, capacity: int):
+        b, h, _, d = like.shape
+        self.rows = 0
+        self.capacity = max(capacity, first_rows + first_rows // 2)
+        self.k = torch.empty((b, h, self.capacity, d), dtype=like.dtype, pin_memory=True)
+        self.v = torch.empty_like(self.k, pin_memory=True)
+
+    def reserve(self, rows: int):
+        if rows <= self.capacity:
+            return
+        torch.cuda.current_stream().synchronize()          # earlier copies out of the old buffers must be done
+        cap = self.capacity
+        while cap < rows:
+            cap += cap // 2 + 1
+        for name in ("k", "v"):
+            old = getattr(self, name)
+            new = torch.empty(old.shape[:2] + (cap, old.shape[3]), dtype=old.dtype, pin_memory=True)
+            new[:, :, :self.rows].copy_(old[:, :, :self.rows])
+            setattr(self, name, new)
+        self.capacity = cap
+
+
+class FullOffloadCache(_CacheBase):
+    """The "everything on the host" row of the reference's throughput table (lrqk_attention.py:1973-2026):
+    no K/V row stays on the GPU between calls.  ``update(key_states, value_states, layer_idx)`` stores the
+    new rows in the layer's page-locked host buffers and returns ALL rows of that layer on the device.
+
+    The device side is one staging pair shared by every layer, as large as the longest layer so far: the
+    tensors ``update`` returns are views of it and stay valid until the next ``update`` call (the copies
+    and the attention that reads them are ordered on the current stream)."""
+
+    def __init__(self, capacity: int = 4096) -> None:
         if not torch.cuda.is_available():
-            raise RuntimeError("OffloadedCache can only be used with a GPU")
+            raise RuntimeError("FullOffloadCache stages through a CUDA device; none is available")
         if _CacheBase is not object:
             try:
                 super().__init__(layers=[])
             except TypeError:
                 super().__init__()
-        self.KVcpu = defaultdict(lambda: AutoIncreaseTensorSharedKV(capacity=4096, dim=2, device="cpu", pin_memory=True))
+        self._capacity = capacity
+        self._layers: Dict[int, _HostKV] = {}
+        self._stage_k: Optional[torch.Tensor] = None
+        self._stage_v: Optional[torch.Tensor] = None
 
     def __len__(self):
-        return len(self.KVcpu)
+        return len(self._layers)
 
     def get_seq_length(self, layer_idx=0):
-        return len(self.KVcpu[layer_idx])
+        lay = self._layers.get(layer_idx)
+        return 0 if lay is None else lay.rows
 
     def get_max_cache_shape(self, *a, **kw) -> Optional[int]:
         return None
 
     def get_mask_sizes(self, query_length, layer_idx: int = 0):
-        """(kv_length, kv_offset) for the mask builder of transformers 5.x: everything cached so far plus the new tokens."""
+        """(kv_length, kv_offset) for the mask builder of transformers 5.x: every stored row plus the new tokens."""
         q = int(query_length.shape[0]) if hasattr(query_length, "shape") else int(query_length)
         return self.get_seq_length(layer_idx) + q, 0
 
+    def _staging(self, like: torch.Tensor, rows: int):
+        s = self._stage_k
+        if s is None or s.shape[2] < rows or s.shape[:2] != like.shape[:2] or s.dtype != like.dtype:
+            cap = max(rows + rows // 2, self._capacity)
+            shape = like.shape[:2] + (cap, like.shape[3])
+            self._stage_k = torch.empty(shape, dtype=like.dtype, device=like.device)
+            self._stage_v = torch.empty(shape, dtype=like.dtype, device=like.device)
+        return self._stage_k, self._stage_v
+
+    @torch.no_grad()
     def update(self, key_states: torch.Tensor, value_states: torch.Tensor, layer_idx: int, *args, **kwargs):
-        kv = self.KVcpu[layer_idx]
-        kv.append(key_states, value_states)
-        hdim = key_states.shape[-1]
-        full = kv.tensor()
-        return (full.narrow(3, 0, hdim).to(key_states.device), full.narrow(3, hdim, hdim).to(value_states.device))
+        new_rows = key_states.shape[2]
+        lay = self._layers.get(layer_idx)
+        if lay is None:
+            lay = self._layers[layer_idx] = _HostKV(key_states, new_rows, self._capacity)
+        total = lay.rows + new_rows
+        lay.reserve(total)
+        dk, dv = self._staging(key_states, total)
+        # the layer's stored rows come up from the host, the new rows are appended on both sides
+        if lay.rows:
+            dk[:, :, :lay.rows].copy_(lay.k[:, :, :lay.rows], non_blocking=True)
+            dv[:, :, :lay.rows].copy_(lay.v[:, :, :lay.rows], non_blocking=True)
+        dk[:, :, lay.rows:total].copy_(key_states)
+        dv[:, :, lay.rows:total].copy_(value_states)
+        lay.k[:, :, lay.rows:total].copy_(key_states, non_blocking=True)
+        lay.v[:, :, lay.rows:total].copy_(value_states, non_blocking=True)
+        lay.rows = total
+        return dk[:, :, :total], dv[:, :, :total]
 
 
 class WrapForwardTimer:
-    """Wall-clock timer around ``module.forward``: the first call is the prompt pass, every later
-    call one decode step (lrqk_attention.py:2031-2105)."""
+    """Prompt and decode throughput of a model, from CUDA events recorded around its ``forward``.
+
+    Same use as the reference's timer (lrqk_attention.py:2031-2105): ``timer, model = WrapForwardTimer.wrap(model)``;
+    the first timed call after ``wrap`` / ``reset`` is the prompt pass, every later call one decode step;
+    ``prefill_tps()`` is prompt tokens per second, ``decode_tps()`` decode steps per second; ``remove_wrapper()``
+    restores the model.  The times are device times: an event before and after each call on the current
+    stream, no synchronisation inside the timed loop.  Decode time is the span from the first decode call's
+    start to the last one's end, so host-side gaps between the steps (sampling, launch overhead) count too."""
 
     def __init__(self, module: torch.nn.Module):
         self.module = module
-        self.prefill_begin = None
-        self.prefill_end = None
-        self.decode_begin = None
-        self.decode_time_list = []
         self.seq_len = 0
-        self.original_method = None
+        self._prompt = None            # (begin, end) events of the prompt pass
+        self._decode = []              # (begin, end) events of every decode step
+        self._inner = None
+        self._shadowed = None
 
-    def prefill_tps(self):
-        """Prefill token per second"""
-        if self.prefill_begin is None:
+    # -- results ------------------------------------------------------------------------------
+    @staticmethod
+    def _seconds(begin, end) -> float:
+        end.synchronize()
+        return begin.elapsed_time(end) * 1e-3
+
+    def prefill_tps(self) -> float:
+        if self._prompt is None:
             return 0.0
-        return self.seq_len / (self.prefill_end - self.prefill_begin)
+        return self.seq_len / self._seconds(*self._prompt)
 
-    def decode_tps(self):
-        """Decode token per second"""
-        if len(self.decode_time_list) == 0:
+    def decode_tps(self) -> float:
+        if not self._decode:
             return 0.0
-        return len(self.decode_time_list) / sum(self.decode_time_list)
+        return len(self._decode) / self._seconds(self._decode[0][0], self._decode[-1][1])
 
-    def remove_wrapper(self):
-        setattr(self.module, "forward", self.original_method)
-        del self.original_method
-        setattr(self.module, "manual_time_wrapped", False)
+    @property
+    def decode_time_list(self):
+        """Seconds of each decode step (device time inside the call)."""
+        return [self._seconds(b, e) for b, e in self._decode]
 
     def reset(self):
-        self.prefill_begin = None
-        self.prefill_end = None
-        self.decode_begin = None
-        self.decode_time_list.clear()
-        self.seq_len = 0
+        self.seq_len, self._prompt = 0, None
+        self._decode.clear()
+
+    # -- installation -------------------------------------------------------------------------
+    def _timed(self, *args, **kwargs):
+        first = self._prompt is None
+        if first:
+            ids = kwargs.get("input_ids")
+            if ids is None:
+                raise ValueError("the timed forward takes input_ids as a keyword argument")
+            self.seq_len = ids.shape[1]
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        result = self._inner(*args, **kwargs)
+        end.record()
+        if first:
+            self._prompt = (begin, end)
+        else:
+            self._decode.append((begin, end))
+        return result
 
     @classmethod
     def wrap(cls, module: torch.nn.Module):
-        wraper = cls(module)
-        if getattr(module, "manual_time_wrapped", False):
-            return wraper, wraper.module
-        original_method = getattr(module, "forward")
-        wraper.original_method = original_method
-        setattr(wraper.module, "manual_time_wrapped", True)
+        timer = getattr(module, "_lrqk_forward_timer", None)
+        if timer is None:
+            timer = cls(module)
+            timer._shadowed = module.__dict__.get("forward")      # an instance-level forward, if one was set
+            timer._inner = module.forward
+            module.forward = timer._timed
+            module._lrqk_forward_timer = timer
+        return timer, module
 
-        def __new_method(self, *args, **kwargs):
-            if wraper.prefill_begin is None:
-                input_ids = kwargs.get("input_ids", None)
-                if input_ids is None:
-                    raise ValueError("input_ids is None")
-                wraper.seq_len = input_ids.shape[1]
-                wraper.prefill_begin = time.time()
+    def remove_wrapper(self):
+        if self._inner is not None:
+            if self._shadowed is not None:
+                self.module.forward = self._shadowed
             else:
-                wraper.decode_begin = time.time()
-            result = original_method(*args, **kwargs)
-            torch.cuda.synchronize()   # the step's work is asynchronous here: wait for it before reading the clock
-            if wraper.prefill_end is None:
-                wraper.prefill_end = time.time()
-            else:
-                wraper.decode_time_list.append(time.time() - wraper.decode_begin)
-            return result
-
-        setattr(wraper.module, "forward", __new_method.__get__(wraper.module))
-        return wraper, wraper.module
+                del self.module.__dict__["forward"]               # the class's own forward shows again
+            self._inner = None
+            del self.module._lrqk_forward_timer
 
 
 class HitRateCounter(LightAttentionIndicesFactory):
-    """Records the miss rate of every decode step (wikitext_hitrate.py:36-51).  Overriding
-    ``only_indices_in_cpu`` switches the object to the stage-by-stage path with int64 tensors of the
-    reference's shapes."""
+    """A factory that logs the miss rate of every selecting decode step (what the reference's
+    ``wikitext_hitrate.py:36-51`` collects by overriding ``only_indices_in_cpu``).
+
+    Here the step's hit/miss difference already leaves a per-head miss count on the device, so the
+    counter keeps the fused step and appends ``sum(miss_count) / (heads * attn_topk)`` to a device-side
+    log after each step, without a host synchronisation; ``miss_rates`` copies the log to the host."""
 
     def __init__(self, *args, **kwargs):
         super().__init__(*args, **kwargs)
-        self.miss_rates = []
+        self._log: Optional[torch.Tensor] = None
+        self._logged = 0
 
-    def only_indices_in_cpu(self, now_indices: torch.Tensor, new_indices: torch.Tensor):
-        updated_indices, now_in_new = super().only_indices_in_cpu(now_indices, new_indices)
-        self.miss_rates.append((torch.sum(now_in_new) / now_in_new.numel()).item())   # 1 = miss: loaded from the host
-        return updated_indices, now_in_new
+    def _decode(self, *args, **kwargs):
+        st = super()._decode(*args, **kwargs)
+        if self.current_len > self.gpu_capacity:            # a step that ran the difference (:1571-1573)
+            if self._log is None or self._logged == self._log.numel():
+                grown = torch.zeros(max(256, 2 * self._logged), dtype=torch.float32, device=st.device)
+                if self._log is not None:
+                    grown[:self._logged].copy_(self._log)
+                self._log = grown
+            self._log[self._logged] = st.miss_count.sum() / float(st.miss_count.numel() * st.k)
+            self._logged += 1
+        return st
 
-    def average_miss_rate(self):
-        return float(np.mean(self.miss_rates))
+    @property
+    def miss_rates(self):
+        return [] if self._log is None else self._log[:self._logged].tolist()
+
+    def average_miss_rate(self) -> float:
+        return float(self._log[:self._logged].mean()) if self._logged else float("nan")
 
 
 task_dict = {

@@ -247,7 +247,16 @@ class LightAttentionIndicesFactory:
     what the patched attention modules use.
 
     ``weights`` other than all-ones is not supported (the reference's cache never passes it,
-    lrqk_attention.py:1811-1820).  Prompts must be longer than ``attn_topk + num_lite_tokens``.
+    lrqk_attention.py:1811-1820).
+
+    Prompts of ``attn_topk .. attn_topk + num_lite_tokens`` rows take the reference's short branch
+    (:1444-1466): every prompt row stays resident (slot = position), nothing is selected, and decode
+    steps project against all earlier rows (:1526-1545) until the context outgrows the resident rows.
+    The same kernels serve it: lite slots that hold no token yet point at a row of ``A_K`` that is
+    still zero, so they add nothing to any sum.  A prompt of exactly ``attn_topk + num_lite_tokens``
+    rows makes the reference fail at its first decode step (its ring write lands one slot past the
+    ring); here the full ring is flushed to the host store at once, as a decode step that fills it
+    would (:1192-1196).
     """
 
     def __init__(self, num_lite_tokens: int = 1, attn_topk: int = 128, num_key_value_groups: int = 1,
@@ -274,6 +283,7 @@ class LightAttentionIndicesFactory:
         self.device, self.dtype = device, dtype
         self.lite_len = 0
         self.lite_indices: List[int] = [-1] * num_lite_tokens
+        self.resident_rows = self.gpu_capacity           # rows of Kgpu/Vgpu the last decode step attended to
         self.state: Optional[LayerState] = None
         self.verbose = False
         self._hook = type(self).only_indices_in_cpu is not LightAttentionIndicesFactory.only_indices_in_cpu
@@ -393,11 +403,11 @@ class LightAttentionIndicesFactory:
         assert seq_len >= self.attn_topk, "seq_len must be larger than attn_topk"
         if hq != hkv * self.num_key_value_groups:
             raise ValueError("num_key_value_groups does not match the head counts of q and k")
-        if seq_len <= self.gpu_capacity + 1:
-            raise NotImplementedError("prompts not longer than attn_topk + num_lite_tokens + 1 are not supported")
         q = query_states.contiguous()
         k = key_states.contiguous()
         v = value_states.contiguous()
+        if seq_len <= self.gpu_capacity:
+            return self._prefill_short(q, k, v)
         st = self.state = self._new_state(bsz, hq, hkv, d, seq_len, q.dtype, q.device)
         self.prefill_length = self.current_len = seq_len
         # the prompt's K|V rows go to the page-locked host store on a second stream: that copy is bound
@@ -408,13 +418,7 @@ class LightAttentionIndicesFactory:
             st.kv_pack_host(k, v, 0)
         k.record_stream(side)
         v.record_stream(side)
-        aq, ak = self._initial_factors(q, k)
-        nb = st.lib.lrqk_prefill_factorize_workspace_bytes(C.byref(st.c), seq_len)
-        ws = torch.empty((max(nb, 16),), dtype=torch.uint8, device=q.device)
-        a_q_last = torch.empty((bsz, hq, self.r), dtype=q.dtype, device=q.device)
-        _lib.check(st.lib.lrqk_prefill_factorize(C.byref(st.c), _ptr(q), _ptr(k), _ptr(aq), _ptr(ak), seq_len,
-                                                 self.max_iter[0], self.tol[0], _ptr(a_q_last), None, _ptr(ws),
-                                                 _stream()), "lrqk_prefill_factorize")
+        a_q_last = self._factorize(st, q, k, seq_len)
         st.host.current_len = seq_len
         st.score_topk(a_q_last, seq_len - self.num_lite_tokens)       # candidates 0 .. S-m-1, :1471-1474
         st.table.copy_(st.wanted)
@@ -422,7 +426,49 @@ class LightAttentionIndicesFactory:
         self.lite_indices = list(range(seq_len - self.num_lite_tokens, seq_len))
         self.lite_len = 0
         main.wait_stream(side)                                         # the host store is complete from here on
-        del aq, ak, ws
+
+    def _factorize(self, st: LayerState, q, k, seq_len: int) -> torch.Tensor:
+        """Prompt factorisation into st.A_K[:seq_len], st.B_Q, st.B_K; returns the last row of A_Q."""
+        aq, ak = self._initial_factors(q, k)
+        nb = st.lib.lrqk_prefill_factorize_workspace_bytes(C.byref(st.c), seq_len)
+        ws = torch.empty((max(nb, 16),), dtype=torch.uint8, device=q.device)
+        a_q_last = torch.empty((q.shape[0], q.shape[1], self.r), dtype=q.dtype, device=q.device)
+        _lib.check(st.lib.lrqk_prefill_factorize(C.byref(st.c), _ptr(q), _ptr(k), _ptr(aq), _ptr(ak), seq_len,
+                                                 self.max_iter[0], self.tol[0], _ptr(a_q_last), None, _ptr(ws),
+                                                 _stream()), "lrqk_prefill_factorize")
+        return a_q_last
+
+    def _prefill_short(self, q, k, v):
+        """attn_topk <= seq_len <= attn_topk + num_lite_tokens (lrqk_attention.py:1444-1466): the first
+        attn_topk rows go to the host store, ALL rows stay resident in position order, the slot table
+        is 0..attn_topk-1 and the remaining rows are the first entries of the lite ring."""
+        bsz, hq, seq_len, d = q.shape
+        hkv, kk, m, g = k.shape[1], self.attn_topk, self.num_lite_tokens, self.num_key_value_groups
+        # host capacity follows the rows it is first given (:880): the first attn_topk rows
+        cap_a = max(self.capacity, int(seq_len * self.scaling_ratio), self.gpu_capacity + 2)
+        cap_h = max(self.capacity, int(kk * self.scaling_ratio), self.gpu_capacity + 2)
+        st = self.state = LayerState(bsz, hq, hkv, d, self.r, kk, m, a_capacity=cap_a, host_capacity=cap_h,
+                                     dtype=q.dtype, device=q.device, max_iter=self.max_iter[1], zero_host=True)
+        self.prefill_length = self.current_len = seq_len
+        self._factorize(st, q, k, seq_len)
+        st.kv_pack_host(k[:, :, :kk].contiguous(), v[:, :, :kk].contiguous(), 0)
+        st.host.current_len = kk
+        st.K_res[:, :, :seq_len].copy_(repeat_kv(k, g))
+        st.V_res[:, :, :seq_len].copy_(repeat_kv(v, g))
+        st.table.copy_(torch.arange(kk, dtype=torch.int32, device=q.device).expand(bsz, hq, kk))
+        rem = seq_len - kk
+        self.lite_len = rem
+        self.lite_indices = list(range(kk, kk + rem)) + [-1] * (m - rem)
+        # device copy of the ring positions: an empty slot points at row attn_topk + num_lite_tokens of
+        # A_K, which stays zero until every slot has been filled (that position is appended last)
+        st.lite_pos.copy_(torch.tensor([p if p >= 0 else self.gpu_capacity for p in self.lite_indices],
+                                       dtype=torch.int32))
+        if rem >= m:      # full ring: flush it now (the reference fails here, see the class docstring)
+            ring = torch.cat([st.K_res[:, ::g, kk:kk + m], st.V_res[:, ::g, kk:kk + m]], dim=-1)
+            torch.cuda.current_stream().synchronize()
+            st.host.data[:, :, kk:kk + m].copy_(ring)
+            st.host.current_len = kk + m
+            self.lite_len = 0
 
     def load_state(self, *, A_K, B_Q, B_K, keys, values, table, dtype=None):
         """Adopt factors and a first resident set produced elsewhere (same layout as after
@@ -494,13 +540,24 @@ class LightAttentionIndicesFactory:
         st = self.state
         if st is None:
             raise RuntimeError("decode before prefill")
-        if self.current_len <= self.gpu_capacity:
-            raise NotImplementedError("decode with fewer tokens than resident slots is not supported")
         self._reserve()
         q = self._flat(query_states.to(st.dtype), st.q_heads)
         k = self._flat(key_states.to(st.dtype), st.kv_heads)
         v = self._flat(value_states.to(st.dtype), st.kv_heads)
         slot, position, flush_rows, host_row, candidates = self._step_counters()
+        self.resident_rows = self.gpu_capacity
+        if self.current_len <= self.gpu_capacity or candidates <= self.attn_topk:
+            # Every token is still resident (lrqk_attention.py:1526-1545), or the context has just outgrown
+            # the resident rows and there are no more candidates than slots yet (:1247-1255): ring write and
+            # projection only, nothing to select or fetch.  Empty ring slots are zero rows (see prefill).
+            st.lite_append(k, v, slot, position, flush_rows, host_row)
+            st.project_update(q, k, self.max_iter[1], self.tol[1], position)
+            st.mask.zero_()
+            st.miss_count.zero_()
+            self.resident_rows = min(self.current_len, self.gpu_capacity)
+            if attention:
+                st.flash_decode(q, rows=self.resident_rows, exchange=exchange)
+            return st
         if not self._hook:
             args = st.make_step_args(q, k, v, slot, position, flush_rows, host_row, candidates,
                                      self.max_iter[1], self.tol[1], attention=attention)
@@ -534,6 +591,8 @@ class LightAttentionIndicesFactory:
     def decode(self, query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor):
         """One step; returns the resident (K, V) [B,Hq,k+m,d] (lrqk_attention.py:1506-1613)."""
         st = self._decode(query_states, key_states, value_states, attention=False)
+        if self.resident_rows < self.gpu_capacity:           # short prompt: the filled rows only, :1541-1544
+            return st.K_res.narrow(2, 0, self.resident_rows), st.V_res.narrow(2, 0, self.resident_rows)
         return st.K_res, st.V_res
 
     def decode_attend(self, query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor,

@@ -204,10 +204,17 @@ class LayerState:
         _lib.check(self.lib.lrqk_miss_gather(C.byref(self.c), _ptr(self.miss_list), _ptr(self.counters), _stream()),
                    "lrqk_miss_gather")
 
-    def flash_decode(self, q, rows: Optional[int] = None, scale: Optional[float] = None):
+    def flash_decode(self, q, rows: Optional[int] = None, scale: Optional[float] = None, exchange=None):
+        """Attention over the first `rows` resident rows; with `exchange` (a sharding.HeadExchange) the
+        kernel's epilogue also stores the rows into every rank's exchange buffer."""
         self._chk(q, (self.bsz, self.q_heads, self.head_dim), "q")
         rows = self.k + self.m if rows is None else rows
         scale = self.head_dim ** -0.5 if scale is None else scale
+        if exchange is not None:
+            _lib.check(self.lib.lrqk_flash_decode_push(C.byref(self.c), _ptr(q), _ptr(self.attn_out), rows, scale,
+                                                       _ptr(self.attn_ws), C.byref(exchange.c), exchange.seq.next_push(),
+                                                       _stream()), "lrqk_flash_decode_push")
+            return self.attn_out
         _lib.check(self.lib.lrqk_flash_decode(C.byref(self.c), _ptr(q), _ptr(self.attn_out), rows, scale,
                                               _ptr(self.attn_ws), _stream()), "lrqk_flash_decode")
         return self.attn_out

@@ -426,7 +426,12 @@ class StepTrace:
 
 class OracleLayer:
     """State machine of one layer: mirrors LightAttentionIndicesFactory
-    (lrqk_attention.py:1031-1613) for prompts longer than k + m.
+    (lrqk_attention.py:1031-1613), both prompt branches: longer than k + m (:1467-1504) and
+    k <= length <= k + m (:1444-1466, every prompt row resident, no selection until the
+    context outgrows the resident rows).  A prompt of exactly k + m rows makes the reference
+    itself fail at its first decode step (the ring write lands one slot past the ring); here the
+    full ring is flushed to the host store at once, which is what :1192-1196 does when a decode
+    step fills it.
 
     `faithful=True` evaluates selection and difference with the reference's own op
     sequence (torch.topk / broadcast compare); `faithful=False` uses the pinned tie
@@ -461,10 +466,10 @@ class OracleLayer:
             return grown
         return buf
 
-    # -- prefill: lrqk_attention.py:1385-1504 (branch seq_len > k + m) --
+    # -- prefill: lrqk_attention.py:1385-1504 --
     def prefill(self, Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, init_factors_override=None):
         b, hq, s, d = Q.shape
-        assert s > self.k + self.m, "oracle covers the long-prompt branch only"
+        assert s >= self.k, "seq_len must be larger than attn_topk"       # :1411
         Krep = expand_kv_heads(K, self.groups)
         self.Kres = torch.zeros((b, hq, self.k + self.m, d), dtype=Q.dtype)
         self.Vres = torch.zeros_like(self.Kres)
@@ -476,10 +481,26 @@ class OracleLayer:
         self.A_K = torch.zeros((b, hq, cap, self.r), dtype=A_K.dtype)
         self.A_K[:, :, :s] = A_K
         self.a_len = s
+        self.A_Q_last = A_Q[:, :, -1:, :]
+        if s <= self.k + self.m:                                         # :1444-1466
+            kk, rem = self.k, s - self.k
+            hcap = self._first_capacity(kk)
+            self.host = torch.zeros((b, K.shape[1], hcap, 2 * d), dtype=K.dtype)
+            self.host[:, :, :kk] = torch.cat([K[:, :, :kk], V[:, :, :kk]], dim=-1)
+            self.host_len = kk
+            self.lite_len = rem
+            self.lite_indices = list(range(kk, kk + rem)) + [-1] * (self.m - rem)
+            self.Kres[:, :, :s] = Krep
+            self.Vres[:, :, :s] = expand_kv_heads(V, self.groups)
+            self.table = np.broadcast_to(np.arange(kk, dtype=np.int32), (b, hq, kk)).copy()
+            if rem >= self.m:                                            # see the class docstring
+                g = self.groups
+                self._host_append(torch.cat([self.Kres[:, ::g, kk:kk + self.m], self.Vres[:, ::g, kk:kk + self.m]], dim=-1))
+                self.lite_len = 0
+            return self
         self.host = torch.zeros((b, K.shape[1], cap, 2 * d), dtype=K.dtype)
         self.host[:, :, :s] = torch.cat([K, V], dim=-1)                  # :962, :1469
         self.host_len = s
-        self.A_Q_last = A_Q[:, :, -1:, :]
         cand = s - self.m                                                # :1473
         wanted = self._select(A_K[:, :, :cand], self.A_Q_last)
         self.table = wanted.copy()
@@ -519,6 +540,22 @@ class OracleLayer:
             ring = torch.cat([self.Kres[:, ::g, kk:kk + m], self.Vres[:, ::g, kk:kk + m]], dim=-1)
             self._host_append(ring)
             self.lite_len = 0
+        if self.current_len <= kk + m:                                   # :1526-1545
+            # every token is still resident: project against all earlier rows, no selection
+            n = self.current_len - 1
+            B_Q, B_K, q_hat, k_hat = cast_decode(self.B_Q, self.A_K[:, :, :self.a_len], self.B_K, self.Kres[:, :, :n],
+                                                 q, expand_kv_heads(k, g), self.max_iter[1], self.tol[1])
+            self.B_Q, self.B_K = B_Q, B_K
+            self.A_K = self._ensure(self.A_K, self.a_len, 1)
+            self.A_K[:, :, self.a_len:self.a_len + 1] = k_hat
+            self.a_len += 1
+            tr.q_hat, tr.k_hat, tr.candidates = q_hat, k_hat, -1
+            tr.table = self.table
+            Kv, Vv = self.Kres[:, :, :self.current_len], self.Vres[:, :, :self.current_len]
+            if want_attention:
+                tr.attn = attention(q, Kv, Vv)
+            self.trace.append(tr)
+            return Kv, Vv
         # rank-r rows of the active set out of the zero-initialised store, :1156-1171
         act = np.concatenate([self.table, np.broadcast_to(np.asarray(self.lite_indices, dtype=np.int32),
                                                           self.table.shape[:2] + (m,))], axis=-1)
@@ -534,7 +571,10 @@ class OracleLayer:
         # candidates, selection, difference, :1562-1573
         cand = self.lite_indices[self.lite_len] - 1
         tr.candidates = cand
-        wanted = self._select(self.A_K[:, :, :cand], q_hat)
+        if cand <= kk:                                                   # :1247-1255: nothing to choose from yet
+            wanted = np.broadcast_to(np.arange(cand, dtype=np.int32), self.table.shape[:2] + (cand,)).copy()
+        else:
+            wanted = self._select(self.A_K[:, :, :cand], q_hat)
         if self.faithful:
             upd, msk = slot_diff_reference_ops(torch.from_numpy(self.table.astype(np.int64))[..., None],
                                                torch.from_numpy(wanted.astype(np.int64))[..., None])

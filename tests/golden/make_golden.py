@@ -49,6 +49,14 @@ CASES = {
     # shared-column init, single iteration, group size 1.
     "topcol_g1": dict(seed=31, init_seed=6, bsz=1, hq=2, hkv=2, seq=512, d=128, r=16, k=32, m=8,
                       max_iter=(1, 1), tol=1e-2, init="topcol", steps=9),
+    # prompt only a little longer than the resident set (k <= seq <= k + m, lrqk_attention.py:1444-1466):
+    # steps 0-4 run the all-resident branch (:1526-1545), step 4 flushes the ring, steps 5.. select again.
+    "short_k3": dict(seed=41, init_seed=8, bsz=2, hq=4, hkv=2, seq=67, d=128, r=8, k=64, m=8,
+                     max_iter=(2, 2), tol=1e-2, init="top", steps=16),
+    # prompt of exactly k rows: what DynamicLRQKCache hands over when a collected short prompt reaches
+    # num_active_tokens (:1928-1958).
+    "short_exact_k": dict(seed=43, init_seed=9, bsz=1, hq=4, hkv=1, seq=32, d=128, r=8, k=32, m=4,
+                          max_iter=(2, 2), tol=1e-2, init="randn", steps=10),
 }
 
 
@@ -120,9 +128,12 @@ def run_case(ref, name: str, c: dict) -> dict:
     for s in range(c["steps"]):
         q, k, v = orc.make_step(c["seed"], s, c["bsz"], c["hq"], c["hkv"], c["d"])
         a_len_before = len(f._A_K)
+        captured.clear()
         Kres, Vres = f.decode(q.clone(), k.clone(), v.clone())
         out[f"s{s}_k_hat"] = f._A_K.data[:, :, a_len_before:a_len_before + 1].numpy().copy()
-        out[f"s{s}_wanted"] = captured["wanted"][..., 0].numpy().astype(np.int32)
+        if "wanted" in captured:        # the all-resident branch of a short prompt selects nothing
+            out[f"s{s}_wanted"] = captured["wanted"][..., 0].numpy().astype(np.int32)
+        out[f"s{s}_rows"] = np.array(Kres.shape[2])
         out[f"s{s}_table"] = f.hit_indices[..., 0].numpy().astype(np.int32)
         out[f"s{s}_B_Q_sha256"] = np.array(sha(f.B_Q))
         out[f"s{s}_lite"] = np.array(f.lite_indices + [f.lite_len, f.current_len, len(f.KVcpu)], dtype=np.int64)

@@ -211,3 +211,144 @@ def test_dynamic_cache_state_machine():
     with pytest.raises(RuntimeError):
         cache.attend(q.cuda(), k.cuda(), v.cuda(), 1)
     cache.lwattn[0].close()
+
+
+# --------------------------------------------------------------------------------------------
+# short prompts: attn_topk <= length <= attn_topk + num_lite_tokens (lrqk_attention.py:1444-1466, :1526-1545)
+# --------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", ["short_k3", "short_exact_k"])
+def test_short_prompt_factory_matches_oracle_and_reference_trace(name):
+    """The factory on a prompt barely longer than the resident set: the all-resident steps, the ring
+    flush, the steps with no more candidates than slots, then selecting steps -- against the oracle
+    step by step (the oracle adopts the device's factors after each step so that round-off cannot
+    cascade into the selection) and against the trace recorded from the reference."""
+    import json
+    import os
+    from lrqk_b200 import LightAttentionIndicesFactory
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", f"{name}.npz"))
+    c = json.loads(str(z["config"]))
+    grp = c["hq"] // c["hkv"]
+    Q, K, V = orc.make_prompt(c["seed"], c["bsz"], c["hq"], c["hkv"], c["seq"], c["d"])
+    lay = orc.OracleLayer(c["r"], c["k"], c["m"], grp, c["max_iter"], c["tol"], capacity=c["seq"] + 64, init="top")
+    lay.prefill(Q, K, V)
+    fac = LightAttentionIndicesFactory(num_lite_tokens=c["m"], attn_topk=c["k"], num_key_value_groups=grp, r=c["r"],
+                                       max_iter=c["max_iter"], tol=c["tol"], capacity=c["seq"] + 64,
+                                       init_aq_ak_method="top")
+    fac.prefill(Q.cuda(), K.cuda(), V.cuda())
+    st = fac.state
+    assert fac.lite_len == lay.lite_len and fac.lite_indices == lay.lite_indices and len(fac) == c["seq"]
+    assert st.host.capacity == int(z["host_capacity"]) and st.host.current_len == lay.host_len
+    assert np.array_equal(st.table.cpu().numpy(), lay.table)
+    assert torch.equal(st.K_res.cpu(), lay.Kres) and torch.equal(st.V_res.cpu(), lay.Vres)
+    assert torch.equal(st.host.data[:, :, :lay.host_len], lay.host[:, :, :lay.host_len])
+    assert _rel(st.B_Q.cpu(), lay.B_Q) < 2e-3 and _rel(st.A_K[:, :, :c["seq"]].cpu(), lay.A_K[:, :, :c["seq"]]) < 2e-3
+    # both sides continue from the device's factors
+    lay.B_Q, lay.B_K = st.B_Q.cpu().clone(), st.B_K.cpu().clone()
+    lay.A_K[:, :, :c["seq"]] = st.A_K[:, :, :c["seq"]].cpu()
+    saw = set()
+    for s in range(c["steps"]):
+        q, k, v = orc.make_step(c["seed"], s, c["bsz"], c["hq"], c["hkv"], c["d"])
+        out = fac.decode_attend(q.cuda(), k.cuda(), v.cuda()).clone()
+        torch.cuda.synchronize()
+        table_before = lay.table.copy()
+        Kv, Vv = lay.decode(q, k, v)
+        tr = lay.trace[-1]
+        rows = Kv.shape[2]
+        assert rows == int(z[f"s{s}_rows"]) == fac.resident_rows
+        lite = z[f"s{s}_lite"]
+        assert fac.lite_indices == list(lite[:c["m"]]) and (fac.lite_len, len(fac), st.host.current_len) == tuple(int(x) for x in lite[-3:])
+        assert _rel(st.A_K[:, :, lay.a_len - 1].cpu(), tr.k_hat[:, :, 0]) < 5e-4
+        assert _rel(st.q_hat.cpu(), tr.q_hat[:, :, 0]) < 5e-4
+        if tr.candidates > c["k"]:
+            saw.add("selecting")
+            wanted = orc.topk_sorted(orc.proxy_scores(lay.A_K[:, :, :tr.candidates], st.q_hat.cpu()[:, :, None]), c["k"])
+            assert np.array_equal(st.wanted.cpu().numpy(), wanted)
+            table, mask, cnt = orc.slot_diff(table_before, wanted)
+            assert np.array_equal(st.table.cpu().numpy(), table) and np.array_equal(st.mask.cpu().numpy(), mask)
+            lay.table = table
+            idx = torch.from_numpy(table.astype(np.int64))
+            for b in range(c["bsz"]):
+                for h in range(c["hq"]):
+                    got = st.host.data[b, h // grp][idx[b, h]]
+                    lay.Kres[b, h, :c["k"]], lay.Vres[b, h, :c["k"]] = got[:, :c["d"]], got[:, c["d"]:]
+        else:
+            saw.add("all-resident" if tr.candidates < 0 else "no-choice")
+            assert np.array_equal(st.table.cpu().numpy(), z[f"s{s}_table"]) and int(st.mask.sum()) == 0
+        assert torch.equal(st.host.data[:, :, :lay.host_len], lay.host[:, :, :lay.host_len])
+        assert torch.equal(st.K_res.cpu(), lay.Kres) and torch.equal(st.V_res.cpu(), lay.Vres)
+        att = orc.attention(q, lay.Kres[:, :, :rows], lay.Vres[:, :, :rows])
+        assert _rel(out.cpu(), att) < 1e-5
+        if tr.candidates <= c["k"]:      # before any selection the resident rows ARE the reference's, whatever the factors
+            assert _rel(out.cpu(), torch.from_numpy(z[f"s{s}_attn"])) < 1e-5
+        Kd, Vd = fac.Kgpu[:, :, :rows], fac.Vgpu[:, :, :rows]
+        assert Kd.shape == Kv.shape and Vd.shape == Vv.shape
+        lay.B_Q, lay.B_K = st.B_Q.cpu().clone(), st.B_K.cpu().clone()
+        lay.A_K[:, :, lay.a_len - 1] = st.A_K[:, :, lay.a_len - 1].cpu()
+    assert saw == {"all-resident", "no-choice", "selecting"}
+    fac.close()
+
+
+def test_prompt_of_exactly_the_resident_rows_flushes_its_ring():
+    """attn_topk + num_lite_tokens rows: the reference's own first decode step fails there; here the
+    ring goes to the host store at once and decoding proceeds with selection from the first step."""
+    from lrqk_b200 import LightAttentionIndicesFactory
+    c = dict(seed=12, bsz=1, hq=4, hkv=2, d=128, r=8, k=64, m=8)
+    seq, grp = c["k"] + c["m"], 2
+    Q, K, V = orc.make_prompt(c["seed"], c["bsz"], c["hq"], c["hkv"], seq, c["d"])
+    lay = orc.OracleLayer(c["r"], c["k"], c["m"], grp, (2, 2), (1e-2, 1e-2), capacity=seq + 64, init="top")
+    lay.prefill(Q, K, V)
+    fac = LightAttentionIndicesFactory(num_lite_tokens=c["m"], attn_topk=c["k"], num_key_value_groups=grp, r=c["r"],
+                                       max_iter=2, tol=1e-2, capacity=seq + 64, init_aq_ak_method="top")
+    fac.prefill(Q.cuda(), K.cuda(), V.cuda())
+    st = fac.state
+    assert (fac.lite_len, st.host.current_len) == (0, seq) == (lay.lite_len, lay.host_len)
+    assert torch.equal(st.host.data[:, :, :seq], lay.host[:, :, :seq])
+    for s in range(3):
+        q, k, v = orc.make_step(c["seed"], s, c["bsz"], c["hq"], c["hkv"], c["d"])
+        Kd, Vd = fac.decode(q.cuda(), k.cuda(), v.cuda())
+        assert Kd.shape[2] == seq and fac.lite_indices[s] == seq + s
+        lay.decode(q, k, v, want_attention=False)
+        assert lay.lite_indices == fac.lite_indices and lay.trace[-1].candidates == fac.lite_indices[s + 1] - 1
+    fac.close()
+
+
+def test_dynamic_cache_short_prompt_crosses_into_decoding():
+    """pending -> collecting -> decoding with a prompt shorter than num_active_tokens, one token at a
+    time like generate(): the step that reaches num_active_tokens factorises the collected rows
+    (lrqk_attention.py:1928-1958); later steps decode -- first with every row resident, then selecting."""
+    from lrqk_b200 import DynamicLRQKCache
+    c = dict(seed=21, bsz=2, hq=4, hkv=2, d=128, r=8, k=48, m=4)
+    grp, total = 2, 48 + 4 + 6
+    Q, K, V = orc.make_prompt(c["seed"], c["bsz"], c["hq"], c["hkv"], total, c["d"])
+    Q, K, V = Q.cuda(), K.cuda(), V.cuda()
+    cache = DynamicLRQKCache(r=c["r"], num_active_tokens=c["k"], lite_tokens=c["m"], max_iter=2, tol=1e-2,
+                             max_sequence_length=256, num_key_value_groups=grp, init_aq_ak_method="top")
+    S = DynamicLRQKCache.State
+    first = 30
+    k_out, v_out = cache.update(Q[:, :, :first].contiguous(), K[:, :, :first].contiguous(), V[:, :, :first].contiguous(), 0)
+    assert cache.sequence_state[0] == S.collecting and k_out.shape[2] == first
+    for t in range(first, total):
+        q, k, v = (x[:, :, t:t + 1].contiguous() for x in (Q, K, V))
+        state_before = cache.sequence_state[0]
+        if state_before == S.decoding and t % 2 == 0:
+            out = cache.attend(q, k, v, 0)
+            fac = cache.lwattn[0]
+            rows = fac.resident_rows
+            att = orc.attention(q.cpu(), fac.Kgpu[:, :, :rows].cpu(), fac.Vgpu[:, :, :rows].cpu())
+            assert _rel(out.cpu(), att) < 1e-5
+        else:
+            k_out, v_out = cache.update(q, k, v, 0)
+            if state_before == S.collecting:
+                assert k_out.shape[2] == t + 1 and torch.equal(k_out, K[:, :, :t + 1])      # the rows collected so far
+                assert cache.sequence_state[0] == (S.decoding if t + 1 == c["k"] else S.collecting)
+            else:
+                assert k_out.shape == (c["bsz"], c["hq"], min(t + 1, c["k"] + c["m"]), c["d"])
+        if cache.sequence_state[0] == S.decoding:
+            assert cache.get_seq_length(0) == t + 1
+            fac = cache.lwattn[0]
+            if t + 1 <= c["k"] + c["m"]:     # every token resident, in position order
+                assert torch.equal(fac.Kgpu[:, ::grp, :t + 1], K[:, :, :t + 1]) and torch.equal(fac.Vgpu[:, ::grp, :t + 1], V[:, :, :t + 1])
+    fac = cache.lwattn[0]
+    assert fac.state.host.current_len == c["k"] + c["m"] and int(fac.state.table.max()) >= c["k"]   # selection has begun
+    assert torch.equal(fac.state.host.data[:, :, :c["k"] + c["m"]].cuda(), torch.cat([K, V], -1)[:, :, :c["k"] + c["m"]])
+    cache.close()
