@@ -200,11 +200,8 @@ template <int R>
 int launch_r(const ApplyTcArgs &a, cudaStream_t stream) {
   constexpr size_t smem = (size_t)kAStages * kAStageBytes + 2 * kBPartBytes + (2 * kAStages + 4) * 8 + 16 + 16 * 4 + 1024;
   auto kern = apply_tc_kernel<R>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    LRQK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr_set = true;
-  }
+  static SmemOptIn opt_in;
+  LRQK_CUDA_TRY(opt_in.ensure(kern, smem));
   CUtensorMap mk;
   const int rc = make_prompt_map(&mk, a.K, (int64_t)a.bsz * a.kv_heads, a.seq_len, kATileRows);
   if (rc != LRQK_OK) return rc;

@@ -82,6 +82,59 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
+// ---- bulk asynchronous copies completing on an mbarrier -----------------------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+constexpr uint32_t kMbarWaitLimit = 1u << 22;  // polls of an mbarrier before a wait gives up
+
+__device__ __forceinline__ void mbarrier_init(uint64_t *bar, uint32_t arrivals) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(arrivals));
+}
+__device__ __forceinline__ void mbarrier_init_fence() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+
+// Wait for the phase with the given parity; false if the poll limit ran out (the caller records it
+// and carries on with whatever the buffer holds, so that no CTA is left waiting).
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity) {
+  const uint32_t a = smem_addr(bar);
+  for (uint32_t i = 0; i < kMbarWaitLimit; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(a), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+// One thread: expect `bytes` on the barrier and start the copy global -> shared (both 16-byte aligned,
+// bytes a multiple of 16).
+__device__ __forceinline__ void bulk_load(void *dst_smem, const void *src_gmem, uint32_t bytes, uint64_t *bar) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_addr(dst_smem)), "l"(src_gmem), "r"(bytes), "r"(smem_addr(bar)) : "memory");
+}
+
+// ---- one-time function attributes, per device ---------------------------------------------------
+// cudaFuncSetAttribute applies to the device that is current when it is called, so what has been set
+// is remembered per device (a process may drive several GPUs, one after another or from several threads).
+constexpr int kMaxDevices = 64;
+struct SmemOptIn {
+  size_t set[kMaxDevices] = {};
+  template <typename K>
+  cudaError_t ensure(K kernel, size_t bytes) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    if (bytes <= set[dev]) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess) set[dev] = bytes;
+    return e;
+  }
+};
+
 // ---- programmatic dependent launch -------------------------------------------------------------
 // The kernels of a decode step depend on one another in stream order.  Each is launched with the
 // programmatic-stream-serialization attribute, calls pdl_launch_dependents() first thing and

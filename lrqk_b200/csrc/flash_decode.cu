@@ -27,7 +27,6 @@ constexpr int kAThreads = 256;
 constexpr int kAWarps = kAThreads / 32;
 constexpr int kMaxSplits = 64;
 constexpr int kStageBytes = 32 * 1024;        // staging buffer for the keys of one round
-constexpr uint32_t kWaitLimit = 1u << 22;     // polls of an mbarrier before giving up
 
 struct AttnParams {
   const void *q, *K_res, *V_res;
@@ -41,22 +40,6 @@ struct AttnParams {
   float scale_log2;   // softmax scale * log2(e)
   PushTargets push;   // world == 0: no exchange with other ranks
 };
-
-__device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity) {
-  const uint32_t a = smem_addr(bar);
-  for (uint32_t i = 0; i < kWaitLimit; ++i) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done) : "r"(a), "r"(parity) : "memory");
-    if (done) return true;
-  }
-  return false;
-}
 
 template <typename T, int D>
 __global__ void __launch_bounds__(kAThreads, 4) flash_decode_kernel(AttnParams p) {
@@ -316,11 +299,8 @@ int launch_flash_decode(const lrqk_layer *L, const void *q, void *out, int32_t r
 #define LRQK_ATTN_LAUNCH(T, D)                                                                              \
   do {                                                                                                      \
     auto kern = flash_decode_kernel<T, D>;                                                                  \
-    static bool attr_set = false;                                                                           \
-    if (!attr_set) {                                                                                        \
-      LRQK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem)); \
-      attr_set = true;                                                                                      \
-    }                                                                                                       \
+    static SmemOptIn opt_in;                                                                                \
+    LRQK_CUDA_TRY(opt_in.ensure(kern, kAttnSmem));                                                          \
     LRQK_CUDA_TRY(launch_dependent(kern, grid, dim3(kAThreads), kAttnSmem, s, 0, p));                       \
   } while (0)
   if (L->head_dim == 128) {
@@ -396,9 +376,8 @@ extern "C" int lrqk_flash_decode_push(const lrqk_layer *L, const void *q, void *
 namespace lrqk {
 namespace {
 constexpr size_t kStaticScratchBytes = 4u << 20;  // 4 MiB: e.g. 470 heads of head_dim 128 at 2112 bf16 rows (17 splits)
-constexpr int kMaxDevices = 64;
 static __device__ __align__(256) unsigned char g_static_attn_scratch[kStaticScratchBytes];
-static void *g_static_scratch_ptr[kMaxDevices] = {};  // device-usable address, per device
+static void *g_static_scratch_ptr[lrqk::kMaxDevices] = {};  // device-usable address, per device
 }  // namespace
 }  // namespace lrqk
 
@@ -425,7 +404,7 @@ extern "C" int lrqk_flash_decode_static(const lrqk_layer *L, const void *q, void
   }
   int dev = -1;
   LRQK_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= kMaxDevices) return LRQK_EUNSUPPORTED;
+  if (dev < 0 || dev >= lrqk::kMaxDevices) return LRQK_EUNSUPPORTED;
   if (!g_static_scratch_ptr[dev]) {  // set-up, once per device, with that device current
     void *ptr = nullptr;
     LRQK_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_attn_scratch));

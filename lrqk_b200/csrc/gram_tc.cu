@@ -217,11 +217,8 @@ int launch_r(const GramTcArgs &a, cudaStream_t stream) {
   constexpr int kStages = stage_count<R>();
   constexpr size_t smem = (size_t)kStages * (3 * kGroupBytes + kRawBytes) + (3 * kStages + 1) * 8 + 16 + 1024;
   auto kern = gram_tc_kernel<R>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    LRQK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr_set = true;
-  }
+  static SmemOptIn opt_in;
+  LRQK_CUDA_TRY(opt_in.ensure(kern, smem));
   CUtensorMap mq, mk;
   int rc = make_prompt_map(&mq, a.Q, (int64_t)a.bsz * a.q_heads, a.seq_len, kTileRows);
   if (rc != LRQK_OK) return rc;

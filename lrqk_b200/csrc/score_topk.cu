@@ -406,16 +406,10 @@ int launch_score_topk(const ScoreTopkParams &p, int n_heads, int csize, cudaStre
   size_t smem = ((size_t)p.seg_len + 3 * kBins + 2 * (kWarps + 1) + 6 + R) * sizeof(uint32_t);
   if (p.table != nullptr && slot_diff_smem_bytes(p.k) > smem) smem = slot_diff_smem_bytes(p.k);
   auto kern = score_topk_kernel<T, R>;
-  static size_t smem_set = 0;
-  static bool nonportable_set = false;
-  if (smem > smem_set) {
-    LRQK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    smem_set = smem;
-  }
-  if (csize > 8 && !nonportable_set) {
+  static SmemOptIn opt_in;
+  LRQK_CUDA_TRY(opt_in.ensure(kern, smem));
+  if (csize > 8)   // clusters of 16 need the non-portable opt-in (per device, cheap: only the very long contexts get here)
     LRQK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
-    nonportable_set = true;
-  }
   LRQK_CUDA_TRY(launch_dependent(kern, dim3(csize, n_heads, 1), dim3(kThreads), smem, stream, csize, p));
   return LRQK_OK;
 }

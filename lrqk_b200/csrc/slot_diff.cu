@@ -27,11 +27,8 @@ extern "C" int lrqk_slot_diff(const lrqk_layer *L, const int32_t *wanted, uint8_
   if (!wanted || !mask || !miss_count || !list || !list_len || !status || !L->table) return LRQK_EINVAL;
   const size_t smem = slot_diff_smem_bytes(L->k);
   if (smem > 200 * 1024) return LRQK_EUNSUPPORTED;
-  static size_t smem_set = 48 * 1024;
-  if (smem > smem_set) {
-    LRQK_CUDA_TRY(cudaFuncSetAttribute(slot_diff_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    smem_set = smem;
-  }
+  static SmemOptIn opt_in;
+  if (smem > 48 * 1024) LRQK_CUDA_TRY(opt_in.ensure(slot_diff_kernel, smem));
   LRQK_CUDA_TRY(launch_dependent(slot_diff_kernel, dim3(L->bsz * L->q_heads), dim3(kDThreads), smem, as_stream(stream), 0,
                                  L->table, wanted, mask, miss_count, list, list_len, status, (int)L->k));
   return LRQK_OK;

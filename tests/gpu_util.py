@@ -89,16 +89,17 @@ def synthetic_state(bsz, hq, hkv, d, r, k, m, ctx, seed=0, dtype=torch.bfloat16,
     return st
 
 
-def bf16_excess(dev: torch.Tensor, ref32: torch.Tensor, fp32_tol: float) -> float:
+def bf16_excess(dev: torch.Tensor, ref32: torch.Tensor, fp32_tol: float, roundings: int = 1) -> float:
     """How far a bf16 result `dev` lies from the fp32 oracle value `ref32`, in units of the allowed
     distance; <= 1 passes.  Allowed per element: the arithmetic tolerance the same kernel meets in
     fp32 (`fp32_tol`, relative to the largest magnitude of the tensor -- 1e-5 for scores and
     attention) plus ONE rounding to bf16 of that element (half a bf16 ulp at the element's own
     magnitude, 2^-9 relative).  A bound "1e-3 of the largest magnitude" cannot be met by any value
     STORED in bf16 (the rounding of an element near the maximum alone is up to 2^-9 = 1.95e-3 of it);
-    this bound is the tight form of the same statement: fp32 arithmetic, then a single rounding."""
+    this bound is the tight form of the same statement: fp32 arithmetic, then a single rounding.
+    `roundings=2` is for a reference that was itself rounded to bf16 (the oracle's per-step state)."""
     d, r = dev.detach().double().cpu(), ref32.detach().double().cpu()
     mag = torch.maximum(d.abs(), r.abs()).clamp_min(2.0 ** -126)
     half_ulp = torch.exp2(torch.floor(torch.log2(mag)) - 8.0)        # bf16: 8 significant bits, ulp = 2^(e-7)
-    allowed = half_ulp * (1 + 1e-6) + fp32_tol * float(r.abs().max())
+    allowed = roundings * half_ulp * (1 + 1e-6) + fp32_tol * float(r.abs().max())
     return float(((d - r).abs() / allowed).max())

@@ -1,8 +1,13 @@
 """Parity of the CUDA decode-path kernels (called through the C ABI) with the CPU oracle.
 
 Tolerances: integer outputs (selected positions, slot table, masks, gathered rows) must be
-bit-exact; proxy scores and attention outputs within 1e-5 relative in fp32 and 1e-3 relative in
-bf16 (relative to the largest magnitude of the compared tensor).
+bit-exact.  Proxy scores are fp32 in either dtype: within 1e-5 (fp32 operands) / 1e-3 (bf16 operands)
+of the oracle's, relative to the largest magnitude of the tensor, and bit-exact against the oracle's
+emulation of the kernel's summation order.  Results that are STORED in bf16 (attention rows, projected
+query / key, right factors) are held to the fp32 tolerance of the same quantity -- 1e-5 for attention,
+2e-4 for the r x r solves, whose round-off the solves amplify -- plus one rounding of the element to
+bf16 (``gpu_util.bf16_excess``): a bound of 1e-3 of the largest magnitude cannot hold for a stored bf16
+value, whose rounding alone is up to 2^-9 = 1.95e-3 of it.
 """
 import json
 import os
@@ -12,6 +17,7 @@ import pytest
 import torch
 
 import lrqk_oracle as orc
+from gpu_util import bf16_excess
 
 pytestmark = pytest.mark.gpu
 
@@ -245,8 +251,9 @@ def test_flash_decode_matches_oracle(dtype, d, rows, bsz, hq):
         out = st.flash_decode(q.cuda(), rows=use_rows).float().cpu()
         ref = orc.attention(q[:, :, None], K[:, :, :use_rows], V[:, :, :use_rows])[:, :, 0]
         if dtype == torch.bfloat16:
-            ref = ref.to(torch.bfloat16).float()
-        assert _rel(out, ref) < (4e-3 if dtype == torch.bfloat16 else tol)
+            assert bf16_excess(out, ref, 1e-5) <= 1.0
+        else:
+            assert _rel(out, ref) < tol
     # calling twice gives the same bits (the ticket is re-armed, the fold order is fixed)
     a = st.flash_decode(q.cuda()).clone()
     b = st.flash_decode(q.cuda()).clone()
@@ -289,11 +296,15 @@ def test_project_update_matches_oracle(dtype, r, k, m, bsz, hq, hkv, max_iter):
             BQ.to(f), A_act.to(f), BK.to(f), Kres.to(f), q[:, :, None].to(f), krep.to(f), max_iter, tol_exit,
             return_iters=True)
         assert int(st.counters[2].item()) == iters
-        eq, ek, eBQ, eBK = (x.to(dtype).float() for x in (eq, ek, eBQ, eBK))
-        tol = 2e-4 if dtype == torch.float32 else 1.6e-2   # solves amplify round-off; bf16 adds one rounding
-        assert _rel(qh, eq[:, :, 0]) < tol
-        assert _rel(st.A_K[:, :, append_row].float(), ek[:, :, 0]) < tol
-        assert _rel(st.B_Q.float(), eBQ) < tol and _rel(st.B_K.float(), eBK) < tol
+        tol = 2e-4                                   # the solves amplify fp32 round-off
+        if dtype == torch.float32:
+            assert _rel(qh, eq[:, :, 0]) < tol
+            assert _rel(st.A_K[:, :, append_row].float(), ek[:, :, 0]) < tol
+            assert _rel(st.B_Q.float(), eBQ) < tol and _rel(st.B_K.float(), eBK) < tol
+        else:                                        # the same bound, plus the rounding of the stored value
+            assert bf16_excess(qh, eq[:, :, 0], tol) <= 1.0
+            assert bf16_excess(st.A_K[:, :, append_row], ek[:, :, 0], tol) <= 1.0
+            assert bf16_excess(st.B_Q, eBQ, tol) <= 1.0 and bf16_excess(st.B_K, eBK, tol) <= 1.0
         assert torch.equal(st.A_K[:, :, :append_row].cpu(), A[:, :, :append_row])
 
 
@@ -382,7 +393,7 @@ def test_layer_step_free_running_bf16(c):
         lay.decode(q, k, v, want_attention=False)
         tr = lay.trace[-1]
         assert bk["candidates"] == tr.candidates
-        assert _rel(st.q_hat.cpu().float(), tr.q_hat[:, :, 0].float()) < 3e-2
+        assert bf16_excess(st.q_hat, tr.q_hat[:, :, 0].float(), 5e-4, roundings=2) <= 1.0   # the oracle's is rounded too
         wanted = orc.topk_sorted(orc.proxy_scores(lay.A_K[:, :, :tr.candidates], st.q_hat.cpu()[:, :, None]), c["k"])
         assert np.array_equal(st.wanted.cpu().numpy(), wanted), f"step {s}"
         table, mask, cnt = orc.slot_diff(table_before, wanted)
@@ -400,8 +411,7 @@ def test_layer_step_free_running_bf16(c):
                 assert torch.equal(Vres[b, h, :c["k"]], rows[:, c["d"]:])
         assert torch.equal(Kres[:, :, c["k"]:], lay.Kres[:, :, c["k"]:])
         assert torch.equal(Vres[:, :, c["k"]:], lay.Vres[:, :, c["k"]:])
-        att = orc.attention(q, Kres, Vres)[:, :, 0].to(torch.bfloat16).float()
-        assert _rel(st.attn_out.cpu().float(), att) < 4e-3
+        assert bf16_excess(st.attn_out, orc.attention(q, Kres, Vres)[:, :, 0], 1e-5) <= 1.0
         # the oracle adopts the device's state for the next step
         lay.table = table
         lay.B_Q, lay.B_K = st.B_Q.cpu(), st.B_K.cpu()

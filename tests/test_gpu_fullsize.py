@@ -9,7 +9,7 @@ m=64, bf16), checked through properties that do not need the CPU oracle to repea
 * miss fetch: every refilled slot holds the host store's row of its new position, byte for byte,
   and no other resident row changed (checksums before/after);
 * attention: equals softmax(q K^T / sqrt(d)) V over the resident rows computed by torch on the
-  same device within the bf16 tolerance the small-shape tests use.
+  same device within the tolerance the small-shape tests use (1e-5 plus one rounding to bf16).
 """
 import numpy as np
 import pytest
@@ -90,6 +90,6 @@ def test_full_shape_step_properties():
     assert torch.equal(st.K_res[:, :, k:], K_before[:, :, k:]) and torch.equal(st.V_res[:, :, k:], V_before[:, :, k:])
     # ---- attention ----
     ref = torch.nn.functional.scaled_dot_product_attention(q[:, :, None].float(), st.K_res.float(), st.V_res.float())[:, :, 0]
-    err = float((out.float() - ref).abs().max() / ref.abs().max())
-    assert err < 4e-3, err
+    from gpu_util import bf16_excess
+    assert bf16_excess(out, ref, 1e-5) <= 1.0     # fp32 tolerance plus the rounding of the stored bf16 row
     st.close()

@@ -349,6 +349,8 @@ def test_dynamic_cache_short_prompt_crosses_into_decoding():
             if t + 1 <= c["k"] + c["m"]:     # every token resident, in position order
                 assert torch.equal(fac.Kgpu[:, ::grp, :t + 1], K[:, :, :t + 1]) and torch.equal(fac.Vgpu[:, ::grp, :t + 1], V[:, :, :t + 1])
     fac = cache.lwattn[0]
-    assert fac.state.host.current_len == c["k"] + c["m"] and int(fac.state.table.max()) >= c["k"]   # selection has begun
-    assert torch.equal(fac.state.host.data[:, :, :c["k"] + c["m"]].cuda(), torch.cat([K, V], -1)[:, :, :c["k"] + c["m"]])
+    flushed = c["k"] + c["m"] * ((total - c["k"]) // c["m"])          # the prompt's first k rows, then whole rings
+    assert fac.state.host.current_len == flushed and int(fac.state.table.max()) >= c["k"]   # selection has begun
+    torch.cuda.synchronize()
+    assert torch.equal(fac.state.host.data[:, :, :flushed].cuda(), torch.cat([K, V], -1)[:, :, :flushed])
     cache.close()
