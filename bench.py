@@ -45,10 +45,10 @@ WORKLOADS = {
     "cfg4-layer": dict(bsz=1, hq=40, hkv=8, d=128, seq=262144, r=64, k=4096, m=128, max_iter=(4, 4), tol=1e-2),
     "cfg0": dict(bsz=1, hq=8, hkv=2, d=128, seq=4096, r=16, k=256, m=16, max_iter=(2, 2), tol=1e-2),
 }
-# dram__bytes (read + write) of one launch from the ncu capture summarised in
-# profiles/path_kernels_cfg2_ncu_sections.md (1 GPU, cfg2-layer)
-NCU_TRAFFIC_CFG2 = {"score_topk": 272.8e6, "flash_decode": 35.2e6, "project_update": 27.2e6, "slot_diff": 0.5e6,
-                    "miss_gather": 0.8e6, "lite_append": 0.0}
+# DRAM bytes moved per algorithmic byte of the scoring kernel, from the ncu capture summarised under profiles/
+# (dram__bytes_read.sum + dram__bytes_write.sum of one launch = 272.8 MB against 268.6 MB algorithmic); the
+# kernel's traffic grows in proportion to the rows it scores, so other sizes are scaled by this ratio.
+NCU_TRAFFIC_RATIO = {"score_topk": 1.0156}
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -220,6 +220,8 @@ def run_ours(args):
     hkv_l, hq_l = w["hkv"] // world, w["hq"] // world
     n_tokens = args.warmup + 3 * args.steps + 8
     layers = args.layers
+    sweep_rhos = [r for r in (0.9, 0.99) if not args.no_rho_sweep and abs(r - args.rho) > 1e-9]
+    sweep_warm, sweep_probe = 6, 2
     t_setup = time.time()
     facs, prefill_ms = build_layers(w, layers, hq_l, hkv_l, rank * 1000, device, dtype, args.seed, n_tokens)
     q_all, k_all, v_all = make_steps(args.seed + 1 + rank, n_tokens, layers, w, hq_l, hkv_l, args.rho, device, dtype)
@@ -284,7 +286,6 @@ def run_ours(args):
         torch.cuda.current_stream().synchronize()
     e3.record()
     barrier()
-    clocks = sampler.stop()
     ms_e2e = e2.elapsed_time(e3)
     tcur += args.steps
     h2d = (dq.numel() + dk.numel() + dv.numel()) * dq.element_size()
@@ -317,6 +318,48 @@ def run_ours(args):
     misses_per_step = float(miss_acc.item()) / len(evs)
     miss_rate = misses_per_step / (w["bsz"] * hq_l * w["k"])
 
+    # ---- the same timed loop at other query localities: q_t = rho q_(t-1) + sqrt(1 - rho^2) eps.  Independent
+    # queries (rho = 0) miss nearly every selected row; a model's consecutive queries are correlated ----
+    def floor_us(misses):
+        b = stage_bytes(w, hq_l, hkv_l, cand_seen, misses, e=2 if dtype == torch.bfloat16 else 4)
+        return sum(b[n] / ((link_peak if n == "miss_gather" else hbm_peak) * 1e9) for n in names) * 1e6
+
+    hbm_peak, peak_kind = measured_hbm_peak()
+    link_peak = host_link_peak_gbs(device)
+    by_rho = {}
+    for rho in sweep_rhos:
+        n_sw = sweep_warm + args.steps + sweep_probe
+        qs_, ks_, vs_ = make_steps(args.seed + 17 + rank, n_sw, layers, w, hq_l, hkv_l, rho, device, dtype)
+
+        def tok(t):
+            for li, fac in enumerate(facs):
+                layer(fac, qs_[t, li], ks_[t, li], vs_[t, li])
+
+        for t in range(sweep_warm):
+            tok(t)
+        barrier()
+        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        r0.record()
+        for t in range(sweep_warm, sweep_warm + args.steps):
+            tok(t)
+        r1.record()
+        barrier()
+        acc = torch.zeros((), dtype=torch.int64, device=device)
+        for t in range(sweep_warm + args.steps, n_sw):
+            for li, fac in enumerate(facs):
+                layer(fac, qs_[t, li], ks_[t, li], vs_[t, li])
+                acc += fac.state.miss_count.sum()
+        ms_r = torch.tensor([r0.elapsed_time(r1)], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(ms_r, op=dist.ReduceOp.MAX)
+        us_r = float(ms_r[0]) * 1e3 / (args.steps * layers)
+        miss_r = float(acc.item()) / (sweep_probe * layers)
+        fl = floor_us(miss_r)
+        by_rho[str(rho)] = {"us_measured": round(us_r, 2), "us_at_roofline": round(fl, 1), "frac": round(fl / us_r, 4),
+                            "miss_rate": round(miss_r / (w["bsz"] * hq_l * w["k"]), 4)}
+        del qs_, ks_, vs_
+    clocks = sampler.stop()
+
     # ---- self-check, outside every timed region: one more step per layer state, issued stage by stage and
     # fused from the same starting state; every output must be bit-identical and the diff status clear ----
     from lrqk_b200 import selfcheck
@@ -341,6 +384,7 @@ def run_ours(args):
         problems = [p for ps in everyone for p in ps]
 
     # max over ranks
+    ms_dev_own = ms_dev
     vals = torch.tensor([ms_dev, ms_e2e], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(vals, op=dist.ReduceOp.MAX)
@@ -348,8 +392,6 @@ def run_ours(args):
     us_per_layer = ms_dev * 1e3 / (args.steps * layers)
     us_per_layer_e2e = ms_e2e * 1e3 / (args.steps * layers)
 
-    hbm_peak, peak_kind = measured_hbm_peak()
-    link_peak = host_link_peak_gbs(device)
     bytes_ = stage_bytes(w, hq_l, hkv_l, cand_seen, misses_per_step, e=2 if dtype == torch.bfloat16 else 4)
     per_kernel = {}
     for n in names:
@@ -358,7 +400,11 @@ def run_ours(args):
         peak = link_peak if n == "miss_gather" else hbm_peak
         per_kernel[n] = {"us": round(stage_us[n], 2), "bytes": int(bytes_[n]), "bound": bound,
                          "achieved": round(gbs, 1), "peak": round(peak, 1), "unit": "GB/s", "frac": round(gbs / peak, 4),
-                         "traffic": (NCU_TRAFFIC_CFG2.get(n) if args.workload == "cfg2-layer" and world == 1 else None)}
+                         # DRAM traffic of one launch (ncu) where a capture exists; the miss fetch moves its bytes over
+                         # the host link, not out of DRAM, so it has none
+                         "traffic": (round(bytes_[n] * NCU_TRAFFIC_RATIO[n]) if n in NCU_TRAFFIC_RATIO else None)}
+        if n == "miss_gather":
+            per_kernel[n]["host_link_bytes"] = int(bytes_[n])
     dominant = max(names, key=lambda n: stage_us[n])
     roof = dict(per_kernel[dominant])
     roof.update({"kernel": dominant,
@@ -372,8 +418,17 @@ def run_ours(args):
     # algorithmic bytes over their peaks (HBM for all but the miss fetch, the host link for that)
     step_floor_us = sum(bytes_[n] / ((link_peak if n == "miss_gather" else hbm_peak) * 1e9) for n in names) * 1e6
     roof_step = {"us_at_roofline": round(step_floor_us, 1), "us_measured": round(us_per_layer, 2),
-                 "frac": round(step_floor_us / us_per_layer, 4),
+                 "frac": round(step_floor_us / us_per_layer, 4), "miss_rate": round(miss_rate, 4),
                  "note": "sum over the six stages of algorithmic bytes / measured peak"}
+    by_rho[str(args.rho)] = {k2: roof_step[k2] for k2 in ("us_measured", "us_at_roofline", "frac", "miss_rate")}
+    # every rank's own figures (the value above is the slowest rank's): unequal host links show up here
+    mine = {"rank": rank, "us_per_layer_step": round(ms_dev_own * 1e3 / (args.steps * layers), 2),
+            "host_link_peak_gbs": round(link_peak, 1), "host_issue_us_per_layer_step": round(host_issue_us, 1),
+            "stage_us": {n: round(stage_us[n], 2) for n in names}}
+    per_rank = [mine]
+    if world > 1:
+        per_rank = [None] * world
+        dist.all_gather_object(per_rank, mine)
     line = {
         "metric": "decode_us_per_layer_128k" if args.workload == "cfg2-layer" else f"decode_us_per_layer_{args.workload}",
         "value": round(us_per_layer, 2), "unit": "us/layer/step", "n_gpus": world, "steps": args.steps,
@@ -397,20 +452,35 @@ def run_ours(args):
         # per layer-step: projection, update, scoring(+diff), miss fetch, attention (+ exchange wait);
         # plus one ring-flush kernel per layer every m steps
         "gpu_launches": int(args.steps * layers * (5 + (1 if exchange is not None else 0)) + layers * (args.steps // w["m"])),
-        "roofline": roof, "roofline_hbm": roof_hbm, "roofline_step": roof_step, "kernels": per_kernel,
+        "roofline": roof, "roofline_hbm": roof_hbm, "roofline_step": roof_step,
+        "roofline_step_by_rho": dict(sorted(by_rho.items())), "kernels": per_kernel, "per_rank": per_rank,
         "host_link_peak_gbs": round(link_peak, 1), "clocks": clocks,
         "selfcheck": "ok" if not problems else problems,
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline_from_state(facs[0], w, q_all, k_all, v_all, tcur, n_steps=5)
-    if rank == 0:
-        print(json.dumps(line), flush=True)
     if exchange is not None:
         exchange.check_status()
         dist.barrier()
         exchange.close()
     for fac in facs:
         fac.close()
+    del facs, q_all, k_all, v_all
+    torch.cuda.empty_cache()
+    # ---- whole model: tokens/s of the Llama-3-8B architecture at this workload's settings (all 32 layers, the
+    # 131072-token prompt, 256 greedy tokens), through the patched forward and DynamicLRQKCache on these ranks ----
+    if args.workload == "cfg2-layer" and not args.no_model:
+        try:
+            m = model_run("llama3-8b", args)
+            line["model"] = {"metric": m["metric"], "tokens_per_s": m["value"], "ms_per_token": m["ms_per_step"],
+                             "host_issue_ms_per_step": m["host_issue_ms_per_step"], "prefill_s": m["prefill_s"],
+                             "prefill_tokens_per_s": m["prefill_tokens_per_s"], "decode_tokens": m["steps"],
+                             "us_per_layer_step_including_dense": m["us_per_layer_step_including_dense"],
+                             "hit_rate_per_step": m["hit_rate_per_step"], "config": m["config"], "clocks": m["clocks"]}
+        except Exception as e:   # the per-layer figures above stand on their own
+            line["model"] = {"error": f"{type(e).__name__}: {e}"[:300]}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
@@ -539,10 +609,29 @@ MODELS = {
 
 
 def run_model(args):
+    """`--model NAME`: the whole-model run alone; prints its own JSON line."""
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
+    torch.cuda.set_device(local_rank)
+    from lrqk_b200 import sharding as _sharding
+    _sharding.bind_host_to_gpu_numa(local_rank)                # the host K|V stores are allocated after this
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    line = model_run(args.model, args)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def model_run(model_name: str, args) -> dict:
+    """Prompt pass and greedy decode of a random-init decoder stack of the named architecture through the patched
+    forward and DynamicLRQKCache, on this process group (already initialised when there are several ranks)."""
     import transformers
     from lrqk_b200 import DynamicLRQKCache, patch_model
-    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
-    spec = dict(MODELS[args.model])
+    spec = dict(MODELS[model_name])
     family = spec.pop("family")
     r, k, m, max_iter = spec.pop("r"), spec.pop("k"), spec.pop("m"), spec.pop("max_iter")
     prompt = args.prompt or spec.pop("prompt")
@@ -558,13 +647,9 @@ def run_model(args):
     cfg._attn_implementation = "sdpa"
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    from lrqk_b200 import sharding as _sharding
-    _sharding.bind_host_to_gpu_numa(local_rank)                # the host K|V stores are allocated after this
     dist = None
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     torch.manual_seed(args.seed)                               # every rank builds the same weights
     t0 = time.time()
     with torch.device("cuda"):
@@ -636,7 +721,7 @@ def run_model(args):
         "metric": "decode_tokens_per_s", "value": round(batch * n_decode / (ms * 1e-3), 2), "unit": "tokens/s",
         "n_gpus": world, "steps": n_decode, "warmup": args.warmup, "ms_per_step": round(ms / n_decode, 3),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"{args.model} architecture, random init, {cfg.num_hidden_layers} layers, batch {batch}, "
+        "config": {"workload": f"{model_name} architecture, random init, {cfg.num_hidden_layers} layers, batch {batch}, "
                                f"{prompt}-token uniform-random prompt, greedy decode", "r": r, "k": k, "m": m,
                    "max_iter": list(max_iter), "dense_parts": "transformers modules (library GEMMs, SDPA for the prompt pass)"
                    + (", replicated on every rank" if world > 1 else ""),
@@ -655,11 +740,10 @@ def run_model(args):
         "miss_fetch_host_link_gbs_over_whole_step": round(fetched / (ms * 1e-3) / 1e9, 2),
         "clocks": clocks,
     }
-    if rank == 0:
-        print(json.dumps(line), flush=True)
     cache.close()
-    if world > 1:
-        dist.destroy_process_group()
+    del model, cache, out
+    torch.cuda.empty_cache()
+    return line
 
 
 def main():
@@ -673,6 +757,9 @@ def main():
     ap.add_argument("--rho", type=float, default=0.0)
     ap.add_argument("--seed", type=int, default=2024)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-rho-sweep", action="store_true", help="skip the extra timed loops at rho = 0.9 and 0.99")
+    ap.add_argument("--no-model", action="store_true",
+                    help="skip the whole-model tokens/s block (Llama-3-8B architecture) of the default line")
     ap.add_argument("--collective", default="push", choices=["push", "nccl", "none"],
                     help="N > 1: how the attention rows of all heads reach every rank")
     ap.add_argument("--model", default=None, choices=sorted(MODELS),
