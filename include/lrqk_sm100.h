@@ -133,9 +133,16 @@ int lrqk_decode_project_update(const lrqk_layer *L, const void *q, const void *k
  *   wanted     : out [B,Hq,k] int32, ascending.  Scores are fp32 dot products of the stored
  *                operands; of equal scores the lower position wins (-0 equals +0).
  *   scores_out : optional [B,Hq,scores_stride] fp32 copy of the scores (testing)
+ *   workspace  : optional scratch of lrqk_score_topk_workspace_bytes(L, largest candidate count to come).
+ *                With few heads (a rank's share of a head-sharded layer) the scoring is cut into two
+ *                kernels -- keys formed on all SMs into this scratch, then the selection -- which is quicker
+ *                than clusters that cover a fraction of the GPU; that function returns 0 where the one-kernel
+ *                plan is the better one.  NULL: always one kernel.  The selection is the same either way.
  * ---------------------------------------------------------------------------------- */
+size_t lrqk_score_topk_workspace_bytes(const lrqk_layer *L, int64_t max_candidates);
 int lrqk_score_topk(const lrqk_layer *L, const void *q_hat, int64_t candidates, int32_t *wanted,
-                    float *scores_out, int64_t scores_stride, lrqk_stream_t stream);
+                    float *scores_out, int64_t scores_stride, void *workspace, size_t workspace_bytes,
+                    lrqk_stream_t stream);
 
 /* ------------------------------------------------------------------------------------
  * Hit/miss difference of `wanted` against the slot table, in place.
@@ -272,6 +279,8 @@ typedef struct lrqk_step_args {
   void *attn_workspace;
   const struct lrqk_peer_group *peers; /* NULL, or the ranks that receive this layer's attention output */
   int32_t push_seq;       /* sequence number of this push (see lrqk_flash_decode_push)  */
+  void *score_workspace;  /* NULL, or scratch of lrqk_score_topk_workspace_bytes() for the scoring stage */
+  size_t score_workspace_bytes;
 } lrqk_step_args;
 
 int lrqk_layer_step(const lrqk_layer *L, const lrqk_step_args *a, lrqk_stream_t stream);

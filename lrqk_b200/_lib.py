@@ -49,6 +49,7 @@ class StepArgs(C.Structure):
         ("miss_list", C.c_void_p), ("counters", C.c_void_p),
         ("project_workspace", C.c_void_p), ("attn_workspace", C.c_void_p),
         ("peers", C.c_void_p), ("push_seq", C.c_int32),
+        ("score_workspace", C.c_void_p), ("score_workspace_bytes", C.c_size_t),
     ]
 
 
@@ -77,8 +78,9 @@ _SIGNATURES = {
     "lrqk_decode_project_update_workspace_bytes": (C.c_size_t, [C.POINTER(Layer), C.c_int32]),
     "lrqk_decode_project_update": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_void_p, C.c_int32, C.c_float,
                                              C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "lrqk_score_topk_workspace_bytes": (C.c_size_t, [C.POINTER(Layer), C.c_int64]),
     "lrqk_score_topk": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64,
-                                  C.c_void_p]),
+                                  C.c_void_p, C.c_size_t, C.c_void_p]),
     "lrqk_slot_diff": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                  C.c_void_p, C.c_void_p]),
     "lrqk_miss_gather": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_void_p, C.c_void_p]),

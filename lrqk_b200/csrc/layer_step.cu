@@ -26,7 +26,8 @@ extern "C" int lrqk_layer_step(const lrqk_layer *L, const lrqk_step_args *a, lrq
   FusedDiff diff;
   diff.mask = a->mask; diff.miss_count = a->miss_count; diff.list = a->miss_list;
   diff.list_len = a->counters; diff.status = a->counters + 1;
-  rc = score_topk_enqueue(L, a->q_hat, a->candidates, a->wanted, nullptr, 0, nullptr, as_stream(stream), &diff);
+  rc = score_topk_enqueue(L, a->q_hat, a->candidates, a->wanted, nullptr, 0, nullptr, as_stream(stream), &diff,
+                          a->score_workspace, a->score_workspace_bytes);
   if (rc != LRQK_OK) return rc;
   rc = lrqk_miss_gather(L, a->miss_list, a->counters, stream);
   if (rc != LRQK_OK) return rc;

@@ -13,6 +13,13 @@
 // "above the digit", "equal to it"), and the later passes and the ordered, ascending compaction
 // only revisit the marked keys.  Of equal scores the lower position wins.
 //
+// With few heads that plan leaves most SMs idle (a head spans at most 8 CTAs).  Then the work is cut
+// differently: a first kernel streams A_K over ALL SMs -- work items of 2048 rows dealt out evenly,
+// whatever head they belong to -- and writes the keys to a workspace that stays in L2 (4 bytes per
+// candidate row); the select kernel then runs unchanged except that its CTAs fill their key segments from
+// that workspace instead of from A_K.  Scores, keys and therefore the selection are bit-identical in
+// both plans.
+//
 // Summation order of a score (fixed, so results are reproducible): the r columns are split
 // over `lanes = max(1, row_bytes / 64)` lanes; each lane sums the even and the odd columns of its
 // run separately, left to right with fused multiply-adds starting from zero (the two sums share
@@ -102,6 +109,8 @@ struct ScoreTopkParams {
   float *scores_out;    // optional [N, scores_stride]
   int64_t scores_stride;
   int32_t *clear_word;  // optional: set to zero by the kernel
+  const uint32_t *keys_in;  // optional [N, keys_stride]: keys already formed by score_keys_kernel
+  int64_t keys_stride;
   // optional fused hit/miss difference (table != nullptr): after the selection, the first CTA of
   // every cluster runs slot_diff_head for its head
   int32_t *table;
@@ -162,8 +171,13 @@ __device__ __forceinline__ int key_slot(int i, int V, uint32_t magic) {
   return (int)(((j * kThreads + t) << 2) | ((uint32_t)i & 3u));
 }
 
-template <typename T, int R>
-__global__ void __launch_bounds__(kThreads, 1) score_topk_kernel(ScoreTopkParams p) {
+// Scores of the rows [seg_begin, seg_begin + seg_rows) of head n, by all kThreads threads of the CTA:
+// sink(local_row, score) is called by the lane that ends up with a row's sum, for every local row below the
+// returned count (the row count rounded up to whole trips; rows past seg_rows re-read the last row and their
+// score is to be discarded).  `qs`: q_hat of the head as fp32 in shared memory, visible to all threads.
+template <typename T, int R, typename Sink>
+__device__ __forceinline__ int score_rows(const void *A_K, int64_t a_capacity, int n, int64_t seg_begin, int64_t seg_rows,
+                                          const float *qs, Sink sink) {
   constexpr int RB = R * (int)sizeof(T);          // bytes per row
   constexpr int VB = RB >= 32 ? 32 : 16;          // bytes per load
   constexpr int VPL = RB >= 64 ? 2 : 1;           // loads per lane and row: a lane covers up to 64 bytes of a row
@@ -174,40 +188,12 @@ __global__ void __launch_bounds__(kThreads, 1) score_topk_kernel(ScoreTopkParams
   constexpr int RPI = kThreads / LPR;             // rows per CTA-wide load
   constexpr int kUnroll = 4 / VPL;                // rows a thread keeps in flight (128 bytes)
   static_assert(kGranule % (RPI * kUnroll) == 0, "a granule must be a whole number of unrolled loads");
-
-  cg::cluster_group cluster = cg::this_cluster();
-  const int rank = (int)cluster.block_rank();
-  const int csize = (int)cluster.num_blocks();
-  const int n = blockIdx.y;
   const int tid = threadIdx.x;
-
-  extern __shared__ __align__(16) uint32_t smem[];
-  uint32_t *keys = smem;                       // [seg_len]
-  uint32_t *hist = keys + p.seg_len;           // [3][kBins] this CTA's histogram of each pass (peers read it)
-  uint32_t *scratch = hist + 3 * kBins;          // [2*(kWarps + 1)]
-  uint32_t *bcast = scratch + 2 * (kWarps + 1);  // [6]
-  float *qs = reinterpret_cast<float *>(bcast + 6);  // [R] q_hat in fp32 (8-byte aligned: the counts before it are even)
-
-  pdl_launch_dependents();
-  for (int i = tid; i < 3 * kBins; i += kThreads) hist[i] = 0;
-  __syncthreads();
-  pdl_wait();  // everything above touched shared memory only
-  if (p.clear_word && n == 0 && rank == 0 && tid == 0) *p.clear_word = 0;
-  const int V = p.seg_len / (4 * kThreads);  // 16-byte key vectors per thread
-  const uint32_t magic = p.seg_magic;
-
-  // ---- streaming pass: scores -> keys in shared memory, pass-0 histogram on the fly -------
-  const int64_t seg_begin = (int64_t)rank * p.seg_len;
   const int lane_in_row = tid % LPR;
   const int row_in_iter = tid / LPR;
   // q_hat as fp32 pairs in shared memory: every lane of a warp reads the same pair (a broadcast)
-  if (tid < R) qs[tid] = Elt<T>::to_float(reinterpret_cast<const T *>(p.q_hat)[(int64_t)n * R + tid]);
-  __syncthreads();
   const float4 *q4 = reinterpret_cast<const float4 *>(qs + lane_in_row * EPL);
-  const char *base = reinterpret_cast<const char *>(p.A_K) + ((int64_t)n * p.a_capacity) * RB + lane_in_row * (VB * VPL);
-  int64_t seg_rows = p.candidates - seg_begin;   // rows of this segment that hold candidates
-  if (seg_rows < 0) seg_rows = 0;
-  if (seg_rows > p.seg_len) seg_rows = p.seg_len;
+  const char *base = reinterpret_cast<const char *>(A_K) + ((int64_t)n * a_capacity) * RB + lane_in_row * (VB * VPL);
   const int n_iter_rows = (int)((seg_rows + RPI * kUnroll - 1) / (RPI * kUnroll)) * (RPI * kUnroll);
   // rows past the end of the segment re-read its last row (the result is discarded), so that the
   // loop body is free of special cases
@@ -245,16 +231,117 @@ __global__ void __launch_bounds__(kThreads, 1) score_topk_kernel(ScoreTopkParams
       float acc = acc2.x + acc2.y;
 #pragma unroll
       for (int o = 1; o < LPR; o <<= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
-      if (lane_in_row == 0) {
-        uint32_t key = 0;
-        if (local < seg_rows) {
-          key = order_key(acc);
-          atomicAdd(&hist[key >> 21], 1u);
-          if (p.scores_out) p.scores_out[(int64_t)n * p.scores_stride + seg_begin + local] = acc;
-        }
-        keys[key_slot(local, V, magic)] = key;
+      if (lane_in_row == 0) sink(local, acc);
+    }
+  }
+  return n_iter_rows;
+}
+
+// Work item of the key-streaming kernel: kItemRows rows of one head.
+constexpr int kItemRows = 2048;
+
+struct ScoreKeysParams {
+  const void *A_K, *q_hat;
+  int64_t a_capacity, candidates;
+  uint32_t *keys;        // [N, keys_stride]
+  int64_t keys_stride;
+  float *scores_out;     // optional [N, scores_stride]
+  int64_t scores_stride;
+  int32_t items_per_head, n_items;
+};
+
+// Keys of every candidate row of every head into the workspace.  The items (head, run of kItemRows rows) are
+// dealt out in order, an equal share to every CTA, so all SMs stream whatever the head count is.
+template <typename T, int R>
+__global__ void __launch_bounds__(kThreads, 1) score_keys_kernel(ScoreKeysParams p) {
+  __shared__ __align__(16) float qs[R];
+  const int tid = threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int first = (int)(((int64_t)blockIdx.x * p.n_items) / gridDim.x);
+  const int last = (int)(((int64_t)(blockIdx.x + 1) * p.n_items) / gridDim.x);
+  int cur_head = -1;
+  for (int item = first; item < last; ++item) {
+    const int n = item / p.items_per_head;
+    const int64_t row0 = (int64_t)(item % p.items_per_head) * kItemRows;
+    const int64_t rows = min((int64_t)kItemRows, p.candidates - row0);
+    if (n != cur_head) {
+      __syncthreads();  // the previous head's q_hat is no longer read
+      if (tid < R) qs[tid] = Elt<T>::to_float(reinterpret_cast<const T *>(p.q_hat)[(int64_t)n * R + tid]);
+      __syncthreads();
+      cur_head = n;
+    }
+    uint32_t *kout = p.keys + (int64_t)n * p.keys_stride + row0;
+    score_rows<T, R>(p.A_K, p.a_capacity, n, row0, rows, qs, [&](int local, float acc) {
+      if (local < rows) {
+        kout[local] = order_key(acc);
+        if (p.scores_out) p.scores_out[(int64_t)n * p.scores_stride + row0 + local] = acc;
+      }
+    });
+  }
+}
+
+template <typename T, int R>
+__global__ void __launch_bounds__(kThreads, 1) score_topk_kernel(ScoreTopkParams p) {
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank();
+  const int csize = (int)cluster.num_blocks();
+  const int n = blockIdx.y;
+  const int tid = threadIdx.x;
+
+  extern __shared__ __align__(16) uint32_t smem[];
+  uint32_t *keys = smem;                       // [seg_len]
+  uint32_t *hist = keys + p.seg_len;           // [3][kBins] this CTA's histogram of each pass (peers read it)
+  uint32_t *scratch = hist + 3 * kBins;          // [2*(kWarps + 1)]
+  uint32_t *bcast = scratch + 2 * (kWarps + 1);  // [6]
+  float *qs = reinterpret_cast<float *>(bcast + 6);  // [R] q_hat in fp32 (8-byte aligned: the counts before it are even)
+
+  pdl_launch_dependents();
+  for (int i = tid; i < 3 * kBins; i += kThreads) hist[i] = 0;
+  __syncthreads();
+  pdl_wait();  // everything above touched shared memory only
+  if (p.clear_word && n == 0 && rank == 0 && tid == 0) *p.clear_word = 0;
+  const int V = p.seg_len / (4 * kThreads);  // 16-byte key vectors per thread
+  const uint32_t magic = p.seg_magic;
+
+  // ---- streaming pass: scores -> keys in shared memory, pass-0 histogram on the fly -------
+  const int64_t seg_begin = (int64_t)rank * p.seg_len;
+  int64_t seg_rows = p.candidates - seg_begin;   // rows of this segment that hold candidates
+  if (seg_rows < 0) seg_rows = 0;
+  if (seg_rows > p.seg_len) seg_rows = p.seg_len;
+  int n_iter_rows;
+  if (p.keys_in != nullptr) {
+    // the keys were formed by score_keys_kernel: fetch this segment's (they sit in L2), four per thread and trip
+    const uint32_t *kin = p.keys_in + (int64_t)n * p.keys_stride + seg_begin;
+    n_iter_rows = (int)((seg_rows + 4 * kThreads - 1) / (4 * kThreads)) * (4 * kThreads);
+    for (int i0 = 4 * tid; i0 < n_iter_rows; i0 += 4 * kThreads) {
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (i0 + 3 < seg_rows) {
+        v = __ldcg(reinterpret_cast<const uint4 *>(kin + i0));
+      } else {
+        if (i0 < seg_rows) v.x = __ldcg(kin + i0);
+        if (i0 + 1 < seg_rows) v.y = __ldcg(kin + i0 + 1);
+        if (i0 + 2 < seg_rows) v.z = __ldcg(kin + i0 + 2);
+      }
+      const uint32_t kk[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        if (i0 + c < seg_rows) atomicAdd(&hist[kk[c] >> 21], 1u);
+        keys[key_slot(i0 + c, V, magic)] = i0 + c < seg_rows ? kk[c] : 0u;
       }
     }
+  } else {
+    if (tid < R) qs[tid] = Elt<T>::to_float(reinterpret_cast<const T *>(p.q_hat)[(int64_t)n * R + tid]);
+    __syncthreads();
+    n_iter_rows = score_rows<T, R>(p.A_K, p.a_capacity, n, seg_begin, seg_rows, qs, [&](int local, float acc) {
+      uint32_t key = 0;
+      if (local < seg_rows) {
+        key = order_key(acc);
+        atomicAdd(&hist[key >> 21], 1u);
+        if (p.scores_out) p.scores_out[(int64_t)n * p.scores_stride + seg_begin + local] = acc;
+      }
+      keys[key_slot(local, V, magic)] = key;
+    });
   }
   for (int i = n_iter_rows + tid; i < p.seg_len; i += kThreads) keys[key_slot(i, V, magic)] = 0;  // padding sorts last
   __syncthreads();
@@ -414,6 +501,24 @@ int launch_score_topk(const ScoreTopkParams &p, int n_heads, int csize, cudaStre
   return LRQK_OK;
 }
 
+template <typename T, int R>
+int launch_score_keys(const ScoreKeysParams &p, cudaStream_t stream) {
+  const int grid = p.n_items < kNumSMs ? p.n_items : kNumSMs;
+  LRQK_CUDA_TRY(launch_dependent(score_keys_kernel<T, R>, dim3(grid), dim3(kThreads), 0, stream, 0, p));
+  return LRQK_OK;
+}
+
+template <typename T>
+int dispatch_keys(int r, const ScoreKeysParams &p, cudaStream_t stream) {
+  switch (r) {
+    case 8: return launch_score_keys<T, 8>(p, stream);
+    case 16: return launch_score_keys<T, 16>(p, stream);
+    case 32: return launch_score_keys<T, 32>(p, stream);
+    case 64: return launch_score_keys<T, 64>(p, stream);
+    default: return LRQK_EUNSUPPORTED;
+  }
+}
+
 template <typename T>
 int dispatch_rank(int r, const ScoreTopkParams &p, int n_heads, int csize, cudaStream_t stream) {
   switch (r) {
@@ -451,17 +556,38 @@ int plan_score_topk(int64_t candidates, int n_heads, int *csize_out, int *seg_le
   return LRQK_OK;
 }
 
+// Whether the keys should be formed by the all-SM streaming kernel first: when the clusters of the one-kernel
+// plan would occupy fewer than two thirds of the SMs.
+static bool plan_wants_key_pass(int n_heads, int csize) { return n_heads * csize * 3 < kNumSMs * 2; }
+
+static int64_t keys_stride_for(int64_t rows) { return (rows + 3) / 4 * 4; }
+
 }  // namespace lrqk
 
+extern "C" size_t lrqk_score_topk_workspace_bytes(const lrqk_layer *L, int64_t max_candidates) {
+  if (!L || max_candidates <= 0 || lrqk::check_layer(L) != LRQK_OK) return 0;
+  const int n_heads = L->bsz * L->q_heads;
+  // the cluster size only grows with the candidate count, so the smallest count decides whether any call
+  // may take the two-kernel plan
+  int csize = 1, seg_len = 0;
+  if (lrqk::plan_score_topk(L->k + 1, n_heads, &csize, &seg_len) != LRQK_OK) return 0;
+  if (!lrqk::plan_wants_key_pass(n_heads, csize)) {
+    if (lrqk::plan_score_topk(max_candidates, n_heads, &csize, &seg_len) != LRQK_OK) return 0;
+    if (!lrqk::plan_wants_key_pass(n_heads, csize)) return 0;
+  }
+  return sizeof(uint32_t) * (size_t)n_heads * (size_t)lrqk::keys_stride_for(max_candidates);
+}
+
 extern "C" int lrqk_score_topk(const lrqk_layer *L, const void *q_hat, int64_t candidates, int32_t *wanted,
-                               float *scores_out, int64_t scores_stride, lrqk_stream_t stream) {
+                               float *scores_out, int64_t scores_stride, void *workspace, size_t workspace_bytes,
+                               lrqk_stream_t stream) {
   return lrqk::score_topk_enqueue(L, q_hat, candidates, wanted, scores_out, scores_stride, nullptr,
-                                  lrqk::as_stream(stream));
+                                  lrqk::as_stream(stream), nullptr, workspace, workspace_bytes);
 }
 
 int lrqk::score_topk_enqueue(const lrqk_layer *L, const void *q_hat, int64_t candidates, int32_t *wanted,
                              float *scores_out, int64_t scores_stride, int32_t *clear_word, cudaStream_t stream,
-                             const FusedDiff *diff) {
+                             const FusedDiff *diff, void *workspace, size_t workspace_bytes) {
   int rc = check_device();
   if (rc != LRQK_OK) return rc;
   rc = check_layer(L);
@@ -482,6 +608,7 @@ int lrqk::score_topk_enqueue(const lrqk_layer *L, const void *q_hat, int64_t can
   p.scores_out = scores_out;
   p.scores_stride = scores_stride;
   p.clear_word = clear_word;
+  p.keys_in = nullptr; p.keys_stride = 0;
   p.table = nullptr; p.mask = nullptr; p.miss_count = nullptr; p.miss_list = nullptr; p.list_len = nullptr; p.diff_status = nullptr;
   if (diff) {
     if (!L->table || !diff->mask || !diff->miss_count || !diff->list || !diff->list_len || !diff->status) return LRQK_EINVAL;
@@ -496,6 +623,21 @@ int lrqk::score_topk_enqueue(const lrqk_layer *L, const void *q_hat, int64_t can
   {
     const uint32_t v = (uint32_t)(seg_len / kGranule);
     p.seg_magic = (uint32_t)((0x100000000ull + v - 1) / v);
+  }
+  const int64_t kstride = keys_stride_for(candidates);
+  if (workspace && plan_wants_key_pass(n_heads, csize) &&
+      workspace_bytes >= sizeof(uint32_t) * (size_t)n_heads * (size_t)kstride) {
+    // few heads: form the keys on all SMs first, the clusters then select from the workspace
+    ScoreKeysParams kp;
+    kp.A_K = L->A_K; kp.q_hat = q_hat; kp.a_capacity = L->a_capacity; kp.candidates = candidates;
+    kp.keys = reinterpret_cast<uint32_t *>(workspace); kp.keys_stride = kstride;
+    kp.scores_out = scores_out; kp.scores_stride = scores_stride;
+    kp.items_per_head = (int32_t)ceil_div64(candidates, kItemRows);
+    kp.n_items = kp.items_per_head * n_heads;
+    LRQK_DISPATCH_DTYPE(L->dtype, T, rc = dispatch_keys<T>(L->r, kp, stream));
+    if (rc != LRQK_OK) return rc;
+    p.keys_in = kp.keys; p.keys_stride = kstride;
+    p.scores_out = nullptr;
   }
   LRQK_DISPATCH_DTYPE(L->dtype, T, return dispatch_rank<T>(L->r, p, n_heads, csize, stream));
   return LRQK_EUNSUPPORTED;

@@ -501,6 +501,7 @@ class LightAttentionIndicesFactory:
             grown[:, :, :self.current_len].copy_(st.A_K[:, :, :self.current_len])
             st.A_K = grown
             st._rebuild_struct()
+            st._size_score_ws()
         if st.host.current_len + self.num_lite_tokens >= st.host.capacity:
             torch.cuda.synchronize()
             new_cap = st.host.capacity

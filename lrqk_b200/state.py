@@ -145,6 +145,13 @@ class LayerState:
         self.attn_ws = torch.zeros((max(nb, 16),), dtype=torch.uint8, device=self.device)
         self._step_args = None
         self._qkv_in = None
+        self._size_score_ws()
+
+    def _size_score_ws(self):
+        """Scratch of the scoring stage's two-kernel plan (few heads); empty where one kernel is the plan."""
+        nb = self.lib.lrqk_score_topk_workspace_bytes(C.byref(self.c), self.A_K.shape[2])
+        self.score_ws = torch.empty((nb,), dtype=torch.uint8, device=self.device) if nb else None
+        self._step_args = None
 
     def _rebuild_struct(self):
         c = _lib.Layer()
@@ -188,8 +195,10 @@ class LayerState:
         if scores_out is not None:
             assert scores_out.dtype == torch.float32 and scores_out.is_contiguous()
             stride = scores_out.shape[-1]
+        ws = self.score_ws
         _lib.check(self.lib.lrqk_score_topk(C.byref(self.c), _ptr(q_hat), candidates, _ptr(self.wanted),
-                                            _ptr(scores_out), stride, _stream()), "lrqk_score_topk")
+                                            _ptr(scores_out), stride, _ptr(ws), 0 if ws is None else ws.numel(),
+                                            _stream()), "lrqk_score_topk")
         return self.wanted
 
     def slot_diff(self, wanted: Optional[torch.Tensor] = None):
@@ -229,6 +238,8 @@ class LayerState:
             a.miss_count, a.miss_list = self.miss_count.data_ptr(), self.miss_list.data_ptr()
             a.counters = self.counters.data_ptr()
             a.project_workspace, a.attn_workspace = self.project_ws.data_ptr(), self.attn_ws.data_ptr()
+            a.score_workspace = None if self.score_ws is None else self.score_ws.data_ptr()
+            a.score_workspace_bytes = 0 if self.score_ws is None else self.score_ws.numel()
             self._attn_out_ptr, self._default_scale = self.attn_out.data_ptr(), self.head_dim ** -0.5
         a.q, a.k_new, a.v_new = q.data_ptr(), k_new.data_ptr(), v_new.data_ptr()
         a.attn_out = self._attn_out_ptr if attention else None

@@ -36,7 +36,7 @@ def test_no_cpu_fallback():
     lib = _lib.lib()
     assert lib.lrqk_device_supported() == 0
     layer = _lib.Layer()
-    assert lib.lrqk_score_topk(C.byref(layer), None, 10, None, None, 0, None) == _lib.ENODEVICE
+    assert lib.lrqk_score_topk(C.byref(layer), None, 10, None, None, 0, None, 0, None) == _lib.ENODEVICE
     assert lib.lrqk_layer_step(None, None, None) == _lib.EINVAL
     from lrqk_b200 import LightAttentionIndicesFactory
     fac = LightAttentionIndicesFactory(num_lite_tokens=4, attn_topk=8, r=8)

@@ -69,6 +69,28 @@ def test_score_topk_matches_oracle(dtype, r, bsz, hq, cand, k):
         assert np.array_equal(scores.numpy().view(np.uint32), canon.view(np.uint32)), "summation order drifted"
 
 
+@pytest.mark.parametrize("r,hq,cand,k", [(32, 4, 131007, 2048), (16, 3, 70001, 1024), (64, 2, 9000, 64), (32, 8, 20000, 512)])
+def test_score_topk_one_and_two_kernel_plans_agree(r, hq, cand, k):
+    """With few heads the keys are formed by a separate all-SM kernel into a workspace (the state sizes one
+    when that plan applies); without a workspace the clusters score their own segments.  Same scores, same
+    selection, bit for bit."""
+    g = torch.Generator().manual_seed(cand)
+    st = _state(bsz=1, q_heads=hq, kv_heads=hq, head_dim=128, r=r, k=k, m=4, a_capacity=cand + 5,
+                host_capacity=16, dtype=torch.bfloat16, with_host=False)
+    assert st.score_ws is not None, "this shape is meant to take the two-kernel plan"
+    st.A_K.copy_(torch.randn(1, hq, cand + 5, r, generator=g).to(torch.bfloat16))
+    st.A_K[:, 0].copy_((st.A_K[:, 0].float() * 2).round() / 2)            # a head with ties at the cut
+    qh = torch.randn(1, hq, r, generator=g).to(torch.bfloat16).cuda()
+    s2 = torch.full((1, hq, cand), float("nan"), device="cuda")
+    two = st.score_topk(qh, cand, scores_out=s2).clone()
+    ws, st.score_ws = st.score_ws, None
+    s1 = torch.full((1, hq, cand), float("nan"), device="cuda")
+    one = st.score_topk(qh, cand, scores_out=s1).clone()
+    st.score_ws = ws
+    assert torch.equal(s1.view(torch.int32), s2.view(torch.int32)) and torch.equal(one, two)
+    assert np.array_equal(two.cpu().numpy(), orc.topk_sorted(s2.cpu(), k))
+
+
 def test_score_topk_heavy_ties():
     # scores restricted to a handful of values: the tie rule decides almost every pick
     g = torch.Generator().manual_seed(5)
