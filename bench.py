@@ -235,8 +235,8 @@ def run_ours(args):
     def layer(fac, q, k, v):
         """One layer-step; with several ranks, every rank ends up with the rows of all heads."""
         if exchange is not None:
-            out = fac.decode_attend_push(q, k, v, exchange)   # the attention epilogue stores into every rank's buffer
-            exchange.wait()
+            # ONE call: the attention epilogue stores into every rank's buffer, then the bounded wait for all rows
+            out = fac.decode_attend_push(q, k, v, exchange)
         else:
             out = fac.decode_attend(q, k, v)
             if world > 1 and args.collective == "nccl":
@@ -371,7 +371,7 @@ def run_ours(args):
     tcur += 1
     if exchange is not None:    # the rows the push delivered against a library all-gather of the same outputs
         out = facs[0].decode_attend_push(q_all[tcur, 0], k_all[tcur, 0], v_all[tcur, 0], exchange)
-        rows = exchange.wait().clone()
+        rows = exchange.rows().clone()
         ref = torch.empty_like(rows)
         dist.all_gather_into_tensor(ref, out.reshape(-1, w["d"]).contiguous())
         torch.cuda.synchronize()
@@ -451,7 +451,9 @@ def run_ours(args):
         "host_issue_us_per_layer_step": round(host_issue_us, 1),
         # per layer-step: projection, update, scoring(+diff), miss fetch, attention (+ exchange wait);
         # plus one ring-flush kernel per layer every m steps
-        "gpu_launches": int(args.steps * layers * (5 + (1 if exchange is not None else 0)) + layers * (args.steps // w["m"])),
+        "gpu_launches": int(args.steps * layers * (5 + (1 if exchange is not None else 0)
+                                                   + (1 if facs[0].state.score_ws is not None else 0))
+                            + layers * (args.steps // w["m"])),
         "roofline": roof, "roofline_hbm": roof_hbm, "roofline_step": roof_step,
         "roofline_step_by_rho": dict(sorted(by_rho.items())), "kernels": per_kernel, "per_rank": per_rank,
         "host_link_peak_gbs": round(link_peak, 1), "clocks": clocks,

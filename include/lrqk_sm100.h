@@ -119,8 +119,12 @@ int lrqk_lite_append(const lrqk_layer *L, const void *k_new, const void *v_new, 
  * read from the capacity buffer, so the row of the token being appended reads as zero.
  * The early exit "mse(k_hat, k_hat') < tol" is a mean over ALL heads, as in the
  * reference (:603-609); it is evaluated on the device, without a host round trip.
+ * Status: the bounded waits of the kernel (bulk copies of the resident keys, tensor-core completion)
+ * record LRQK_ETIMEOUT in the int32 word lrqk_decode_project_update_status_word() points at (the last
+ * 16 bytes of the workspace); zero-fill the workspace before its first use.
  * ---------------------------------------------------------------------------------- */
 size_t lrqk_decode_project_update_workspace_bytes(const lrqk_layer *L, int32_t max_iter);
+int32_t *lrqk_decode_project_update_status_word(const lrqk_layer *L, int32_t max_iter, void *workspace);
 int lrqk_decode_project_update(const lrqk_layer *L, const void *q, const void *k_new, int32_t max_iter,
                                float tol, int64_t append_row, void *q_hat, int32_t *iters_out,
                                void *workspace, lrqk_stream_t stream);
@@ -174,8 +178,12 @@ int lrqk_miss_gather(const lrqk_layer *L, const lrqk_miss *list, const int32_t *
  * (lrqk_attention.py:2326-2327; Qwen2/Mistral :2205-2216, :2438-2449).
  *   q   : [B,Hq,d];  out : [B,Hq,d] in L->dtype;  scale: 1/sqrt(d) in the reference
  *   workspace must be zero-filled before its first use; the kernel leaves it reusable.
+ *   Status: the kernel's one bounded wait (for the bulk copy of its keys) records LRQK_ETIMEOUT in the int32
+ *   word that lrqk_flash_decode_status_word() points at (inside the workspace); it stays set until the
+ *   caller clears it.  lrqk_layer_step uses the same word.
  * ---------------------------------------------------------------------------------- */
 size_t lrqk_flash_decode_workspace_bytes(const lrqk_layer *L, int32_t rows);
+int32_t *lrqk_flash_decode_status_word(const lrqk_layer *L, void *workspace);
 int lrqk_flash_decode(const lrqk_layer *L, const void *q, void *out, int32_t rows, float scale,
                       void *workspace, lrqk_stream_t stream);
 
@@ -196,8 +204,13 @@ int lrqk_flash_decode(const lrqk_layer *L, const void *q, void *out, int32_t row
  *   - All calls share the one array and it keeps the previous call's contents; the entry clears
  *     the part that must start at zero on `stream` before launching.  Two calls that can overlap
  *     on the GPU (different streams, no ordering between them) race on it: serialise them.
+ *   - Status: like lrqk_flash_decode, a bounded wait that runs out leaves LRQK_ETIMEOUT in a word of the
+ *     scratch; the next call clears it.  lrqk_flash_decode_static_status() copies the word of the last call
+ *     on the current device to `status_out` (host memory, page-locked if the copy is to be asynchronous)
+ *     on `stream`; read it after synchronising that stream.  It allocates nothing either.
  * ---------------------------------------------------------------------------------- */
 size_t lrqk_flash_decode_static_capacity_bytes(void);
+int lrqk_flash_decode_static_status(int32_t *status_out, lrqk_stream_t stream);
 int lrqk_flash_decode_static(const lrqk_layer *L, const void *q, void *out, int32_t rows, float scale,
                              lrqk_stream_t stream);
 
@@ -242,7 +255,8 @@ int lrqk_flash_decode_push(const lrqk_layer *L, const void *q, void *out, int32_
 /* Wait (bounded) until push `seq` of every rank has arrived in this rank's buffer, then copy the
  * gathered rows [world][heads_per_rank][d] to gathered_out if it is not NULL.  If the wait runs
  * out, *status (device int32) is set to LRQK_ETIMEOUT and the copy is skipped; the kernel always
- * returns, so the stream and the context stay usable. */
+ * returns, so the stream and the context stay usable.  In that case gathered_out is filled with NaNs
+ * (all-ones bit patterns) instead of being left as it was. */
 int lrqk_allgather_wait(const lrqk_peer_group *g, int32_t seq, void *gathered_out, int32_t *status,
                         lrqk_stream_t stream);
 /* How often lrqk_allgather_wait polls an arrival word (about 1 us per poll) before it gives up;
@@ -281,6 +295,9 @@ typedef struct lrqk_step_args {
   int32_t push_seq;       /* sequence number of this push (see lrqk_flash_decode_push)  */
   void *score_workspace;  /* NULL, or scratch of lrqk_score_topk_workspace_bytes() for the scoring stage */
   size_t score_workspace_bytes;
+  void *gathered_out;     /* with peers: where lrqk_allgather_wait puts all ranks' rows (may be NULL)          */
+  int32_t *wait_status;   /* with peers: non-NULL makes the step end with lrqk_allgather_wait(peers, push_seq,
+                             gathered_out, wait_status), so a head-sharded layer-step is ONE call              */
 } lrqk_step_args;
 
 int lrqk_layer_step(const lrqk_layer *L, const lrqk_step_args *a, lrqk_stream_t stream);

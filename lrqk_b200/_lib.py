@@ -50,6 +50,7 @@ class StepArgs(C.Structure):
         ("project_workspace", C.c_void_p), ("attn_workspace", C.c_void_p),
         ("peers", C.c_void_p), ("push_seq", C.c_int32),
         ("score_workspace", C.c_void_p), ("score_workspace_bytes", C.c_size_t),
+        ("gathered_out", C.c_void_p), ("wait_status", C.c_void_p),
     ]
 
 
@@ -88,6 +89,9 @@ _SIGNATURES = {
     "lrqk_flash_decode": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_void_p, C.c_int32, C.c_float, C.c_void_p,
                                     C.c_void_p]),
     "lrqk_flash_decode_static_capacity_bytes": (C.c_size_t, []),
+    "lrqk_flash_decode_static_status": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "lrqk_flash_decode_status_word": (C.c_void_p, [C.POINTER(Layer), C.c_void_p]),
+    "lrqk_decode_project_update_status_word": (C.c_void_p, [C.POINTER(Layer), C.c_int32, C.c_void_p]),
     "lrqk_flash_decode_static": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_void_p, C.c_int32, C.c_float,
                                            C.c_void_p]),
     "lrqk_peer_buffer_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),

@@ -378,6 +378,7 @@ namespace {
 constexpr size_t kStaticScratchBytes = 4u << 20;  // 4 MiB: e.g. 470 heads of head_dim 128 at 2112 bf16 rows (17 splits)
 static __device__ __align__(256) unsigned char g_static_attn_scratch[kStaticScratchBytes];
 static void *g_static_scratch_ptr[lrqk::kMaxDevices] = {};  // device-usable address, per device
+static int g_static_last_heads[lrqk::kMaxDevices] = {};      // head count of the last call: where its status word sits
 }  // namespace
 }  // namespace lrqk
 
@@ -414,5 +415,26 @@ extern "C" int lrqk_flash_decode_static(const lrqk_layer *L, const void *q, void
   cudaStream_t s = as_stream(stream);
   // the array keeps whatever the previous call left: the tickets and the status word must start at zero
   LRQK_CUDA_TRY(cudaMemsetAsync(scratch, 0, ticket_bytes, s));
+  g_static_last_heads[dev] = n_heads;
   return launch_flash_decode(L, q, out, rows, scale, scratch, s);
+}
+
+extern "C" int lrqk_flash_decode_static_status(int32_t *status_out, lrqk_stream_t stream) {
+  using namespace lrqk;
+  if (!status_out) return LRQK_EINVAL;
+  int dev = -1;
+  LRQK_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= lrqk::kMaxDevices) return LRQK_EUNSUPPORTED;
+  if (!g_static_scratch_ptr[dev]) {  // no call on this device yet: nothing to report
+    *status_out = 0;
+    return LRQK_OK;
+  }
+  const int32_t *word = reinterpret_cast<const int32_t *>(g_static_scratch_ptr[dev]) + g_static_last_heads[dev];
+  LRQK_CUDA_TRY(cudaMemcpyAsync(status_out, word, sizeof(int32_t), cudaMemcpyDeviceToHost, as_stream(stream)));
+  return LRQK_OK;
+}
+
+extern "C" int32_t *lrqk_flash_decode_status_word(const lrqk_layer *L, void *workspace) {
+  if (!L || !workspace || L->bsz <= 0 || L->q_heads <= 0) return nullptr;
+  return reinterpret_cast<int32_t *>(workspace) + (size_t)L->bsz * L->q_heads;
 }

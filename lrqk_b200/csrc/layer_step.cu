@@ -35,6 +35,10 @@ extern "C" int lrqk_layer_step(const lrqk_layer *L, const lrqk_step_args *a, lrq
     rc = lrqk_flash_decode_push(L, a->q, a->attn_out, L->k + L->m, a->scale, a->attn_workspace, a->peers, a->push_seq,
                                 stream);
     if (rc != LRQK_OK) return rc;
+    if (a->wait_status) {  // ... and the wait for every rank's rows of this push, in the same call
+      rc = lrqk_allgather_wait(a->peers, a->push_seq, a->gathered_out, a->wait_status, stream);
+      if (rc != LRQK_OK) return rc;
+    }
   } else if (a->attn_out) {
     rc = lrqk_flash_decode(L, a->q, a->attn_out, L->k + L->m, a->scale, a->attn_workspace, stream);
     if (rc != LRQK_OK) return rc;

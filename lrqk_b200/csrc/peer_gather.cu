@@ -41,7 +41,13 @@ __global__ void __launch_bounds__(256) allgather_wait_kernel(WaitParams p) {
     }
   }
   __syncthreads();
-  if (!ok || !p.out) return;
+  if (!p.out) return;
+  if (!ok) {
+    // the rows did not arrive: hand out NaNs (all-ones bit patterns in either dtype) rather than leave the
+    // previous step's rows in place, so that a caller that does not look at the status word cannot miss it
+    for (int i = threadIdx.x; i < p.vecs; i += blockDim.x) p.out[i] = make_uint4(~0u, ~0u, ~0u, ~0u);
+    return;
+  }
   for (int i = threadIdx.x; i < p.vecs; i += blockDim.x) p.out[i] = p.data[i];
 }
 

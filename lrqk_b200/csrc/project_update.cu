@@ -1054,6 +1054,11 @@ extern "C" size_t lrqk_decode_project_update_workspace_bytes(const lrqk_layer *L
   return project_iterates_bytes(L, max_iter < 1 ? 1 : max_iter) + 16;
 }
 
+extern "C" int32_t *lrqk_decode_project_update_status_word(const lrqk_layer *L, int32_t max_iter, void *workspace) {
+  if (!L || !workspace || max_iter < 0) return nullptr;
+  return reinterpret_cast<int32_t *>(reinterpret_cast<char *>(workspace) + project_iterates_bytes(L, max_iter < 1 ? 1 : max_iter));
+}
+
 extern "C" int lrqk_decode_project_update(const lrqk_layer *L, const void *q, const void *k_new, int32_t max_iter,
                                           float tol, int64_t append_row, void *q_hat, int32_t *iters_out,
                                           void *workspace, lrqk_stream_t stream) {

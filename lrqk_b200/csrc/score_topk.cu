@@ -5,10 +5,12 @@
 // segment once from HBM with 32-byte evict-first loads, forms the fp32 dot product with q_hat
 // and keeps the scores -- as order-preserving 32-bit keys -- in shared memory; they never
 // travel to global memory.  The k-th largest key is then found by a three-pass (11+11+10 bit)
-// radix select: every CTA builds the histogram of its own keys, and after ONE cluster barrier
-// per pass each CTA reads its peers' histograms through distributed shared memory, so that it
-// knows both the cluster totals (which digit holds the k-th key) and how many of the larger
-// keys sit in lower-ranked CTAs (where its own output starts).  No further exchange is needed:
+// radix select: every CTA builds the histogram of its own keys and exchanges it with its peers
+// through distributed shared memory -- added into a cluster-wide histogram kept by every CTA where
+// few bins are occupied, read from the peers where nearly all are -- so that after ONE cluster
+// barrier per pass each CTA knows both the cluster totals (which digit holds the k-th key) and
+// how many of the larger keys sit in lower-ranked CTAs (where its own output starts).  No further
+// exchange is needed:
 // every thread owns a contiguous run of keys, walks it once after the first pass (two bit masks:
 // "above the digit", "equal to it"), and the later passes and the ordered, ascending compaction
 // only revisit the marked keys.  Of equal scores the lower position wins.
@@ -260,17 +262,16 @@ __global__ void __launch_bounds__(kThreads, 1) score_keys_kernel(ScoreKeysParams
   pdl_wait();
   const int first = (int)(((int64_t)blockIdx.x * p.n_items) / gridDim.x);
   const int last = (int)(((int64_t)(blockIdx.x + 1) * p.n_items) / gridDim.x);
-  int cur_head = -1;
-  for (int item = first; item < last; ++item) {
+  // a CTA's items are consecutive: those of one head form one contiguous run of rows, streamed in one go so
+  // that the prefetch pipeline never drains inside it (at most two or three runs per CTA)
+  for (int item = first; item < last;) {
     const int n = item / p.items_per_head;
+    const int run_end = min(last, (n + 1) * p.items_per_head);
     const int64_t row0 = (int64_t)(item % p.items_per_head) * kItemRows;
-    const int64_t rows = min((int64_t)kItemRows, p.candidates - row0);
-    if (n != cur_head) {
-      __syncthreads();  // the previous head's q_hat is no longer read
-      if (tid < R) qs[tid] = Elt<T>::to_float(reinterpret_cast<const T *>(p.q_hat)[(int64_t)n * R + tid]);
-      __syncthreads();
-      cur_head = n;
-    }
+    const int64_t rows = min((int64_t)(run_end - item) * kItemRows, p.candidates - row0);
+    __syncthreads();  // the previous head's q_hat is no longer read
+    if (tid < R) qs[tid] = Elt<T>::to_float(reinterpret_cast<const T *>(p.q_hat)[(int64_t)n * R + tid]);
+    __syncthreads();
     uint32_t *kout = p.keys + (int64_t)n * p.keys_stride + row0;
     score_rows<T, R>(p.A_K, p.a_capacity, n, row0, rows, qs, [&](int local, float acc) {
       if (local < rows) {
@@ -278,6 +279,7 @@ __global__ void __launch_bounds__(kThreads, 1) score_keys_kernel(ScoreKeysParams
         if (p.scores_out) p.scores_out[(int64_t)n * p.scores_stride + row0 + local] = acc;
       }
     });
+    item = run_end;
   }
 }
 
@@ -291,14 +293,16 @@ __global__ void __launch_bounds__(kThreads, 1) score_topk_kernel(ScoreTopkParams
 
   extern __shared__ __align__(16) uint32_t smem[];
   uint32_t *keys = smem;                       // [seg_len]
-  uint32_t *hist = keys + p.seg_len;           // [3][kBins] this CTA's histogram of each pass (peers read it)
-  uint32_t *scratch = hist + 3 * kBins;          // [2*(kWarps + 1)]
-  uint32_t *bcast = scratch + 2 * (kWarps + 1);  // [6]
-  float *qs = reinterpret_cast<float *>(bcast + 6);  // [R] q_hat in fp32 (8-byte aligned: the counts before it are even)
+  uint32_t *hist = keys + p.seg_len;           // [3][kBins] this CTA's own histogram of each pass
+  uint32_t *sums = hist + 3 * kBins;           // [tot, low][kBins] cluster-wide histograms of passes 0 and 2, filled by the peers
+  uint32_t *scratch = sums + 2 * kBins;          // [2*(kWarps + 1)]
+  uint32_t *bcast = scratch + 2 * (kWarps + 1);  // [3 passes][4] (+2: keeps what follows on a 16-byte boundary)
+  float *qs = reinterpret_cast<float *>(bcast + 14);  // [R] q_hat in fp32, read as float4
 
   pdl_launch_dependents();
-  for (int i = tid; i < 3 * kBins; i += kThreads) hist[i] = 0;
-  __syncthreads();
+  for (int i = tid; i < 5 * kBins; i += kThreads) hist[i] = 0;
+  // no peer may add to this CTA's cluster-wide histograms before they are cleared
+  cluster.sync();
   pdl_wait();  // everything above touched shared memory only
   if (p.clear_word && n == 0 && rank == 0 && tid == 0) *p.clear_word = 0;
   const int V = p.seg_len / (4 * kThreads);  // 16-byte key vectors per thread
@@ -397,27 +401,80 @@ __global__ void __launch_bounds__(kThreads, 1) score_topk_kernel(ScoreTopkParams
       }
       __syncthreads();
     }
-    cluster.sync();  // every CTA's histogram of this pass is complete and visible
+    // Every CTA ADDS its histogram to the cluster-wide one held by each CTA of the cluster (remote
+    // shared-memory atomics on integers: the sums do not depend on the order), and to the "held by
+    // lower-ranked CTAs" histogram of the CTAs ranked above it.  After the barrier everything a CTA needs
+    // is in its own shared memory; nobody reads a peer's memory.  Two sets alternate; the set of pass 0
+    // is cleared again once it has been read, for pass 2.
+    // Passes 0 and 2 (a few dozen occupied bins): every CTA ADDS its histogram to the cluster-wide one held
+    // by each CTA of the cluster (remote shared-memory atomics on integers: the sums do not depend on the
+    // order), and to the "held by lower-ranked CTAs" histogram of the CTAs ranked above it; after the barrier
+    // everything a CTA needs is in its own shared memory.  Pass 1 (nearly every bin occupied) reads the peers'
+    // histograms after the barrier instead: two bins per thread and peer cost less than that many atomics.
+    uint32_t *tot_s = sums, *low_s = sums + kBins;
     uint32_t tot[2] = {0u, 0u}, low[2] = {0u, 0u};
-    for (int c = 0; c < csize; ++c) {
-      const uint2 v = *reinterpret_cast<const uint2 *>(cluster.map_shared_rank(hl, c) + 2 * tid);
-      tot[0] += v.x; tot[1] += v.y;
-      if (c < rank) { low[0] += v.x; low[1] += v.y; }
+    if (pass != 1) {
+      const uint2 own = *reinterpret_cast<const uint2 *>(hl + 2 * tid);
+      if (own.x | own.y) {
+        for (int c = 0; c < csize; ++c) {
+          uint32_t *rt = c == rank ? tot_s : cluster.map_shared_rank(tot_s, c);
+          if (own.x) atomicAdd(rt + 2 * tid, own.x);
+          if (own.y) atomicAdd(rt + 2 * tid + 1, own.y);
+          if (c > rank) {
+            uint32_t *rl = cluster.map_shared_rank(low_s, c);
+            if (own.x) atomicAdd(rl + 2 * tid, own.x);
+            if (own.y) atomicAdd(rl + 2 * tid + 1, own.y);
+          }
+        }
+      }
     }
-    if (pass == 2) cluster.barrier_arrive();  // this CTA reads no peer's memory after this point
-    const uint32_t mine = tot[0] + tot[1];
-    uint32_t inc[2] = {mine, low[0] + low[1]}, all[2];
-    block_inclusive_scan<2>(inc, scratch, all);
-    uint32_t above = all[0] - inc[0];      // keys in bins above this thread's two bins
-    uint32_t above_low = all[1] - inc[1];  // those of them held by lower-ranked CTAs
+    cluster.sync();  // every CTA's histogram of this pass is complete, its additions have arrived
+    if (pass != 1) {
+      const uint2 tv = *reinterpret_cast<const uint2 *>(tot_s + 2 * tid);
+      const uint2 lv = *reinterpret_cast<const uint2 *>(low_s + 2 * tid);
+      tot[0] = tv.x; tot[1] = tv.y; low[0] = lv.x; low[1] = lv.y;
+      if (pass == 0) {  // pass 2 uses the same arrays: clear them (the peers add to them only after the next barrier)
+        *reinterpret_cast<uint2 *>(tot_s + 2 * tid) = make_uint2(0u, 0u);
+        *reinterpret_cast<uint2 *>(low_s + 2 * tid) = make_uint2(0u, 0u);
+      }
+    } else {
+      for (int c = 0; c < csize; ++c) {
+        const uint2 v = *reinterpret_cast<const uint2 *>(cluster.map_shared_rank(hl, c) + 2 * tid);
+        tot[0] += v.x; tot[1] += v.y;
+        if (c < rank) { low[0] += v.x; low[1] += v.y; }
+      }
+    }
+    // keys in the bins ABOVE this thread's two bins, and those of them held by lower-ranked CTAs: a scan by
+    // shuffles inside the warp, the warp totals through shared memory
+    const uint32_t mine = tot[0] + tot[1], mine_low = low[0] + low[1];
+    uint32_t inc = mine, inc_low = mine_low;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t x = __shfl_up_sync(0xFFFFFFFFu, inc, o), y = __shfl_up_sync(0xFFFFFFFFu, inc_low, o);
+      if ((tid & 31) >= o) { inc += x; inc_low += y; }
+    }
+    const uint32_t warp_tot = __shfl_sync(0xFFFFFFFFu, inc, 31), warp_tot_low = __shfl_sync(0xFFFFFFFFu, inc_low, 31);
+    if ((tid & 31) == 0) { scratch[tid >> 5] = warp_tot; scratch[kWarps + (tid >> 5)] = warp_tot_low; }
+    __syncthreads();
+    uint32_t above, above_low;
+    {
+      // totals of the warps above this one: lane l holds warp l's totals, masked and summed
+      const int lane = tid & 31, wp = tid >> 5;
+      uint32_t a = lane > wp ? scratch[lane] : 0u, al = lane > wp ? scratch[kWarps + lane] : 0u;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) { a += __shfl_xor_sync(0xFFFFFFFFu, a, o); al += __shfl_xor_sync(0xFFFFFFFFu, al, o); }
+      above = a + (warp_tot - inc);
+      above_low = al + (warp_tot_low - inc_low);
+    }
+    uint32_t *bc = bcast + 4 * pass;
     if (above < need && need <= above + mine) {
 #pragma unroll
       for (int j = 1; j >= 0; --j) {
         if (above + tot[j] >= need) {
-          bcast[0] = (uint32_t)(2 * tid + j);
-          bcast[1] = need - above;
-          bcast[2] = above_low;
-          bcast[3] = low[j];
+          bc[0] = (uint32_t)(2 * tid + j);
+          bc[1] = need - above;
+          bc[2] = above_low;
+          bc[3] = low[j];
           break;
         }
         above += tot[j];
@@ -425,17 +482,16 @@ __global__ void __launch_bounds__(kThreads, 1) score_topk_kernel(ScoreTopkParams
       }
     }
     __syncthreads();
-    prefix = (prefix << bits) | bcast[0];
-    need = bcast[1];
-    out_base += bcast[2];
+    prefix = (prefix << bits) | bc[0];
+    need = bc[1];
+    out_base += bc[2];
     if (pass == 2) {
-      const uint32_t ties_low = bcast[3];          // keys equal to the threshold in lower-ranked CTAs
-      const uint32_t ties_mine = hl[bcast[0]];
+      const uint32_t ties_low = bc[3];          // keys equal to the threshold in lower-ranked CTAs
+      const uint32_t ties_mine = hl[bc[0]];
       const uint32_t left = need > ties_low ? need - ties_low : 0u;
       quota = ties_mine < left ? ties_mine : left;
       out_base += ties_low < need ? ties_low : need;
     }
-    __syncthreads();  // bcast is rewritten by the next pass
   }
   const uint32_t T_key = prefix;  // the k-th largest key
 
@@ -475,7 +531,6 @@ __global__ void __launch_bounds__(kThreads, 1) score_topk_kernel(ScoreTopkParams
       e_at += is_e ? 1u : 0u;
     }
   }
-  cluster.barrier_wait();  // peers may still be reading this CTA's histograms
   if (p.table != nullptr) {
     // fused hit/miss difference: once every CTA of the cluster has written its part of `wanted`
     // (release/acquire through the cluster barrier), the first CTA diffs the head's wanted set
@@ -490,7 +545,8 @@ __global__ void __launch_bounds__(kThreads, 1) score_topk_kernel(ScoreTopkParams
 
 template <typename T, int R>
 int launch_score_topk(const ScoreTopkParams &p, int n_heads, int csize, cudaStream_t stream) {
-  size_t smem = ((size_t)p.seg_len + 3 * kBins + 2 * (kWarps + 1) + 6 + R) * sizeof(uint32_t);
+  size_t smem = ((size_t)p.seg_len + 5 * kBins + 2 * (kWarps + 1) + 14 + R) * sizeof(uint32_t);
+  static_assert((5 * kBins + 2 * (kWarps + 1) + 14) % 4 == 0, "q_hat must start on a 16-byte boundary");
   if (p.table != nullptr && slot_diff_smem_bytes(p.k) > smem) smem = slot_diff_smem_bytes(p.k);
   auto kern = score_topk_kernel<T, R>;
   static SmemOptIn opt_in;
@@ -541,7 +597,7 @@ int dispatch_rank(int r, const ScoreTopkParams &p, int n_heads, int csize, cudaS
 static int kMaxResident(int cs) { return cs >= 8 ? 15 * 8 : (cs == 4 ? 36 * 4 : kNumSMs); }
 
 int plan_score_topk(int64_t candidates, int n_heads, int *csize_out, int *seg_len_out) {
-  const int64_t max_seg = 49152;  // 192 KiB of keys next to the histograms
+  const int64_t max_seg = 45056;  // 176 KiB of keys next to the histograms (40 KiB)
   int best = -1;
   for (int cs = 1; cs <= 16; cs *= 2) {
     const int64_t seg = ceil_div64(ceil_div64(candidates, cs), kGranule) * kGranule;
@@ -557,8 +613,9 @@ int plan_score_topk(int64_t candidates, int n_heads, int *csize_out, int *seg_le
 }
 
 // Whether the keys should be formed by the all-SM streaming kernel first: when the clusters of the one-kernel
-// plan would occupy fewer than two thirds of the SMs.
-static bool plan_wants_key_pass(int n_heads, int csize) { return n_heads * csize * 3 < kNumSMs * 2; }
+// plan would occupy less than a quarter of the SMs (measured: with 8 or more heads at 131072 rows the one
+// kernel is the quicker plan).
+static bool plan_wants_key_pass(int n_heads, int csize) { return n_heads * csize * 4 < kNumSMs; }
 
 static int64_t keys_stride_for(int64_t rows) { return (rows + 3) / 4 * 4; }
 

@@ -236,8 +236,9 @@ def load_model(model_name: str, lrqk=True, max_length=None, device=None, yarn=No
     if yarn is None:
         yarn = {}
     if device is None:
-        warnings.warn("When device is None, device_map=auto is used. Only single-GPU placement is tested; "
-                      "specify one device explicitly.")
+        warnings.warn("When device is None, device_map=auto is used: layers may land on several GPUs.  Each layer's "
+                      "LRQK state then lives on, and runs with, that layer's device; name one device to keep the "
+                      "model on a single GPU.")
     if lrqk:
         model = load_model_hack(model_name, device, yarn=yarn, base_model=base_model)
     elif base_model is not None:

@@ -26,7 +26,7 @@ from typing import Dict, List, Optional, Tuple, Union
 import torch
 
 from . import _lib
-from .state import HostStore, LayerState, _ptr, _stream
+from .state import HostStore, LayerState, _ptr, _stream, on_device
 
 try:  # HF is only needed for the Cache base class
     from transformers import cache_utils as _cache_utils
@@ -398,6 +398,10 @@ class LightAttentionIndicesFactory:
 
     @torch.no_grad()
     def prefill(self, query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor):
+        with on_device(query_states.device):
+            return self._prefill(query_states, key_states, value_states)
+
+    def _prefill(self, query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor):
         bsz, hq, seq_len, d = query_states.shape
         hkv = key_states.shape[1]
         assert seq_len >= self.attn_topk, "seq_len must be larger than attn_topk"
@@ -541,6 +545,13 @@ class LightAttentionIndicesFactory:
         st = self.state
         if st is None:
             raise RuntimeError("decode before prefill")
+        if query_states.device != st.device:
+            raise ValueError(f"this layer's state lives on {st.device}, the step's tensors on {query_states.device}")
+        with on_device(st.device):
+            return self._decode_on_device(query_states, key_states, value_states, attention, exchange)
+
+    def _decode_on_device(self, query_states, key_states, value_states, attention: bool, exchange=None):
+        st = self.state
         self._reserve()
         q = self._flat(query_states.to(st.dtype), st.q_heads)
         k = self._flat(key_states.to(st.dtype), st.kv_heads)
@@ -562,8 +573,12 @@ class LightAttentionIndicesFactory:
         if not self._hook:
             args = st.make_step_args(q, k, v, slot, position, flush_rows, host_row, candidates,
                                      self.max_iter[1], self.tol[1], attention=attention)
-            if exchange is not None:
+            if exchange is not None:      # push, and the wait for all ranks' rows, in the same call
                 args.peers, args.push_seq = exchange.struct_ptr(), exchange.seq.next_push()
+                args.gathered_out, args.wait_status = exchange.gathered.data_ptr(), exchange.status.data_ptr()
+                exchange.seq.next_wait()
+            else:
+                args.gathered_out = args.wait_status = None
             st.layer_step(args)
         else:
             if exchange is not None:
@@ -606,8 +621,9 @@ class LightAttentionIndicesFactory:
     def decode_attend_push(self, query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor,
                            exchange) -> torch.Tensor:
         """decode_attend for a head-sharded layer: the attention kernel also stores this rank's rows
-        into every rank's exchange buffer (``exchange``: a sharding.HeadExchange).  Follow it with
-        ``exchange.wait()`` to obtain all ranks' rows."""
+        into every rank's exchange buffer (``exchange``: a sharding.HeadExchange), and the same call
+        enqueues the bounded wait for all ranks' rows, which are then in ``exchange.gathered``
+        ([world, heads_per_rank, d]); ``exchange.rows()`` returns them."""
         st = self._decode(query_states, key_states, value_states, attention=True, exchange=exchange)
         return st.attn_out.unsqueeze(2)
 
@@ -770,8 +786,27 @@ class DynamicLRQKCache(_CacheBase):
         fac.decode_attend_push(q, k, v, exchange)
         return self.sharding.gather_step(bsz, kv_heads, q_heads).unsqueeze(2)
 
-    def close(self):
-        """Free every layer's device and page-locked host memory and the exchange buffers."""
+    def check_status(self) -> None:
+        """Synchronising check of every layer's device-side status words (the hit/miss difference's mismatch flag,
+        the bounded waits of the attention and projection kernels) and of the exchange's arrival wait; raises
+        LrqkError for the first that is set.  Off the hot path: ``close()`` calls it, a serving loop may call it
+        once per request."""
+        for fac in self.lwattn.values():
+            if fac.state is not None:
+                fac.state.check_status()
+        if self.sharding is not None and self.sharding._exchange is not None:
+            self.sharding._exchange.check_status()
+
+    def close(self, check: bool = True):
+        """Free every layer's device and page-locked host memory and the exchange buffers (after a last look at
+        the status words, unless ``check=False``)."""
+        try:
+            if check:
+                self.check_status()
+        finally:
+            self._free()
+
+    def _free(self):
         for fac in self.lwattn.values():
             fac.close()
         if self.sharding is not None:

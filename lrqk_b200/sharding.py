@@ -198,9 +198,10 @@ class HeadSharding:
         return ex
 
     def gather_step(self, bsz: int, kv_heads: int, q_heads: int) -> torch.Tensor:
-        """Wait for the outstanding push of this layer; returns the rows of all heads [B, Hq, d]."""
+        """The rows of all heads [B, Hq, d] of this layer's push (the wait was enqueued with the step; it is
+        enqueued here if the push came from the stage-by-stage path)."""
         ex = self._exchange
-        rows = ex.wait()
+        rows = ex.rows()
         s = self.shard(bsz, kv_heads)
         return self._assemble(rows.view(self.world, s.bsz, -1, ex.head_dim), bsz, kv_heads, q_heads)
 
@@ -309,6 +310,11 @@ class HeadExchange:
         _lib.check(self.lib.lrqk_allgather_wait(C.byref(self.c), seq, out, C.c_void_p(self.status.data_ptr()), stream),
                    "lrqk_allgather_wait")
         return self.gathered
+
+    def rows(self) -> torch.Tensor:
+        """All ranks' rows of the last push [world, heads_per_rank, d]; enqueues the wait if the push has not
+        been waited for yet."""
+        return self.gathered if self.seq.waited == self.seq.issued else self.wait()
 
     def check_status(self) -> None:
         """Synchronising check of the device status word (call it off the hot path)."""

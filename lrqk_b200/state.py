@@ -9,6 +9,7 @@ into ``liblrqk_sm100.so``.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes as C
 from typing import Optional
 
@@ -107,6 +108,17 @@ class HostStore:
             pass
 
 
+_SAME_DEVICE = contextlib.nullcontext()
+
+
+def on_device(device: torch.device):
+    """Context in which `device` is the current CUDA device (nothing to do when it already is).  Every entry
+    of the library launches on the CURRENT device, so state that lives on another one must make it current."""
+    if device.index is None or torch.cuda.current_device() == device.index:
+        return _SAME_DEVICE
+    return torch.cuda.device(device)
+
+
 class LayerState:
     def __init__(self, bsz: int, q_heads: int, kv_heads: int, head_dim: int, r: int, k: int, m: int,
                  a_capacity: int, host_capacity: int, dtype: torch.dtype, device="cuda", max_iter: int = 2,
@@ -119,6 +131,8 @@ class LayerState:
         self.bsz, self.q_heads, self.kv_heads, self.head_dim = bsz, q_heads, kv_heads, head_dim
         self.r, self.k, self.m = r, k, m
         self.dtype, self.device = dtype, torch.device(device)
+        if self.device.type == "cuda" and self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
         n = bsz * q_heads
         z = dict(dtype=dtype, device=self.device)
         self.A_K = torch.zeros((bsz, q_heads, a_capacity, r), **z)          # zero-initialised (:888)
@@ -286,6 +300,24 @@ class LayerState:
         self._chk(values, (self.bsz, self.kv_heads, s, self.head_dim), "values")
         _lib.check(self.lib.lrqk_prefill_fill_resident(C.byref(self.c), _ptr(keys), _ptr(values), s, _stream()),
                    "lrqk_prefill_fill_resident")
+
+    # ---- device-side status words ----------------------------------------------------------
+    def status_words(self) -> torch.Tensor:
+        """int32 [3] (a fresh device tensor): the hit/miss difference's mismatch flag, the attention kernel's
+        and the projection kernel's bounded-wait words (LRQK_ETIMEOUT when a wait ran out)."""
+        attn = self.attn_ws.view(torch.int32)[self.bsz * self.q_heads]
+        proj = self.project_ws.view(torch.int32)[(self.project_ws.numel() - 16) // 4]
+        return torch.stack([self.counters[1], attn, proj])
+
+    def check_status(self) -> None:
+        """Synchronising check of the words above; raises LrqkError for the first that is set."""
+        diff, attn, proj = (int(x) for x in self.status_words().tolist())
+        if diff != 0:
+            raise _lib.LrqkError(_lib.EINVAL, "lrqk_slot_diff", "a head's evicted and missing counts differ "
+                                 "(the wanted set holds duplicates or the slot table is corrupt)")
+        for code, where in ((attn, "lrqk_flash_decode"), (proj, "lrqk_decode_project_update")):
+            if code != 0:
+                raise _lib.LrqkError(code, where, self.lib.lrqk_strerror(code).decode())
 
     def close(self):
         if self.host is not None:

@@ -77,8 +77,9 @@ def test_wait_runs_out_and_reports_without_hanging():
     _push(st, q, group[0], lib, _lib)                       # rank 1 never pushes
     assert lib.lrqk_peer_set_wait_polls(2000) == 0          # a couple of milliseconds
     try:
-        group[0].wait()
+        got = group[0].wait()
         torch.cuda.synchronize()                            # returns: the wait is bounded
+        assert bool(torch.isnan(got).all())                 # no stale rows: what did not arrive reads as NaN
         with pytest.raises(_lib.LrqkError) as e:
             group[0].check_status()
         assert e.value.code == _lib.ETIMEOUT

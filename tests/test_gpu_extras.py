@@ -9,18 +9,37 @@ import lrqk_oracle as orc
 pytestmark = pytest.mark.gpu
 
 
-def _run(factory_cls, steps=6):
+def _run(factory_cls, steps=6, device="cuda"):
     c = dict(seed=31, bsz=1, hq=4, hkv=2, seq=900, d=128, r=16, k=64, m=4)
     Q, K, V = orc.make_prompt(c["seed"], c["bsz"], c["hq"], c["hkv"], c["seq"], c["d"])
     fac = factory_cls(num_lite_tokens=c["m"], attn_topk=c["k"], num_key_value_groups=2, r=c["r"], max_iter=(2, 2),
                       tol=1e-2, capacity=c["seq"] + 64, init_aq_ak_method="top")
-    fac.prefill(Q.cuda(), K.cuda(), V.cuda())
+    fac.prefill(Q.to(device), K.to(device), V.to(device))
     outs = []
     for s in range(steps):
         q, k, v = orc.make_step(c["seed"], s, c["bsz"], c["hq"], c["hkv"], c["d"])
-        outs.append(fac.decode_attend(q.cuda(), k.cuda(), v.cuda()).clone())
-    torch.cuda.synchronize()
+        outs.append(fac.decode_attend(q.to(device), k.to(device), v.to(device)).clone())
+    torch.cuda.synchronize(device)
+    fac.state.check_status()
     return fac, outs
+
+
+def test_layers_on_two_devices_of_one_process():
+    """One process, layer states on cuda:0 and cuda:1 (what device_map="auto" does to a large model): every entry
+    runs with the state's device current, whatever the caller's current device is."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from lrqk_b200 import LightAttentionIndicesFactory
+    assert torch.cuda.current_device() == 0
+    a, outs_a = _run(LightAttentionIndicesFactory)
+    b, outs_b = _run(LightAttentionIndicesFactory, device="cuda:1")      # cuda:0 stays current throughout
+    assert torch.cuda.current_device() == 0 and b.state.device == torch.device("cuda", 1)
+    assert all(torch.equal(x.cpu(), y.cpu()) for x, y in zip(outs_a, outs_b))
+    assert torch.equal(a.state.table.cpu(), b.state.table.cpu())
+    q, k, v = orc.make_step(31, 99, 1, 4, 2, 128)
+    with pytest.raises(ValueError):
+        b.decode_attend(q.cuda(), k.cuda(), v.cuda())                   # tensors of another device are refused
+    a.close(); b.close()
 
 
 def test_offload_prefill_factory_matches_the_default_factory():

@@ -35,8 +35,12 @@ def test_static_scratch_attention_matches_workspace_attention():
             _lib.check(lib.lrqk_flash_decode_static(C.byref(st.c), C.c_void_p(q.data_ptr()),
                                                     C.c_void_p(out.data_ptr()), rows, 128 ** -0.5, stream()),
                        "lrqk_flash_decode_static")
+            status = torch.full((1,), -99, dtype=torch.int32).pin_memory()
+            _lib.check(lib.lrqk_flash_decode_static_status(C.c_void_p(status.data_ptr()), stream()),
+                       "lrqk_flash_decode_static_status")
             torch.cuda.synchronize()
             assert torch.equal(out, ref), f"{dtype} call {call}"
+            assert int(status[0]) == 0                 # no bounded wait of the call ran out
     # beyond the built-in array: a clear refusal, nothing launched
     big = LayerState(128, 64, 64, 128, 16, 24, 8, a_capacity=64, host_capacity=16, dtype=torch.bfloat16,
                      with_host=False)                       # 8192 heads x 520 bytes > 4 MiB
