@@ -338,6 +338,21 @@ int lrqk_rope_qkv(const void *qkv, const void *cos, const void *sin, int32_t cos
                   lrqk_stream_t stream);
 
 /* ------------------------------------------------------------------------------------
+ * Element-wise glue of a decoder layer around the attention call, for the decode step (one token per
+ * sequence), where every eager framework op is one launch of pure latency.  The reference leaves these to
+ * the transformers modules (LlamaRMSNorm / Qwen2RMSNorm / MistralRMSNorm forward, the residual adds of the
+ * decoder layer, `act_fn(gate_proj(x)) * up_proj(x)` of the MLP); these entries give the same rows with one
+ * launch each, rounding where those tensor ops round.
+ *   lrqk_add_rmsnorm: s = x + delta (delta may be NULL: s = x), rounded to `dtype`; optional sum_out = s;
+ *                     normed_out = weight * dtype(s * rsqrt(mean(s^2) + eps));  x, delta, outs [rows, hidden]
+ *   lrqk_swiglu     : out[r, i] = dtype(dtype(silu(gate_up[r, i])) * gate_up[r, inter + i]),
+ *                     gate_up [rows, 2 * inter] (the fused gate|up projection), out [rows, inter]
+ * ---------------------------------------------------------------------------------- */
+int lrqk_add_rmsnorm(const void *x, const void *delta, const void *weight, float eps, int32_t dtype,
+                     int32_t rows, int32_t hidden, void *sum_out, void *normed_out, lrqk_stream_t stream);
+int lrqk_swiglu(const void *gate_up, int32_t dtype, int32_t rows, int32_t inter, void *out, lrqk_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
  * Prompt-time helpers of LightAttentionIndicesFactory.prefill (lrqk_attention.py:1385-1504).
  * ---------------------------------------------------------------------------------- */
 /* K|V rows of the prompt into the host store (KVcpu.append, :1469, :959-963):

@@ -21,6 +21,7 @@ from .hf_models import (  # noqa: F401,E402
     load_model_hack,
     load_tokenizer,
     lrqk_attention_forward,
+    lrqk_decoder_layer_forward,
     patch_model,
 )
 
@@ -36,7 +37,7 @@ from .extras import (  # noqa: F401,E402
 __all__ = [
     "FullOffloadCache", "HitRateCounter", "LightAttentionIndicesOffloadPrefill", "WrapForwardTimer", "run_task",
     "tps_estimate",
-    "load_lrqk_model", "load_model", "load_model_hack", "load_tokenizer", "lrqk_attention_forward", "patch_model",
+    "load_lrqk_model", "load_model", "load_model_hack", "load_tokenizer", "lrqk_attention_forward", "lrqk_decoder_layer_forward", "patch_model",
     "AutoIncreaseTensor", "AutoIncreaseTensorSharedKV", "DynamicLRQKCache", "InitAQAK",
     "LightAttentionIndicesFactory", "LightAttentionIndicesNoHitMiss", "PreAllocatedTensor", "repeat_kv",
 ]

@@ -113,6 +113,9 @@ _SIGNATURES = {
     "lrqk_rope_qkv": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                 C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
                                 C.c_void_p]),
+    "lrqk_add_rmsnorm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int32, C.c_int32, C.c_int32,
+                                   C.c_void_p, C.c_void_p, C.c_void_p]),
+    "lrqk_swiglu": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "lrqk_kv_pack_host": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
     "lrqk_prefill_fill_resident": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "lrqk_prefill_factorize_workspace_bytes": (C.c_size_t, [C.POINTER(Layer), C.c_int64]),

@@ -187,7 +187,7 @@ struct FusedDiff {
 int score_topk_enqueue(const lrqk_layer *L, const void *q_hat, int64_t candidates, int32_t *wanted, float *scores_out,
                        int64_t scores_stride, int32_t *clear_word, cudaStream_t stream, const FusedDiff *diff = nullptr,
                        void *workspace = nullptr, size_t workspace_bytes = 0);
-int plan_score_topk(int64_t candidates, int n_heads, int *csize_out, int *seg_len_out);
+int plan_score_topk(const lrqk_layer *L, int64_t candidates, int n_heads, int *csize_out, int *seg_len_out);
 
 // lrqk_decode_project_update with extra duties for the fused step: *clear_word = 0 at the end, and --
 // when v_new is given -- the ring write of the step's key/value into lite slot `lite_slot` (position

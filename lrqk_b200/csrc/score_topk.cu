@@ -29,6 +29,8 @@
 // (partner distance 1, 2, 4, ...).
 #include <cooperative_groups.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "slot_diff.cuh"
 
@@ -41,6 +43,7 @@ constexpr int kThreads = 1024;
 constexpr int kWarps = kThreads / 32;
 constexpr int kBins = 2048;          // 11-bit digits for passes 0 and 1, 10 bits for pass 2
 constexpr int kGranule = 4096;       // segment lengths are multiples of this many rows (4 per thread)
+constexpr int kMaxSeg = 45056;       // keys a CTA holds: 176 KiB next to the histograms (40 KiB)
 
 template <int VB> struct Vec;
 template <> struct Vec<32> {
@@ -543,11 +546,18 @@ __global__ void __launch_bounds__(kThreads, 1) score_topk_kernel(ScoreTopkParams
   }
 }
 
+// Shared memory of the select kernel for a segment of seg_len keys (and, fused with the hit/miss difference, at
+// least what that needs).
+static size_t score_smem_bytes(int seg_len, int r, int k_for_diff) {
+  size_t smem = ((size_t)seg_len + 5 * kBins + 2 * (kWarps + 1) + 14 + r) * sizeof(uint32_t);
+  if (k_for_diff > 0 && slot_diff_smem_bytes(k_for_diff) > smem) smem = slot_diff_smem_bytes(k_for_diff);
+  return smem;
+}
+
 template <typename T, int R>
 int launch_score_topk(const ScoreTopkParams &p, int n_heads, int csize, cudaStream_t stream) {
-  size_t smem = ((size_t)p.seg_len + 5 * kBins + 2 * (kWarps + 1) + 14 + R) * sizeof(uint32_t);
   static_assert((5 * kBins + 2 * (kWarps + 1) + 14) % 4 == 0, "q_hat must start on a 16-byte boundary");
-  if (p.table != nullptr && slot_diff_smem_bytes(p.k) > smem) smem = slot_diff_smem_bytes(p.k);
+  const size_t smem = score_smem_bytes(p.seg_len, R, p.table != nullptr ? p.k : 0);
   auto kern = score_topk_kernel<T, R>;
   static SmemOptIn opt_in;
   LRQK_CUDA_TRY(opt_in.ensure(kern, smem));
@@ -588,25 +598,75 @@ int dispatch_rank(int r, const ScoreTopkParams &p, int n_heads, int csize, cudaS
 
 }  // namespace
 
-// Cluster size and segment length for `candidates` rows per head and n_heads heads.
-// One CTA per SM (its keys fill most of the SM's shared memory).  The smallest cluster whose
-// segment fits is grown while the whole grid still fits the SMs in a single, evenly loaded
-// wave and every CTA keeps at least one granule of rows.
-// CTAs of a grid of clusters of `cs` that are resident at once with one CTA per SM: a cluster must
-// fit inside one GPC, and the GPCs of the part hold 16 to 20 usable SMs, so clusters of 8 waste some.
-static int kMaxResident(int cs) { return cs >= 8 ? 15 * 8 : (cs == 4 ? 36 * 4 : kNumSMs); }
-
-int plan_score_topk(int64_t candidates, int n_heads, int *csize_out, int *seg_len_out) {
-  const int64_t max_seg = 45056;  // 176 KiB of keys next to the histograms (40 KiB)
-  int best = -1;
-  for (int cs = 1; cs <= 16; cs *= 2) {
-    const int64_t seg = ceil_div64(ceil_div64(candidates, cs), kGranule) * kGranule;
-    if (seg > max_seg) continue;
-    if (best < 0) { best = cs; continue; }  // smallest cluster whose segment fits
-    // (clusters of more than 8 CTAs are not grown into: they launch far more slowly)
-    if (cs <= 8 && (int64_t)n_heads * cs <= kMaxResident(cs) && ceil_div64(candidates, cs) >= kGranule) best = cs;
+// How many clusters of `cs` CTAs of the select kernel the current device keeps resident at once (one CTA per SM;
+// a cluster must fit inside one GPC, so it is not simply SMs / cs).  Asked of the runtime once per (kernel,
+// cluster size, device); 0 when it cannot be told.
+template <typename T, int R>
+int resident_clusters_of(int cs, size_t smem) {
+  static std::mutex mu;
+  static int cache[kMaxDevices][9];  // 0 = not asked yet, -1 = unknown
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices || cs < 1 || cs > 8) { cudaGetLastError(); return 0; }
+  std::lock_guard<std::mutex> lock(mu);
+  if (cache[dev][cs] == 0) {
+    auto kern = score_topk_kernel<T, R>;
+    int n = 0;
+    // the largest shared-memory size any plan uses, so that the answer holds for every segment length
+    const size_t smem_max = score_smem_bytes(kMaxSeg, R, 0);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(cs, 1, 1);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_max;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cs; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max);
+    if (e == cudaSuccess) e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+    if (e != cudaSuccess) { cudaGetLastError(); n = -1; }
+    cache[dev][cs] = n > 0 ? n : -1;
   }
-  if (best < 0) return LRQK_EUNSUPPORTED;
+  (void)smem;
+  return cache[dev][cs] > 0 ? cache[dev][cs] : 0;
+}
+
+static int resident_clusters(const lrqk_layer *L, int cs, size_t smem) {
+  int n = 0;
+#define LRQK_RC(T, R) n = resident_clusters_of<T, R>(cs, smem)
+  if (L->dtype == LRQK_BF16) {
+    switch (L->r) { case 8: LRQK_RC(__nv_bfloat16, 8); break; case 16: LRQK_RC(__nv_bfloat16, 16); break;
+                    case 32: LRQK_RC(__nv_bfloat16, 32); break; case 64: LRQK_RC(__nv_bfloat16, 64); break; default: break; }
+  } else {
+    switch (L->r) { case 8: LRQK_RC(float, 8); break; case 16: LRQK_RC(float, 16); break;
+                    case 32: LRQK_RC(float, 32); break; case 64: LRQK_RC(float, 64); break; default: break; }
+  }
+#undef LRQK_RC
+  if (n <= 0) n = cs >= 7 ? 15 : (cs >= 5 ? 24 : (cs == 4 ? 36 : kNumSMs / cs));  // estimate for a 148-SM part
+  return n;
+}
+
+// Cluster size (1..8, any value) and segment length for `candidates` rows per head and n_heads heads.
+// One CTA per SM (its keys fill most of the SM's shared memory).  Every cluster size whose segment fits is
+// rated by the time it implies: waves of resident clusters times (rows a CTA streams + the fixed cost of the
+// select passes, expressed in rows); the cheapest wins, the smaller cluster on a draw.
+int plan_score_topk(const lrqk_layer *L, int64_t candidates, int n_heads, int *csize_out, int *seg_len_out) {
+  const int64_t select_cost_rows = 10240;  // ~12 us of select passes at the ~52 GB/s one SM streams (64-byte rows)
+  int best = -1;
+  int64_t best_cost = 0;
+  for (int cs = 1; cs <= 8; ++cs) {
+    const int64_t seg = ceil_div64(ceil_div64(candidates, cs), kGranule) * kGranule;
+    if (seg > kMaxSeg) continue;
+    if (cs > 1 && ceil_div64(candidates, cs) < kGranule && best >= 0) break;  // a CTA keeps at least one granule
+    const int resident = resident_clusters(L, cs, 0);
+    const int64_t waves = ceil_div64(n_heads, resident > 0 ? resident : 1);
+    const int64_t cost = waves * (seg + select_cost_rows);
+    if (best < 0 || cost < best_cost) { best = cs; best_cost = cost; }
+  }
+  if (best < 0) {  // longer than eight segments: a non-portable cluster of 16
+    const int64_t seg = ceil_div64(ceil_div64(candidates, 16), kGranule) * kGranule;
+    if (seg > kMaxSeg) return LRQK_EUNSUPPORTED;
+    best = 16;
+  }
   *csize_out = best;
   *seg_len_out = (int)(ceil_div64(ceil_div64(candidates, best), kGranule) * kGranule);
   return LRQK_OK;
@@ -627,9 +687,9 @@ extern "C" size_t lrqk_score_topk_workspace_bytes(const lrqk_layer *L, int64_t m
   // the cluster size only grows with the candidate count, so the smallest count decides whether any call
   // may take the two-kernel plan
   int csize = 1, seg_len = 0;
-  if (lrqk::plan_score_topk(L->k + 1, n_heads, &csize, &seg_len) != LRQK_OK) return 0;
+  if (lrqk::plan_score_topk(L, L->k + 1, n_heads, &csize, &seg_len) != LRQK_OK) return 0;
   if (!lrqk::plan_wants_key_pass(n_heads, csize)) {
-    if (lrqk::plan_score_topk(max_candidates, n_heads, &csize, &seg_len) != LRQK_OK) return 0;
+    if (lrqk::plan_score_topk(L, max_candidates, n_heads, &csize, &seg_len) != LRQK_OK) return 0;
     if (!lrqk::plan_wants_key_pass(n_heads, csize)) return 0;
   }
   return sizeof(uint32_t) * (size_t)n_heads * (size_t)lrqk::keys_stride_for(max_candidates);
@@ -674,7 +734,7 @@ int lrqk::score_topk_enqueue(const lrqk_layer *L, const void *q_hat, int64_t can
     p.list_len = diff->list_len; p.diff_status = diff->status;
   }
   int csize = 1, seg_len = 0;
-  rc = plan_score_topk(candidates, n_heads, &csize, &seg_len);
+  rc = plan_score_topk(L, candidates, n_heads, &csize, &seg_len);
   if (rc != LRQK_OK) return rc;
   p.seg_len = seg_len;
   {

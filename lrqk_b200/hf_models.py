@@ -169,6 +169,98 @@ def lrqk_attention_forward(self, hidden_states: torch.Tensor,
     return self.o_proj(attn_output), None
 
 
+# ------------------------------------------------------------------------------------------------
+# decode-time decoder layer: the element-wise glue around the attention call as two fused kernels
+# ------------------------------------------------------------------------------------------------
+def _lrqk_dtype(t: torch.Tensor):
+    from .state import _DTYPES
+    return _DTYPES.get(t.dtype)
+
+
+def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float, want_sum: bool = True):
+    """(x + delta, weight * rmsnorm(x + delta)) for [..., hidden] tensors in one launch (``lrqk_add_rmsnorm``);
+    ``delta=None``: no add, and no sum is returned unless asked."""
+    import ctypes as C
+    from . import _lib
+    from .state import _ptr, _stream
+    hidden = x.shape[-1]
+    rows = x.numel() // hidden
+    normed = torch.empty_like(x)
+    total = torch.empty_like(x) if (want_sum and delta is not None) else None
+    _lib.check(_lib.lib().lrqk_add_rmsnorm(_ptr(x), _ptr(delta), _ptr(weight), float(eps), _lrqk_dtype(x), rows, hidden,
+                                           _ptr(total), _ptr(normed), _stream()), "lrqk_add_rmsnorm")
+    return (x if delta is None else total), normed
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(gate) * up of the fused gate|up projection [..., 2 * inter] in one launch (``lrqk_swiglu``)."""
+    from . import _lib
+    from .state import _ptr, _stream
+    inter = gate_up.shape[-1] // 2
+    rows = gate_up.numel() // (2 * inter)
+    out = torch.empty(gate_up.shape[:-1] + (inter,), dtype=gate_up.dtype, device=gate_up.device)
+    _lib.check(_lib.lib().lrqk_swiglu(_ptr(gate_up), _lrqk_dtype(gate_up), rows, inter, _ptr(out), _stream()), "lrqk_swiglu")
+    return out
+
+
+def _fused_gate_up(mlp):
+    """Weight [2 * inter, hidden] of one projection that yields gate|up, or None when the MLP is not the plain
+    bias-free SwiGLU of these families.  Built once; the two projections are re-pointed into the fused tensor."""
+    f = getattr(mlp, "_lrqk_gate_up", None)
+    if f is not None:
+        if f is False or mlp.gate_proj.weight.data_ptr() == f.data_ptr():
+            return None if f is False else f
+    ok = (all(hasattr(mlp, n) and type(getattr(mlp, n)) is torch.nn.Linear for n in ("gate_proj", "up_proj", "down_proj"))
+          and mlp.gate_proj.bias is None and mlp.up_proj.bias is None
+          and mlp.gate_proj.weight.dtype == mlp.up_proj.weight.dtype
+          and mlp.gate_proj.weight.shape == mlp.up_proj.weight.shape
+          and type(getattr(mlp, "act_fn", None)).__name__ in ("SiLU", "SiLUActivation"))
+    if not ok:
+        mlp._lrqk_gate_up = False
+        return None
+    with torch.no_grad():
+        w = torch.cat([mlp.gate_proj.weight.data, mlp.up_proj.weight.data], 0)
+        n = mlp.gate_proj.out_features
+        mlp.gate_proj.weight.data = w[:n]
+        mlp.up_proj.weight.data = w[n:]
+    mlp._lrqk_gate_up = w
+    return w
+
+
+def _norm_params(norm):
+    """(weight, eps) of an RMSNorm module of these families, or None for anything else."""
+    eps = getattr(norm, "variance_epsilon", None)
+    w = getattr(norm, "weight", None)
+    if eps is None or w is None or not type(norm).__name__.endswith("RMSNorm"):
+        return None
+    return w, float(eps)
+
+
+def lrqk_decoder_layer_forward(self, hidden_states: torch.Tensor, attention_mask=None, position_ids=None,
+                               past_key_values=None, use_cache=False, position_embeddings=None, **kwargs):
+    """Replacement for ``{Llama,Qwen2,Mistral}DecoderLayer.forward``: while the layer's LRQK state is decoding one
+    token per sequence, the two RMSNorms, the two residual adds and the SwiGLU activation run as four launches of
+    this library instead of some twenty eager ones (same rounding points); anything else takes the module's own
+    forward."""
+    cache = past_key_values
+    n1 = n2 = gate_up = None
+    if (isinstance(cache, DynamicLRQKCache) and hidden_states.shape[1] == 1 and cache.is_decoding(self.self_attn.layer_idx)
+            and _lrqk_dtype(hidden_states) is not None and hidden_states.is_contiguous()):
+        n1, n2 = _norm_params(self.input_layernorm), _norm_params(self.post_attention_layernorm)
+        gate_up = _fused_gate_up(self.mlp)
+    if n1 is None or n2 is None or gate_up is None or n1[0].dtype != hidden_states.dtype or gate_up.dtype != hidden_states.dtype:
+        return self._lrqk_original_layer_forward(hidden_states, attention_mask=attention_mask, position_ids=position_ids,
+                                                 past_key_values=past_key_values, use_cache=use_cache,
+                                                 position_embeddings=position_embeddings, **kwargs)
+    _, normed = add_rmsnorm(hidden_states, None, n1[0], n1[1])
+    attn_out, _ = self.self_attn(hidden_states=normed, attention_mask=attention_mask, position_ids=position_ids,
+                                 past_key_values=past_key_values, use_cache=use_cache,
+                                 position_embeddings=position_embeddings, **kwargs)
+    hidden_states, normed = add_rmsnorm(hidden_states, attn_out.contiguous(), n2[0], n2[1])
+    act = swiglu(F.linear(normed, gate_up))
+    return hidden_states + self.mlp.down_proj(act)
+
+
 def family_of(model_name: str) -> str:
     """Model family by substring of the name, in the reference's order (:2611-2632)."""
     mn = model_name.lower()
@@ -188,6 +280,9 @@ def patch_model(model) -> int:
         if not hasattr(attn, "_lrqk_original_forward"):
             attn._lrqk_original_forward = attn.forward
             attn.forward = types.MethodType(lrqk_attention_forward, attn)
+        if not hasattr(layer, "_lrqk_original_layer_forward") and hasattr(layer, "mlp") and hasattr(layer, "input_layernorm"):
+            layer._lrqk_original_layer_forward = layer.forward
+            layer.forward = types.MethodType(lrqk_decoder_layer_forward, layer)
         n += 1
     return n
 

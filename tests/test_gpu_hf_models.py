@@ -207,3 +207,80 @@ def test_fused_projection_shares_storage_with_the_separate_ones():
     assert torch.allclose(fused.float(), sep.float(), atol=2e-2, rtol=2e-2)
     for p, t in zip((attn.q_proj, attn.k_proj, attn.v_proj), before):
         assert torch.equal(p.weight, t)
+
+
+@pytest.mark.parametrize("dtype,rows,hidden,inter", [(torch.bfloat16, 1, 4096, 14336), (torch.bfloat16, 8, 3584, 18944),
+                                                     (torch.float32, 3, 256, 512)])
+def test_fused_layer_glue_matches_the_eager_modules(dtype, rows, hidden, inter):
+    """lrqk_add_rmsnorm / lrqk_swiglu against the transformers modules they stand in for during decode: the
+    residual add and the activation are element-wise and must agree bit for bit; the normalised row may differ
+    by one unit in the last place where the variance was summed in another order."""
+    from transformers.models.llama.modeling_llama import LlamaRMSNorm
+    from lrqk_b200.hf_models import add_rmsnorm, swiglu
+    g = torch.Generator(device="cuda").manual_seed(hidden)
+    x = torch.randn(rows, 1, hidden, generator=g, device="cuda").to(dtype)
+    d = (torch.randn(rows, 1, hidden, generator=g, device="cuda") * 0.3).to(dtype)
+    norm = LlamaRMSNorm(hidden, eps=1e-5).to("cuda", dtype)
+    with torch.no_grad():
+        norm.weight.copy_((1 + 0.1 * torch.randn(hidden, generator=g, device="cuda")).to(dtype))
+        ref_sum = x + d
+        ref = norm(ref_sum)
+        total, normed = add_rmsnorm(x, d, norm.weight, norm.variance_epsilon)
+        assert torch.equal(total, ref_sum)
+        _, plain = add_rmsnorm(x, None, norm.weight, norm.variance_epsilon)
+        ref_plain = norm(x)
+    for got, want in ((normed, ref), (plain, ref_plain)):
+        if dtype == torch.bfloat16:
+            ulps = (got.view(torch.int16).int() - want.view(torch.int16).int()).abs()
+            assert int(ulps.max()) <= 1 and float((ulps == 0).float().mean()) > 0.995
+        else:
+            assert float((got - want).abs().max() / want.abs().max()) < 1e-6
+    gu = torch.randn(rows, 1, 2 * inter, generator=g, device="cuda").to(dtype) * 2
+    want = torch.nn.functional.silu(gu[..., :inter]) * gu[..., inter:]
+    got = swiglu(gu)
+    if dtype == torch.bfloat16:
+        ulps = (got.view(torch.int16).int() - want.view(torch.int16).int()).abs()
+        assert int(ulps.max()) <= 1 and float((ulps == 0).float().mean()) > 0.999
+    else:
+        assert float((got - want).abs().max() / want.abs().max()) < 1e-6
+
+
+def test_patched_decoder_layer_uses_the_fused_glue_only_while_decoding():
+    import transformers
+    from lrqk_b200 import DynamicLRQKCache, patch_model
+    cfg = transformers.LlamaConfig(vocab_size=300, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                                   num_attention_heads=4, num_key_value_heads=2, head_dim=64, max_position_embeddings=2048)
+    cfg._attn_implementation = "sdpa"
+    torch.manual_seed(3)
+    model = transformers.AutoModelForCausalLM.from_config(cfg).to(torch.bfloat16).cuda().eval()
+    ids = torch.randint(0, 300, (1, 400), generator=torch.Generator().manual_seed(1)).cuda()
+    with torch.no_grad():
+        ref_logits = []                                      # attention patched only: eager glue
+        patch_model(model)
+        for layer in model.model.layers:
+            layer.forward = layer._lrqk_original_layer_forward
+        cache = DynamicLRQKCache(r=16, num_active_tokens=128, lite_tokens=8, max_sequence_length=1024, num_key_value_groups=2,
+                                 init_aq_ak_method="top")
+        out = model(input_ids=ids, past_key_values=cache, use_cache=True)
+        tok = out.logits[:, -1].argmax(-1, keepdim=True)
+        for _ in range(4):
+            out = model(input_ids=tok, past_key_values=cache, use_cache=True)
+            ref_logits.append(out.logits[:, -1].float())
+            tok = out.logits[:, -1].argmax(-1, keepdim=True)
+        cache.close()
+        for layer in model.model.layers:                     # now with the fused glue
+            del layer._lrqk_original_layer_forward
+            del layer.__dict__["forward"]
+        patch_model(model)
+        assert all(hasattr(l, "_lrqk_original_layer_forward") for l in model.model.layers)
+        cache = DynamicLRQKCache(r=16, num_active_tokens=128, lite_tokens=8, max_sequence_length=1024, num_key_value_groups=2,
+                                 init_aq_ak_method="top")
+        out = model(input_ids=ids, past_key_values=cache, use_cache=True)
+        tok = out.logits[:, -1].argmax(-1, keepdim=True)
+        for i in range(4):
+            out = model(input_ids=tok, past_key_values=cache, use_cache=True)
+            got = out.logits[:, -1].float()
+            assert float((got - ref_logits[i]).abs().max()) <= 3e-2 * float(ref_logits[i].abs().max())
+            assert int(got.argmax()) == int(ref_logits[i].argmax())
+            tok = got.argmax(-1, keepdim=True)
+        cache.close()
