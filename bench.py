@@ -22,6 +22,7 @@ cores for the same workload; the default arm also times it on a bounded sample (
 from __future__ import annotations
 
 import argparse
+import ctypes as C
 import json
 import math
 import os
@@ -383,6 +384,12 @@ def run_ours(args):
         dist.all_gather_object(everyone, problems)
         problems = [p for ps in everyone for p in ps]
 
+    # kernels one fused layer-step enqueues (the library's own count for the last step's arguments, without the
+    # ring flush that every m-th step adds)
+    st0 = facs[0].state
+    st0._step_args.flush_rows = 0
+    launches_per_step = int(st0.lib.lrqk_layer_step_launches(C.byref(st0.c), C.byref(st0._step_args)))
+
     # max over ranks
     ms_dev_own = ms_dev
     vals = torch.tensor([ms_dev, ms_e2e], dtype=torch.float64, device=device)
@@ -451,9 +458,7 @@ def run_ours(args):
         "host_issue_us_per_layer_step": round(host_issue_us, 1),
         # per layer-step: projection, update, scoring(+diff), miss fetch, attention (+ exchange wait);
         # plus one ring-flush kernel per layer every m steps
-        "gpu_launches": int(args.steps * layers * (5 + (1 if exchange is not None else 0)
-                                                   + (1 if facs[0].state.score_ws is not None else 0))
-                            + layers * (args.steps // w["m"])),
+        "gpu_launches": int(args.steps * layers * launches_per_step + layers * (args.steps // w["m"])),
         "roofline": roof, "roofline_hbm": roof_hbm, "roofline_step": roof_step,
         "roofline_step_by_rho": dict(sorted(by_rho.items())), "kernels": per_kernel, "per_rank": per_rank,
         "host_link_peak_gbs": round(link_peak, 1), "clocks": clocks,

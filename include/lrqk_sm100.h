@@ -301,6 +301,9 @@ typedef struct lrqk_step_args {
 } lrqk_step_args;
 
 int lrqk_layer_step(const lrqk_layer *L, const lrqk_step_args *a, lrqk_stream_t stream);
+/* Number of kernels that call enqueues for these arguments (4 to 8: projection, [update], [key pass], scoring +
+ * difference, miss fetch, [ring flush], [attention], [exchange wait]); negative LRQK_E* on bad arguments. */
+int lrqk_layer_step_launches(const lrqk_layer *L, const lrqk_step_args *a);
 
 /* ------------------------------------------------------------------------------------
  * The reference's native gather interface (pybind11 module take_along_dim_grouped,

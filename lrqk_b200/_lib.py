@@ -104,6 +104,7 @@ _SIGNATURES = {
     "lrqk_peer_set_wait_polls": (C.c_int, [C.c_uint32]),
     "lrqk_allgather_wait": (C.c_int, [C.POINTER(PeerGroup), C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
     "lrqk_layer_step": (C.c_int, [C.POINTER(Layer), C.POINTER(StepArgs), C.c_void_p]),
+    "lrqk_layer_step_launches": (C.c_int, [C.POINTER(Layer), C.POINTER(StepArgs)]),
     "lrqk_d0_indices_select": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
                                          C.c_void_p]),
     "lrqk_take_along_dim_with_mask_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int64, C.c_int64]),

@@ -177,6 +177,7 @@ inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 bl
 // With `diff`, the kernel also runs the hit/miss difference of every head against L->table right
 // after its selection (what lrqk_slot_diff does as a kernel of its own); *diff->list_len must be
 // zero before the kernel starts.
+struct UpdateArgs;  // update_head.cuh
 struct FusedDiff {
   uint8_t *mask;
   int32_t *miss_count;
@@ -184,17 +185,23 @@ struct FusedDiff {
   int32_t *list_len, *status;
 };
 // `workspace` (optional, lrqk_score_topk_workspace_bytes): room for the keys of the two-kernel plan.
+// `update` (optional): the deferred update of project_update_enqueue -- the kernel derives q_hat from the
+// projection's workspace itself and one CTA per head applies the update while the hit/miss difference runs.
+// score_topk_can_fold_update() says whether that is possible for the plan these arguments get.
 int score_topk_enqueue(const lrqk_layer *L, const void *q_hat, int64_t candidates, int32_t *wanted, float *scores_out,
                        int64_t scores_stride, int32_t *clear_word, cudaStream_t stream, const FusedDiff *diff = nullptr,
-                       void *workspace = nullptr, size_t workspace_bytes = 0);
+                       void *workspace = nullptr, size_t workspace_bytes = 0, const UpdateArgs *update = nullptr);
+bool score_topk_can_fold_update(const lrqk_layer *L, int64_t candidates, void *workspace, size_t workspace_bytes);
 int plan_score_topk(const lrqk_layer *L, int64_t candidates, int n_heads, int *csize_out, int *seg_len_out);
 
 // lrqk_decode_project_update with extra duties for the fused step: *clear_word = 0 at the end, and --
 // when v_new is given -- the ring write of the step's key/value into lite slot `lite_slot` (position
 // append_row), so that no separate ring-write kernel is needed unless the ring is flushed.
+// With `deferred`, only the projection kernel is launched: the arguments of the update (early-exit decision,
+// rank-1 step on B_Q / B_K, q_hat, the new A_K row) are handed back for the scoring kernel to apply.
 int project_update_enqueue(const lrqk_layer *L, const void *q, const void *k_new, int32_t max_iter, float tol,
                            int64_t append_row, void *q_hat, int32_t *iters_out, void *workspace, int32_t *clear_word,
-                           cudaStream_t stream, const void *v_new, int32_t lite_slot);
+                           cudaStream_t stream, const void *v_new, int32_t lite_slot, UpdateArgs *deferred = nullptr);
 // The flush half of lrqk_lite_append alone: the ring of every KV head to host rows [host_row, host_row + m).
 int lite_flush_enqueue(const lrqk_layer *L, int64_t host_row, cudaStream_t stream);
 

@@ -2,6 +2,7 @@
 // back to back on the caller's stream, with no host synchronisation in between (the miss
 // count, the early-exit decision and the slot-table update all stay on the device).
 #include "common.cuh"
+#include "update_head.cuh"
 
 extern "C" int lrqk_layer_step(const lrqk_layer *L, const lrqk_step_args *a, lrqk_stream_t stream) {
   using namespace lrqk;
@@ -16,8 +17,13 @@ extern "C" int lrqk_layer_step(const lrqk_layer *L, const lrqk_step_args *a, lrq
   // the hit/miss difference runs as the tail of the scoring kernel: five launches per step.
   if (a->lite_slot < 0 || a->lite_slot >= L->m) return LRQK_ECAPACITY;
   if (a->flush_rows != 0 && a->flush_rows != L->m) return LRQK_EINVAL;
+  // Where the scoring stage is one kernel, that kernel also applies the projection's update (early-exit
+  // decision, rank-1 step on B_Q / B_K, q_hat, the new A_K row): four launches per step instead of five.
+  UpdateArgs deferred;
+  const bool fold = score_topk_can_fold_update(L, a->candidates, a->score_workspace, a->score_workspace_bytes);
   int rc = project_update_enqueue(L, a->q, a->k_new, a->max_iter, a->tol, a->position, a->q_hat, a->counters + 2,
-                                  a->project_workspace, a->counters, as_stream(stream), a->v_new, a->lite_slot);
+                                  a->project_workspace, a->counters, as_stream(stream), a->v_new, a->lite_slot,
+                                  fold ? &deferred : nullptr);
   if (rc != LRQK_OK) return rc;
   if (a->flush_rows) {
     rc = lite_flush_enqueue(L, a->host_row, as_stream(stream));
@@ -27,7 +33,7 @@ extern "C" int lrqk_layer_step(const lrqk_layer *L, const lrqk_step_args *a, lrq
   diff.mask = a->mask; diff.miss_count = a->miss_count; diff.list = a->miss_list;
   diff.list_len = a->counters; diff.status = a->counters + 1;
   rc = score_topk_enqueue(L, a->q_hat, a->candidates, a->wanted, nullptr, 0, nullptr, as_stream(stream), &diff,
-                          a->score_workspace, a->score_workspace_bytes);
+                          a->score_workspace, a->score_workspace_bytes, fold ? &deferred : nullptr);
   if (rc != LRQK_OK) return rc;
   rc = lrqk_miss_gather(L, a->miss_list, a->counters, stream);
   if (rc != LRQK_OK) return rc;
@@ -44,4 +50,17 @@ extern "C" int lrqk_layer_step(const lrqk_layer *L, const lrqk_step_args *a, lrq
     if (rc != LRQK_OK) return rc;
   }
   return LRQK_OK;
+}
+
+// How many kernels lrqk_layer_step enqueues for these arguments (for launch accounting).
+extern "C" int lrqk_layer_step_launches(const lrqk_layer *L, const lrqk_step_args *a) {
+  using namespace lrqk;
+  if (!L || !a) return LRQK_EINVAL;
+  const bool fold = score_topk_can_fold_update(L, a->candidates, a->score_workspace, a->score_workspace_bytes);
+  int n = 1 /* projection */ + (fold ? 0 : 1) /* update */ + 1 /* scoring + difference */ + (fold ? 0 : 1) /* key pass */ +
+          1 /* miss fetch */;
+  if (a->flush_rows) n += 1;
+  if (a->peers) n += 1 + (a->wait_status ? 1 : 0);
+  else if (a->attn_out) n += 1;
+  return n;
 }

@@ -35,6 +35,7 @@
 #include "common.cuh"
 #include "smallmat.cuh"
 #include "tc_common.cuh"
+#include "update_head.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -54,6 +55,7 @@ struct ProjectParams {
   int32_t q_heads, groups, k, m, max_iter, n_heads;
   float *ws;          // [N][max_iter][2R+2]
   int32_t *status;    // set to LRQK_ETIMEOUT if a bounded wait ran out
+  int32_t *clear_word;  // optional: set to zero by head 0's solver CTA at its end (the fused step's miss-list length)
   // fused ring write (fuse_row >= 0): this kernel also stores the step's key/value into slot
   // fuse_row of the resident rows (and its position into lite_pos), which the ring-write kernel
   // does otherwise; the streaming CTAs take that row from k_new instead of from K_res
@@ -880,107 +882,28 @@ __global__ void __launch_bounds__(kPThreads, 2) project_kernel(ProjectParams p) 
       for (int i = lane; i < R; i += 32) khat[i] = knew[i];
       __syncwarp();
     }
+    if (n == 0 && lane == 0 && p.clear_word) *p.clear_word = 0;
   }
 }
 
 struct UpdateParams {
-  void *A_K, *B_Q, *B_K;
-  const void *q, *k_new;
-  const float *ws;
-  void *q_hat;
-  int32_t *iters_out;
-  int64_t a_capacity, append_row;
-  int32_t q_heads, groups, max_iter, n_heads;
-  float tol;
+  UpdateArgs u;
   int32_t *clear_word;  // optional: set to zero by the kernel
 };
 
 template <typename T, int R, int D>
 __global__ void __launch_bounds__(D) update_kernel(UpdateParams p) {
-  const int n = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int b_idx = n / p.q_heads, h = n % p.q_heads;
-  const int kvh = h / p.groups, kv_heads = p.q_heads / p.groups;
-  constexpr int W = 2 * R + 2;
   __shared__ float delta[8];
-  __shared__ float hat[2][R];
-  __shared__ float red[2][4][D / 32];
-  __shared__ int chosen;
+  extern __shared__ __align__(16) float sh[];  // update_head_smem_floats(R, D)
   pdl_launch_dependents();
-  T *Bg[2] = {reinterpret_cast<T *>(p.B_Q) + (int64_t)n * R * D, reinterpret_cast<T *>(p.B_K) + (int64_t)n * R * D};
-  const T *xg[2] = {reinterpret_cast<const T *>(p.q) + (int64_t)n * D,
-                    reinterpret_cast<const T *>(p.k_new) + ((int64_t)b_idx * kv_heads + kvh) * D};
   pdl_wait();
-
-  // thread e owns column e of both right factors: ask for them first, they do not depend on the choice below
-  const int e = tid;
-  float col[2][R], xe[2];
-#pragma unroll
-  for (int s = 0; s < 2; ++s) {
-#pragma unroll
-    for (int a = 0; a < R; ++a) col[s][a] = Elt<T>::to_float(Bg[s][a * D + e]);
-    xe[s] = Elt<T>::to_float(xg[s][e]);
+  const int n = blockIdx.x;
+  const int chosen = update_chosen<R>(p.u, delta);
+  if (n == 0 && threadIdx.x == 0) {
+    if (p.u.iters_out) *p.u.iters_out = chosen + 1;
+    if (p.clear_word) *p.clear_word = 0;
   }
-  // common stopping iteration: mean over all heads of the squared change of k_hat
-  for (int it = warp; it < p.max_iter && it < 8; it += D / 32) {
-    float s = 0.0f;
-    for (int hh = lane; hh < p.n_heads; hh += 32) s += p.ws[((int64_t)hh * p.max_iter + it) * W + 2 * R];
-    s = warp_sum(s);
-    if (lane == 0) delta[it] = s / (float)(p.n_heads * R);
-  }
-  __syncthreads();
-  if (tid == 0) {
-    int c = p.max_iter - 1;
-    for (int it = 0; it < p.max_iter; ++it) {
-      if (delta[it] < p.tol) { c = it; break; }
-    }
-    chosen = c;
-    if (n == 0 && p.iters_out) *p.iters_out = c + 1;
-    if (n == 0 && p.clear_word) *p.clear_word = 0;
-  }
-  __syncthreads();
-  const float *w = p.ws + ((int64_t)n * p.max_iter + chosen) * W;
-  if (tid < R) { hat[0][tid] = w[tid]; hat[1][tid] = w[R + tid]; }
-  __syncthreads();
-
-  float t[2];
-#pragma unroll
-  for (int s = 0; s < 2; ++s) {
-    float acc = 0.0f;
-#pragma unroll
-    for (int a = 0; a < R; ++a) acc = fmaf(hat[s][a], col[s][a], acc);
-    t[s] = acc - xe[s];  // (x_hat B - x)[e]
-  }
-  // |dB|^2 = sum_{a,e} (x_hat[a] t[e])^2 ;  |x_hat dB|^2 = sum_e (sum_a x_hat[a]^2 t[e])^2
-#pragma unroll
-  for (int s = 0; s < 2; ++s) {
-    float n2 = 0.0f, h2 = 0.0f;
-#pragma unroll
-    for (int a = 0; a < R; ++a) {
-      const float dBae = hat[s][a] * t[s];
-      n2 = fmaf(dBae, dBae, n2);
-      h2 = fmaf(hat[s][a], dBae, h2);
-    }
-    n2 = warp_sum(n2);
-    float hh = warp_sum(h2 * h2);
-    if (lane == 0) { red[s][0][warp] = n2; red[s][1][warp] = hh; }
-  }
-  __syncthreads();
-#pragma unroll
-  for (int s = 0; s < 2; ++s) {
-    float n2 = 0.0f, hh = 0.0f;
-#pragma unroll
-    for (int wv = 0; wv < D / 32; ++wv) { n2 += red[s][0][wv]; hh += red[s][1][wv]; }
-    const float eta = n2 / (hh + 1e-6f);
-#pragma unroll
-    for (int a = 0; a < R; ++a) {
-      const float dBae = hat[s][a] * t[s];
-      Bg[s][a * D + e] = Elt<T>::from_float(col[s][a] - eta * dBae);
-    }
-  }
-  if (tid < R) {
-    reinterpret_cast<T *>(p.q_hat)[(int64_t)n * R + tid] = Elt<T>::from_float(hat[0][tid]);
-    reinterpret_cast<T *>(p.A_K)[((int64_t)n * p.a_capacity + p.append_row) * R + tid] = Elt<T>::from_float(hat[1][tid]);
-  }
+  update_head<T, R>(p.u, n, chosen, sh);
 }
 
 template <typename T, int R, int D>
@@ -1012,7 +935,7 @@ int plan_cluster(int n_heads, int n_act) {
 }
 
 template <typename T, int R, int D>
-int launch(const lrqk_layer *L, ProjectParams pp, const UpdateParams &up, cudaStream_t stream) {
+int launch(const lrqk_layer *L, ProjectParams pp, const UpdateParams &up, cudaStream_t stream, bool with_update) {
   const int n_heads = L->bsz * L->q_heads;
   const int n_act = L->k + L->m;
   const int csize = plan_cluster<T, R, D>(n_heads, n_act);
@@ -1024,18 +947,23 @@ int launch(const lrqk_layer *L, ProjectParams pp, const UpdateParams &up, cudaSt
   static SmemOptIn opt_in;
   LRQK_CUDA_TRY(opt_in.ensure(kern, smem));
   LRQK_CUDA_TRY(launch_dependent(kern, dim3(csize, n_heads, 1), dim3(kPThreads), smem, stream, csize, pp));
-  LRQK_CUDA_TRY(launch_dependent(update_kernel<T, R, D>, dim3(n_heads), dim3(D), 0, stream, 0, up));
+  if (with_update) {
+    constexpr size_t usmem = sizeof(float) * (size_t)update_head_smem_floats(R, D);
+    static SmemOptIn opt_in_u;
+    if (usmem > 48 * 1024) LRQK_CUDA_TRY(opt_in_u.ensure(update_kernel<T, R, D>, usmem));
+    LRQK_CUDA_TRY(launch_dependent(update_kernel<T, R, D>, dim3(n_heads), dim3(D), usmem, stream, 0, up));
+  }
   LRQK_LAUNCH_CHECK();
   return LRQK_OK;
 }
 
 template <typename T, int D>
-int dispatch_r(const lrqk_layer *L, const ProjectParams &pp, const UpdateParams &up, cudaStream_t stream) {
+int dispatch_r(const lrqk_layer *L, const ProjectParams &pp, const UpdateParams &up, cudaStream_t stream, bool with_update) {
   switch (L->r) {
-    case 8: return launch<T, 8, D>(L, pp, up, stream);
-    case 16: return launch<T, 16, D>(L, pp, up, stream);
-    case 32: return launch<T, 32, D>(L, pp, up, stream);
-    case 64: return launch<T, 64, D>(L, pp, up, stream);
+    case 8: return launch<T, 8, D>(L, pp, up, stream, with_update);
+    case 16: return launch<T, 16, D>(L, pp, up, stream, with_update);
+    case 32: return launch<T, 32, D>(L, pp, up, stream, with_update);
+    case 64: return launch<T, 64, D>(L, pp, up, stream, with_update);
     default: return LRQK_EUNSUPPORTED;
   }
 }
@@ -1063,12 +991,13 @@ extern "C" int lrqk_decode_project_update(const lrqk_layer *L, const void *q, co
                                           float tol, int64_t append_row, void *q_hat, int32_t *iters_out,
                                           void *workspace, lrqk_stream_t stream) {
   return lrqk::project_update_enqueue(L, q, k_new, max_iter, tol, append_row, q_hat, iters_out, workspace, nullptr,
-                                      lrqk::as_stream(stream), nullptr, -1);
+                                      lrqk::as_stream(stream), nullptr, -1, nullptr);
 }
 
 int lrqk::project_update_enqueue(const lrqk_layer *L, const void *q, const void *k_new, int32_t max_iter, float tol,
                                  int64_t append_row, void *q_hat, int32_t *iters_out, void *workspace,
-                                 int32_t *clear_word, cudaStream_t s, const void *v_new, int32_t lite_slot) {
+                                 int32_t *clear_word, cudaStream_t s, const void *v_new, int32_t lite_slot,
+                                 UpdateArgs *deferred) {
   int rc = check_device();
   if (rc != LRQK_OK) return rc;
   rc = check_layer(L);
@@ -1093,16 +1022,23 @@ int lrqk::project_update_enqueue(const lrqk_layer *L, const void *q, const void 
     pp.fuse_row = L->k + lite_slot;
   }
   UpdateParams up;
-  up.A_K = L->A_K; up.B_Q = L->B_Q; up.B_K = L->B_K; up.q = q; up.k_new = k_new;
-  up.ws = pp.ws; up.q_hat = q_hat; up.iters_out = iters_out;
-  up.a_capacity = L->a_capacity; up.append_row = append_row;
-  up.q_heads = L->q_heads; up.groups = pp.groups; up.max_iter = max_iter; up.n_heads = pp.n_heads;
-  up.tol = tol;
+  up.u.A_K = L->A_K; up.u.B_Q = L->B_Q; up.u.B_K = L->B_K; up.u.q = q; up.u.k_new = k_new;
+  up.u.ws = pp.ws; up.u.q_hat = q_hat; up.u.iters_out = iters_out;
+  up.u.a_capacity = L->a_capacity; up.u.append_row = append_row;
+  up.u.q_heads = L->q_heads; up.u.groups = pp.groups; up.u.max_iter = max_iter; up.u.n_heads = pp.n_heads;
+  up.u.head_dim = L->head_dim;
+  up.u.tol = tol;
   up.clear_word = clear_word;
+  pp.clear_word = nullptr;
+  const bool with_update = deferred == nullptr;
+  if (deferred) {  // the caller's next kernel applies the update itself; this kernel clears the word instead
+    *deferred = up.u;
+    pp.clear_word = clear_word;
+  }
   if (L->head_dim == 128) {
-    LRQK_DISPATCH_DTYPE(L->dtype, T, return (dispatch_r<T, 128>(L, pp, up, s)));
+    LRQK_DISPATCH_DTYPE(L->dtype, T, return (dispatch_r<T, 128>(L, pp, up, s, with_update)));
   } else if (L->head_dim == 64) {
-    LRQK_DISPATCH_DTYPE(L->dtype, T, return (dispatch_r<T, 64>(L, pp, up, s)));
+    LRQK_DISPATCH_DTYPE(L->dtype, T, return (dispatch_r<T, 64>(L, pp, up, s, with_update)));
   }
   return LRQK_EUNSUPPORTED;
 }

@@ -33,6 +33,7 @@
 
 #include "common.cuh"
 #include "slot_diff.cuh"
+#include "update_head.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -116,6 +117,10 @@ struct ScoreTopkParams {
   int32_t *clear_word;  // optional: set to zero by the kernel
   const uint32_t *keys_in;  // optional [N, keys_stride]: keys already formed by score_keys_kernel
   int64_t keys_stride;
+  // optional folded update (fold_update != 0): q_hat is derived from the projection kernel's workspace here,
+  // and the last CTA of every cluster applies the head's update while the first runs the hit/miss difference
+  int32_t fold_update;
+  UpdateArgs upd;
   // optional fused hit/miss difference (table != nullptr): after the selection, the first CTA of
   // every cluster runs slot_diff_head for its head
   int32_t *table;
@@ -317,6 +322,7 @@ __global__ void __launch_bounds__(kThreads, 1) score_topk_kernel(ScoreTopkParams
   if (seg_rows < 0) seg_rows = 0;
   if (seg_rows > p.seg_len) seg_rows = p.seg_len;
   int n_iter_rows;
+  int chosen = 0;
   if (p.keys_in != nullptr) {
     // the keys were formed by score_keys_kernel: fetch this segment's (they sit in L2), four per thread and trip
     const uint32_t *kin = p.keys_in + (int64_t)n * p.keys_stride + seg_begin;
@@ -338,7 +344,16 @@ __global__ void __launch_bounds__(kThreads, 1) score_topk_kernel(ScoreTopkParams
       }
     }
   } else {
-    if (tid < R) qs[tid] = Elt<T>::to_float(reinterpret_cast<const T *>(p.q_hat)[(int64_t)n * R + tid]);
+    if (p.fold_update) {
+      // the reference's early-exit decision over all heads, then this head's projected query of that
+      // alternation, rounded to the storage dtype as the stored q_hat is
+      chosen = update_chosen<R>(p.upd, reinterpret_cast<float *>(scratch));
+      const float *w = p.upd.ws + ((int64_t)n * p.upd.max_iter + chosen) * (2 * R + 2);
+      if (tid < R) qs[tid] = Elt<T>::to_float(Elt<T>::from_float(w[tid]));
+      if (n == 0 && rank == 0 && tid == 0 && p.upd.iters_out) *p.upd.iters_out = chosen + 1;
+    } else if (tid < R) {
+      qs[tid] = Elt<T>::to_float(reinterpret_cast<const T *>(p.q_hat)[(int64_t)n * R + tid]);
+    }
     __syncthreads();
     n_iter_rows = score_rows<T, R>(p.A_K, p.a_capacity, n, seg_begin, seg_rows, qs, [&](int local, float acc) {
       uint32_t key = 0;
@@ -544,20 +559,27 @@ __global__ void __launch_bounds__(kThreads, 1) score_topk_kernel(ScoreTopkParams
       slot_diff_head(n, p.table, p.wanted, p.mask, p.miss_count, p.miss_list, p.list_len, p.diff_status, p.k,
                      reinterpret_cast<unsigned char *>(smem));
   }
+  if (p.fold_update && rank == csize - 1) {
+    // the head's update of B_Q, B_K, q_hat and the new A_K row: by the cluster's last CTA, which is idle
+    // while the first runs the difference (a cluster of one does it afterwards); the keys' memory is free
+    __syncthreads();
+    update_head<T, R>(p.upd, n, chosen, reinterpret_cast<float *>(smem));
+  }
 }
 
 // Shared memory of the select kernel for a segment of seg_len keys (and, fused with the hit/miss difference, at
 // least what that needs).
-static size_t score_smem_bytes(int seg_len, int r, int k_for_diff) {
+static size_t score_smem_bytes(int seg_len, int r, int k_for_diff, int d_for_update = 0) {
   size_t smem = ((size_t)seg_len + 5 * kBins + 2 * (kWarps + 1) + 14 + r) * sizeof(uint32_t);
   if (k_for_diff > 0 && slot_diff_smem_bytes(k_for_diff) > smem) smem = slot_diff_smem_bytes(k_for_diff);
-  return smem;
+  const size_t upd = d_for_update > 0 ? sizeof(float) * (size_t)update_head_smem_floats(r, d_for_update) : 0;
+  return smem > upd ? smem : upd;
 }
 
 template <typename T, int R>
 int launch_score_topk(const ScoreTopkParams &p, int n_heads, int csize, cudaStream_t stream) {
   static_assert((5 * kBins + 2 * (kWarps + 1) + 14) % 4 == 0, "q_hat must start on a 16-byte boundary");
-  const size_t smem = score_smem_bytes(p.seg_len, R, p.table != nullptr ? p.k : 0);
+  const size_t smem = score_smem_bytes(p.seg_len, R, p.table != nullptr ? p.k : 0, p.fold_update ? p.upd.head_dim : 0);
   auto kern = score_topk_kernel<T, R>;
   static SmemOptIn opt_in;
   LRQK_CUDA_TRY(opt_in.ensure(kern, smem));
@@ -681,6 +703,16 @@ static int64_t keys_stride_for(int64_t rows) { return (rows + 3) / 4 * 4; }
 
 }  // namespace lrqk
 
+bool lrqk::score_topk_can_fold_update(const lrqk_layer *L, int64_t candidates, void *workspace, size_t workspace_bytes) {
+  if (!L || check_layer(L) != LRQK_OK || candidates <= L->k || L->head_dim > 128) return false;
+  const int n_heads = L->bsz * L->q_heads;
+  int csize = 1, seg_len = 0;
+  if (plan_score_topk(L, candidates, n_heads, &csize, &seg_len) != LRQK_OK) return false;
+  const bool key_pass = workspace && plan_wants_key_pass(n_heads, csize) &&
+                        workspace_bytes >= sizeof(uint32_t) * (size_t)n_heads * (size_t)keys_stride_for(candidates);
+  return !key_pass;
+}
+
 extern "C" size_t lrqk_score_topk_workspace_bytes(const lrqk_layer *L, int64_t max_candidates) {
   if (!L || max_candidates <= 0 || lrqk::check_layer(L) != LRQK_OK) return 0;
   const int n_heads = L->bsz * L->q_heads;
@@ -704,7 +736,7 @@ extern "C" int lrqk_score_topk(const lrqk_layer *L, const void *q_hat, int64_t c
 
 int lrqk::score_topk_enqueue(const lrqk_layer *L, const void *q_hat, int64_t candidates, int32_t *wanted,
                              float *scores_out, int64_t scores_stride, int32_t *clear_word, cudaStream_t stream,
-                             const FusedDiff *diff, void *workspace, size_t workspace_bytes) {
+                             const FusedDiff *diff, void *workspace, size_t workspace_bytes, const UpdateArgs *update) {
   int rc = check_device();
   if (rc != LRQK_OK) return rc;
   rc = check_layer(L);
@@ -726,6 +758,7 @@ int lrqk::score_topk_enqueue(const lrqk_layer *L, const void *q_hat, int64_t can
   p.scores_stride = scores_stride;
   p.clear_word = clear_word;
   p.keys_in = nullptr; p.keys_stride = 0;
+  p.fold_update = 0;
   p.table = nullptr; p.mask = nullptr; p.miss_count = nullptr; p.miss_list = nullptr; p.list_len = nullptr; p.diff_status = nullptr;
   if (diff) {
     if (!L->table || !diff->mask || !diff->miss_count || !diff->list || !diff->list_len || !diff->status) return LRQK_EINVAL;
@@ -742,8 +775,14 @@ int lrqk::score_topk_enqueue(const lrqk_layer *L, const void *q_hat, int64_t can
     p.seg_magic = (uint32_t)((0x100000000ull + v - 1) / v);
   }
   const int64_t kstride = keys_stride_for(candidates);
-  if (workspace && plan_wants_key_pass(n_heads, csize) &&
-      workspace_bytes >= sizeof(uint32_t) * (size_t)n_heads * (size_t)kstride) {
+  const bool key_pass = workspace && plan_wants_key_pass(n_heads, csize) &&
+                        workspace_bytes >= sizeof(uint32_t) * (size_t)n_heads * (size_t)kstride;
+  if (update) {
+    if (key_pass || L->head_dim > 128) return LRQK_EINVAL;  // callers ask score_topk_can_fold_update() first
+    p.fold_update = 1;
+    p.upd = *update;
+  }
+  if (key_pass) {
     // few heads: form the keys on all SMs first, the clusters then select from the workspace
     ScoreKeysParams kp;
     kp.A_K = L->A_K; kp.q_hat = q_hat; kp.a_capacity = L->a_capacity; kp.candidates = candidates;
