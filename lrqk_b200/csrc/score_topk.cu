@@ -694,10 +694,11 @@ int plan_score_topk(const lrqk_layer *L, int64_t candidates, int n_heads, int *c
   return LRQK_OK;
 }
 
-// Whether the keys should be formed by the all-SM streaming kernel first: when the clusters of the one-kernel
-// plan would occupy less than a quarter of the SMs (measured: with 8 or more heads at 131072 rows the one
-// kernel is the quicker plan).
-static bool plan_wants_key_pass(int n_heads, int csize) { return n_heads * csize * 4 < kNumSMs; }
+// Whether the keys should be formed by the all-SM streaming kernel first: only when the clusters of the
+// one-kernel plan would occupy less than an eighth of the SMs.  (Measured at 131072 rows: from 4 heads on --
+// 32 CTAs -- one kernel is as quick or quicker, because the select passes, not the stream, set its time; and
+// only the one-kernel plan can apply the projection's update in the same launch.)
+static bool plan_wants_key_pass(int n_heads, int csize) { return n_heads * csize * 8 < kNumSMs; }
 
 static int64_t keys_stride_for(int64_t rows) { return (rows + 3) / 4 * 4; }
 

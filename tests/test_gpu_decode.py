@@ -69,7 +69,7 @@ def test_score_topk_matches_oracle(dtype, r, bsz, hq, cand, k):
         assert np.array_equal(scores.numpy().view(np.uint32), canon.view(np.uint32)), "summation order drifted"
 
 
-@pytest.mark.parametrize("r,hq,cand,k", [(32, 4, 131007, 2048), (16, 3, 70001, 1024), (64, 2, 9000, 64), (32, 8, 20000, 512)])
+@pytest.mark.parametrize("r,hq,cand,k", [(32, 2, 131007, 2048), (16, 2, 70001, 1024), (64, 2, 9000, 64), (32, 4, 20000, 512)])
 def test_score_topk_one_and_two_kernel_plans_agree(r, hq, cand, k):
     """With few heads the keys are formed by a separate all-SM kernel into a workspace (the state sizes one
     when that plan applies); without a workspace the clusters score their own segments.  Same scores, same
@@ -282,24 +282,29 @@ def test_flash_decode_matches_oracle(dtype, d, rows, bsz, hq):
     assert torch.equal(a, b)
 
 
-@pytest.mark.parametrize("dtype,r,k,m,bsz,hq,hkv,max_iter", [
-    (torch.float32, 16, 256, 16, 1, 8, 2, 2), (torch.bfloat16, 32, 512, 64, 2, 8, 2, 2),
-    (torch.float32, 8, 64, 4, 2, 4, 2, 3), (torch.bfloat16, 64, 300, 20, 1, 4, 4, 1),
-    (torch.float32, 32, 100, 7, 1, 2, 1, 0),
+@pytest.mark.parametrize("dtype,r,k,m,bsz,hq,hkv,max_iter,d", [
+    (torch.float32, 16, 256, 16, 1, 8, 2, 2, 128), (torch.bfloat16, 32, 512, 64, 2, 8, 2, 2, 128),
+    (torch.float32, 8, 64, 4, 2, 4, 2, 3, 128), (torch.bfloat16, 64, 300, 20, 1, 4, 4, 1, 128),
+    (torch.float32, 32, 100, 7, 1, 2, 1, 0, 128),
+    (torch.bfloat16, 16, 1024, 32, 2, 4, 2, 1, 128),   # rank and ring of the Qwen2.5-7B configuration (tensor-core Grams at r=16)
+    (torch.bfloat16, 8, 200, 8, 1, 3, 1, 2, 128),
+    (torch.bfloat16, 16, 300, 12, 1, 4, 2, 2, 64),     # head_dim 64: one operand tile per right factor, 128-row key stages
+    (torch.float32, 8, 150, 6, 1, 2, 2, 2, 64),
+    (torch.bfloat16, 64, 4096, 128, 1, 2, 1, 4, 128),  # rank, set size and alternations of the 256K configuration
 ])
-def test_project_update_matches_oracle(dtype, r, k, m, bsz, hq, hkv, max_iter):
+def test_project_update_matches_oracle(dtype, r, k, m, bsz, hq, hkv, max_iter, d):
     g = torch.Generator().manual_seed(r * k)
-    d, cap = 128, 3000
+    cap = 3000 if k < 2000 else 6000
     grp = hq // hkv
     st = _state(bsz=bsz, q_heads=hq, kv_heads=hkv, head_dim=d, r=r, k=k, m=m, a_capacity=cap,
                 host_capacity=16, dtype=dtype, with_host=False, max_iter=max(1, max_iter))
     A = torch.randn(bsz, hq, cap, r, generator=g).to(dtype)
-    append_row = 2500
+    append_row = cap - 500
     A[:, :, append_row:] = 0                     # the row being appended still reads as zero
     BQ = (torch.randn(bsz, hq, r, d, generator=g) * 0.3).to(dtype)
     BK = (torch.randn(bsz, hq, r, d, generator=g) * 0.3).to(dtype)
     Kres = torch.randn(bsz, hq, k + m, d, generator=g).to(dtype)
-    table = torch.stack([torch.randperm(2400, generator=g)[:k] for _ in range(bsz * hq)]).view(bsz, hq, k).int()
+    table = torch.stack([torch.randperm(append_row - m - 5, generator=g)[:k] for _ in range(bsz * hq)]).view(bsz, hq, k).int()
     lite = torch.arange(append_row - m + 1, append_row + 1, dtype=torch.int32)
     q = torch.randn(bsz, hq, d, generator=g).to(dtype)
     kn = torch.randn(bsz, hkv, d, generator=g).to(dtype)
