@@ -84,6 +84,9 @@ typedef struct lrqk_layer {
   int32_t *table;         /* [B,Hq,k]   token position held by each selected slot         */
   int32_t *lite_pos;      /* [m]        token position held by each lite slot             */
   void *host_kv;          /* device-visible address of host [B,Hkv,host_capacity,2d], K|V */
+  float weights[4];       /* lambda_Q, lambda_K of the prompt factorisation, lambda_dec_q,
+                             lambda_dec_k of the decode step (:1040, :1066-1072); each >= 0.
+                             The reference's cache leaves all four at 1.                   */
 } lrqk_layer;
 
 /* One missed row: resident slot `slot` of head `head` (= b*Hq + h) must be refilled with
@@ -109,8 +112,9 @@ int lrqk_lite_append(const lrqk_layer *L, const void *k_new, const void *v_new, 
  * Rank-r projection of the step's q, k and update of B_Q, B_K.
  * Replaces _get_A_K_hitted_with_lite (lrqk_attention.py:1156-1171), cast_lrqk_decode /
  * _lrqk_decode_inv_w1 / _lrqk_decode_gd_B_lr (:522-628, :651-665, :803-839) and the
- * sync_cache append of k_hat (:1208-1233).  Unit weights (lambda = 1) only, like every
- * caller in the reference (:1435-1436 defaults).
+ * sync_cache append of k_hat (:1208-1233); with L->weights[2] or [3] (lambda_dec_q, lambda_dec_k)
+ * different from 1, the weighted form _lrqk_decode_inv (:433-519) -- the same kernel, the active
+ * set's sums scaled by lambda_dec_k, the new token's own q k^T term by lambda_dec_q.
  *   q        : [B,Hq,d], k_new: [B,Hkv,d]
  *   append_row : row of A_K that receives k_hat (the new token's position)
  *   q_hat    : out [B,Hq,r] in L->dtype
@@ -371,7 +375,9 @@ int lrqk_prefill_fill_resident(const lrqk_layer *L, const void *keys, const void
 
 /* ------------------------------------------------------------------------------------
  * Prompt factorisation  Q ~ A_Q B_Q, K ~ A_K B_K with A_Q A_K^T ~ Q K^T.
- * Replaces cast_lrqk_prefill / _lrqk_prefill_inv_w1 (lrqk_attention.py:312-423, :772-800).
+ * Replaces cast_lrqk_prefill / _lrqk_prefill_inv_w1 (lrqk_attention.py:312-423, :772-800) and, when
+ * L->weights[0] or [1] (lambda_Q, lambda_K) differs from 1, _lrqk_prefill_inv (:218-309), whose sweep
+ * renews BOTH left factors from the factors it started with.
  *   Q [B,Hq,S,d], K [B,Hkv,S,d] in L->dtype (K is NOT expanded to the query heads)
  *   A_Q, A_K_init : fp32 [B,Hq,S,r] initial factors (see _init_AQ_AK, :187-209); overwritten
  *   sweeps, tol : max_iter[0], tol[0]; the stop test after a sweep is evaluated on the device

@@ -30,6 +30,7 @@ class Layer(C.Structure):
         ("A_K", C.c_void_p), ("B_Q", C.c_void_p), ("B_K", C.c_void_p),
         ("K_res", C.c_void_p), ("V_res", C.c_void_p),
         ("table", C.c_void_p), ("lite_pos", C.c_void_p), ("host_kv", C.c_void_p),
+        ("weights", C.c_float * 4),
     ]
 
 

@@ -52,6 +52,8 @@ int check_layer(const lrqk_layer *L) {
   if (L->r != 8 && L->r != 16 && L->r != 32 && L->r != 64) return LRQK_EUNSUPPORTED;
   if ((int64_t)L->bsz * L->q_heads * (int64_t)L->k >= (1ll << 31)) return LRQK_EUNSUPPORTED;
   if (L->a_capacity >= (1ll << 31)) return LRQK_EUNSUPPORTED;
+  for (int i = 0; i < 4; ++i)
+    if (!(L->weights[i] >= 0.0f) || L->weights[i] > 3.0e38f) return LRQK_EINVAL;  // negative, NaN or infinite
   return LRQK_OK;
 }
 
@@ -59,7 +61,7 @@ int check_layer(const lrqk_layer *L) {
 
 extern "C" {
 
-const char *lrqk_version(void) { return "lrqk_sm100 0.1.0 (sm_100a)"; }
+const char *lrqk_version(void) { return "lrqk_sm100 0.2.0 (sm_100a)"; }
 
 const char *lrqk_strerror(int code) {
   switch (code) {

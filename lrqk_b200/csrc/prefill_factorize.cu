@@ -132,16 +132,21 @@ __global__ void __launch_bounds__(kFThreads) gram_pass_kernel(GramParams p) {
 }
 
 // ---- 2. algebra -----------------------------------------------------------------------------------
-// C[m x n] = Add + A[m x k] B[k x n] with arbitrary strides (all operands fp32, any memory);
-// every thread of the CTA takes outputs tid, tid + kFThreads, ...  Ends with a barrier.
+// C[m x n] = Add + scale * A[m x k] B[k x n] with arbitrary strides (all operands fp32, any memory);
+// every thread of the CTA takes outputs tid, tid + kFThreads, ...  Ends with a barrier.  With scale = 1 the
+// sum starts from Add (the unit-weight form's summation order); otherwise the product is summed alone
+// and scaled into Add with one fused multiply-add.
 __device__ __forceinline__ void mm(float *C, int ldc, const float *A, int a_rs, int a_cs, const float *B, int b_rs,
-                                   int b_cs, int m, int n, int k, const float *Add, int add_rs, int add_cs) {
+                                   int b_cs, int m, int n, int k, const float *Add, int add_rs, int add_cs,
+                                   float scale = 1.0f) {
+  const bool scaled = Add && scale != 1.0f;
   for (int idx = threadIdx.x; idx < m * n; idx += kFThreads) {
     const int i = idx / n, j = idx % n;
-    float acc = Add ? Add[i * add_rs + j * add_cs] : 0.0f;
+    float acc = (Add && !scaled) ? Add[i * add_rs + j * add_cs] : 0.0f;
     const float *ap = A + (int64_t)i * a_rs, *bp = B + (int64_t)j * b_cs;
 #pragma unroll 4
     for (int x = 0; x < k; ++x) acc = fmaf(ap[(int64_t)x * a_cs], bp[(int64_t)x * b_rs], acc);
+    if (scaled) acc = fmaf(scale, acc, Add[i * add_rs + j * add_cs]);
     C[i * ldc + j] = acc;
   }
   __syncthreads();
@@ -162,6 +167,10 @@ struct AlgebraParams {
   float *ws;
   FactorWs lay;
   int32_t n_heads, sweeps;
+  // Weights of the two reconstruction terms.  With both at 1 a sweep renews A_K from the NEW A_Q
+  // (lrqk_attention.py:385-395); otherwise both left factors are renewed from the factors the sweep
+  // started with (:266-288) -- the reference's two forms differ in more than the weights.
+  float lam_q, lam_k;
 };
 
 template <int R, int D>
@@ -207,6 +216,7 @@ __global__ void __launch_bounds__(kFThreads) algebra_kernel(AlgebraParams p) {
     return block_sum(v, red);
   };
 
+  const bool unit = p.lam_q == 1.0f && p.lam_k == 1.0f;                       // the reference's dispatch (:790)
   invert(GQ, Mi);
   mm(BQ, D, Mi, R, 1, CQ, D, 1, R, D, R, nullptr, 0, 0);                      // B_Q = G_Q^-1 C_Q
   invert(GK, Mi);
@@ -214,12 +224,20 @@ __global__ void __launch_bounds__(kFThreads) algebra_kernel(AlgebraParams p) {
   for (int sw = 0; sw < p.sweeps; ++sw) {
     float *out = p.ws + p.lay.sweep + ((int64_t)n * p.sweeps + sw) * p.lay.sweep_stride;
     float *oXQ = out, *oXK = oXQ + D * R, *oBQ = oXK + D * R, *oBK = oBQ + R * D, *ossd = oBK + R * D;
-    // X_Q = (C_K^T + B_Q^T)(G_K + B_Q B_Q^T)^-1
-    mm(GN, R, BQ, D, 1, BQ, 1, D, R, R, D, GK, R, 1);
+    // X_Q = (C_K^T + lam_q B_Q^T)(G_K + lam_q B_Q B_Q^T)^-1
+    mm(GN, R, BQ, D, 1, BQ, 1, D, R, R, D, GK, R, 1, p.lam_q);
     invert(GN, Mi);
-    for (int i = tid; i < D * R; i += kFThreads) RH[i] = CK[(i % R) * D + i / R] + BQ[(i % R) * D + i / R];
+    for (int i = tid; i < D * R; i += kFThreads) RH[i] = fmaf(p.lam_q, BQ[(i % R) * D + i / R], CK[(i % R) * D + i / R]);
     __syncthreads();
     mm(XQ, R, RH, R, 1, Mi, R, 1, D, R, R, nullptr, 0, 0);
+    if (!unit) {
+      // X_K = (C_Q^T + lam_k B_K^T)(G_Q + lam_k B_K B_K^T)^-1 from the A_Q the sweep started with
+      mm(GN, R, BK, D, 1, BK, 1, D, R, R, D, GQ, R, 1, p.lam_k);
+      invert(GN, Mi);
+      for (int i = tid; i < D * R; i += kFThreads) RH[i] = fmaf(p.lam_k, BK[(i % R) * D + i / R], CQ[(i % R) * D + i / R]);
+      __syncthreads();
+      mm(XK, R, RH, R, 1, Mi, R, 1, D, R, R, nullptr, 0, 0);
+    }
     mm(E, R, SQ, D, 1, XQ, R, 1, D, R, D, nullptr, 0, 0);                     // Q^T A_Q = S_Q X_Q
     const float tr_old_q = trace(GQ);
     float cross = 0.0f;
@@ -227,16 +245,17 @@ __global__ void __launch_bounds__(kFThreads) algebra_kernel(AlgebraParams p) {
     cross = block_sum(cross, red);
     mm(GQ, R, XQ, 1, R, E, R, 1, R, R, D, nullptr, 0, 0);                     // A_Q^T A_Q = X_Q^T S_Q X_Q
     const float ssd_q = tr_old_q - 2.0f * cross + trace(GQ);
-    // X_K = (Q^T A_Q + B_K^T)(A_Q^T A_Q + B_K B_K^T)^-1
-    mm(GN, R, BK, D, 1, BK, 1, D, R, R, D, GQ, R, 1);
-    invert(GN, Mi);
-    for (int i = tid; i < D * R; i += kFThreads) {
-      RH[i] = E[i] + BK[(i % R) * D + i / R];
-      oXQ[i] = XQ[i];
+    if (unit) {
+      // X_K = (Q^T A_Q + B_K^T)(A_Q^T A_Q + B_K B_K^T)^-1 with the new A_Q
+      mm(GN, R, BK, D, 1, BK, 1, D, R, R, D, GQ, R, 1);
+      invert(GN, Mi);
+      for (int i = tid; i < D * R; i += kFThreads) RH[i] = E[i] + BK[(i % R) * D + i / R];
     }
+    for (int i = tid; i < D * R; i += kFThreads) oXQ[i] = XQ[i];
     __syncthreads();
     for (int i = tid; i < R * D; i += kFThreads) CQ[i] = E[(i % D) * R + i / D];  // A_Q^T Q = E^T
-    mm(XK, R, RH, R, 1, Mi, R, 1, D, R, R, nullptr, 0, 0);
+    if (unit) mm(XK, R, RH, R, 1, Mi, R, 1, D, R, R, nullptr, 0, 0);
+    else __syncthreads();
     mm(E, R, SK, D, 1, XK, R, 1, D, R, D, nullptr, 0, 0);                     // K^T A_K = S_K X_K
     const float tr_old_k = trace(GK);
     cross = 0.0f;
@@ -386,6 +405,7 @@ int run(const lrqk_layer *L, const void *Q, const void *K, float *A_Q, float *A_
   }
   AlgebraParams ap;
   ap.ws = ws; ap.lay = lay; ap.n_heads = n_heads; ap.sweeps = sweeps;
+  ap.lam_q = L->weights[0]; ap.lam_k = L->weights[1];  // lambda_Q, lambda_K (:1435-1436)
   algebra_kernel<R, D><<<n_heads, kFThreads, 0, stream>>>(ap);
   LRQK_LAUNCH_CHECK();
   ApplyParams pp;

@@ -53,6 +53,7 @@ struct ProjectParams {
   const int32_t *table, *lite_pos;
   int64_t a_capacity;
   int32_t q_heads, groups, k, m, max_iter, n_heads;
+  float lam_own, lam_act;  // weights of the new token's own q k^T term and of the active set's terms (:462-495)
   float *ws;          // [N][max_iter][2R+2]
   int32_t *status;    // set to LRQK_ETIMEOUT if a bounded wait ran out
   int32_t *clear_word;  // optional: set to zero by head 0's solver CTA at its end (the fused step's miss-list length)
@@ -248,13 +249,13 @@ __device__ __forceinline__ void cta_spd_inverse(float *W, int ld) {
   }
 }
 
-// x = (G + v^T v)^-1 b for symmetric G with a known inverse Gi (Sherman-Morrison), followed by one
-// step of iterative refinement against G itself.  Executed by ONE warp; lane i owns row i (and
+// x = (G + lam v^T v)^-1 b for symmetric G with a known inverse Gi (Sherman-Morrison), followed by one
+// step of iterative refinement against G itself.  (lam = 1 leaves every product below exact.)  Executed by ONE warp; lane i owns row i (and
 // i+32).  G and Gi are read column-wise (they are symmetric), which is free of bank conflicts.
 // x and tmp are R floats of shared memory; x receives the result.
 template <int R>
-__device__ __forceinline__ void warp_rank1_solve(const float *G, const float *Gi, int ld, const float *v, const float *b,
-                                                 float *x, float *tmp) {
+__device__ __forceinline__ void warp_rank1_solve(const float *G, const float *Gi, int ld, const float *v, float lam,
+                                                 const float *b, float *x, float *tmp) {
   constexpr int RPL = (R + 31) / 32;
   const int lane = threadIdx.x & 31;
   float y[RPL], z[RPL], vi[RPL], bi[RPL], xv[RPL];
@@ -274,7 +275,7 @@ __device__ __forceinline__ void warp_rank1_solve(const float *G, const float *Gi
   for (int t = 0; t < RPL; ++t) { alpha = fmaf(vi[t], y[t], alpha); beta = fmaf(vi[t], z[t], beta); }
   alpha = warp_sum(alpha);
   beta = warp_sum(beta);
-  const float inv = 1.0f / (1.0f + beta);
+  const float inv = lam / (1.0f + lam * beta);
   float vx = 0.0f;
 #pragma unroll
   for (int t = 0; t < RPL; ++t) {
@@ -284,7 +285,8 @@ __device__ __forceinline__ void warp_rank1_solve(const float *G, const float *Gi
   }
   vx = warp_sum(vx);
   __syncwarp();
-  // residual r = b - G x - v (v . x), then the same solve for the correction
+  // residual r = b - G x - lam v (v . x), then the same solve for the correction
+  vx *= lam;
 #pragma unroll
   for (int t = 0; t < RPL; ++t) {
     const int i = lane + 32 * t;
@@ -842,30 +844,30 @@ __global__ void __launch_bounds__(kPThreads, 2) project_kernel(ProjectParams p) 
     float s = 0.0f;
     for (int c = 0; c < n_streamers; ++c) s += slots[c * SLOT + i];
     const int idx = (i / R) * LDG + i % R;
-    const float g = GQ[idx] + s;
+    const float g = fmaf(p.lam_act, s, GQ[idx]);
     GQ[idx] = g;
     GQi[idx] = g;
   }
   if (tid < R) {
     float s = 0.0f;
     for (int c = 0; c < n_streamers; ++c) s += slots[c * SLOT + R * R + tid];
-    qrhs[tid] += s;
+    qrhs[tid] = fmaf(p.lam_act, s, qrhs[tid]);
   }
   __syncthreads();
   cta_spd_inverse<R>(GQi, LDG);
 
   float *ws = p.ws + (int64_t)n * p.max_iter * (2 * R + 2);
   if (warp == 0) {
-    const float qk = misc[0];
+    const float qk = p.lam_own * misc[0];
     for (int it = 0; it < p.max_iter; ++it) {
-      // q_hat = (qrhs + qk * k_hat)(GQ + k_hat^T k_hat)^-1
+      // q_hat = (qrhs + qk * k_hat)(GQ + lam_own k_hat^T k_hat)^-1
       for (int i = lane; i < R; i += 32) rhs[i] = fmaf(qk, khat[i], qrhs[i]);
       __syncwarp();
-      warp_rank1_solve<R>(GQ, GQi, LDG, khat, rhs, qhat, tmpv);
-      // k_hat' = (kbk + qk * q_hat)(GK + q_hat^T q_hat)^-1
+      warp_rank1_solve<R>(GQ, GQi, LDG, khat, p.lam_own, rhs, qhat, tmpv);
+      // k_hat' = (kbk + qk * q_hat)(GK + lam_own q_hat^T q_hat)^-1
       for (int i = lane; i < R; i += 32) rhs[i] = fmaf(qk, qhat[i], kbk[i]);
       __syncwarp();
-      warp_rank1_solve<R>(GK, GKi, LDG, qhat, rhs, knew, tmpv);
+      warp_rank1_solve<R>(GK, GKi, LDG, qhat, p.lam_own, rhs, knew, tmpv);
       float ssd = 0.0f;
       for (int i = lane; i < R; i += 32) {
         const float dlt = khat[i] - knew[i];
@@ -1013,6 +1015,7 @@ int lrqk::project_update_enqueue(const lrqk_layer *L, const void *q, const void 
   pp.a_capacity = L->a_capacity;
   pp.q_heads = L->q_heads; pp.groups = L->q_heads / L->kv_heads; pp.k = L->k; pp.m = L->m;
   pp.max_iter = max_iter; pp.n_heads = L->bsz * L->q_heads;
+  pp.lam_own = L->weights[2]; pp.lam_act = L->weights[3];  // lambda_dec_q, lambda_dec_k (:1535-1536 -> :433-446)
   pp.ws = reinterpret_cast<float *>(workspace);
   pp.status = reinterpret_cast<int32_t *>(reinterpret_cast<char *>(workspace) + project_iterates_bytes(L, max_iter));
   pp.v_new = v_new; pp.K_res_w = L->K_res; pp.V_res_w = L->V_res; pp.lite_pos_w = L->lite_pos;

@@ -246,8 +246,10 @@ class LightAttentionIndicesFactory:
     ``decode_attend`` additionally runs the attention kernel and returns its output, which is
     what the patched attention modules use.
 
-    ``weights`` other than all-ones is not supported (the reference's cache never passes it,
-    lrqk_attention.py:1811-1820).
+    ``weights`` = (lambda_Q, lambda_K, lambda_dec_q, lambda_dec_k) as in the reference (:1040,
+    :1435-1436, :1535-1536): with either weight of a pair different from 1 the prompt factorisation /
+    the decode projection take the reference's general forms (:218-309 / :433-519), which the same
+    kernels evaluate.
 
     Prompts of ``attn_topk .. attn_topk + num_lite_tokens`` rows take the reference's short branch
     (:1444-1466): every prompt row stays resident (slot = position), nothing is selected, and decode
@@ -276,9 +278,9 @@ class LightAttentionIndicesFactory:
             weights = (weights,) * 4
         if not isinstance(weights, tuple) or len(weights) != 4:
             raise ValueError("weights must be a float or a tuple of length 4")
-        if any(w != 1.0 for w in weights):
-            raise NotImplementedError("only unit weights are implemented by the sm_100a kernels")
-        self.weights = weights
+        if any(not (0.0 <= float(w) < float("inf")) for w in weights):
+            raise ValueError("weights must be finite and non-negative")
+        self.weights = tuple(float(w) for w in weights)
         self.capacity, self.scaling_ratio = capacity, scaling_ratio
         self.device, self.dtype = device, dtype
         self.lite_len = 0
@@ -383,7 +385,8 @@ class LightAttentionIndicesFactory:
         cap = max(self.capacity, int(seq_len * self.scaling_ratio))   # first allocation, :880
         # the first seq_len rows of the host store are written by the prompt copy: clear only the rest
         st = LayerState(bsz, hq, hkv, d, self.r, self.attn_topk, self.num_lite_tokens, a_capacity=cap,
-                        host_capacity=cap, dtype=dtype, device=device, max_iter=self.max_iter[1], zero_host=False)
+                        host_capacity=cap, dtype=dtype, device=device, max_iter=self.max_iter[1], zero_host=False,
+                        weights=self.weights)
         st.host.zero_rows_from(seq_len)
         return st
 
@@ -452,7 +455,8 @@ class LightAttentionIndicesFactory:
         cap_a = max(self.capacity, int(seq_len * self.scaling_ratio), self.gpu_capacity + 2)
         cap_h = max(self.capacity, int(kk * self.scaling_ratio), self.gpu_capacity + 2)
         st = self.state = LayerState(bsz, hq, hkv, d, self.r, kk, m, a_capacity=cap_a, host_capacity=cap_h,
-                                     dtype=q.dtype, device=q.device, max_iter=self.max_iter[1], zero_host=True)
+                                     dtype=q.dtype, device=q.device, max_iter=self.max_iter[1], zero_host=True,
+                                     weights=self.weights)
         self.prefill_length = self.current_len = seq_len
         self._factorize(st, q, k, seq_len)
         st.kv_pack_host(k[:, :, :kk].contiguous(), v[:, :, :kk].contiguous(), 0)

@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import contextlib
 import ctypes as C
-from typing import Optional
+from typing import Optional, Tuple
 
 import numpy as np
 import torch
@@ -122,12 +122,16 @@ def on_device(device: torch.device):
 class LayerState:
     def __init__(self, bsz: int, q_heads: int, kv_heads: int, head_dim: int, r: int, k: int, m: int,
                  a_capacity: int, host_capacity: int, dtype: torch.dtype, device="cuda", max_iter: int = 2,
-                 with_host: bool = True, zero_host: bool = True):
+                 with_host: bool = True, zero_host: bool = True,
+                 weights: Tuple[float, float, float, float] = (1.0, 1.0, 1.0, 1.0)):
         if dtype not in _DTYPES:
             raise ValueError(f"unsupported dtype {dtype}: the kernels take float32 or bfloat16")
         if not torch.cuda.is_available():
             raise RuntimeError("lrqk_b200 needs a CUDA device (sm_100); there is no CPU path")
         self.lib = _lib.lib()
+        self.weights = tuple(float(w) for w in weights)  # lambda_Q, lambda_K, lambda_dec_q, lambda_dec_k
+        if len(self.weights) != 4 or any(not (0.0 <= w < float("inf")) for w in self.weights):
+            raise ValueError("weights: four finite, non-negative numbers")
         self.bsz, self.q_heads, self.kv_heads, self.head_dim = bsz, q_heads, kv_heads, head_dim
         self.r, self.k, self.m = r, k, m
         self.dtype, self.device = dtype, torch.device(device)
@@ -178,6 +182,7 @@ class LayerState:
         c.K_res, c.V_res = self.K_res.data_ptr(), self.V_res.data_ptr()
         c.table, c.lite_pos = self.table.data_ptr(), self.lite_pos.data_ptr()
         c.host_kv = self.host.device_ptr if self.host is not None else None
+        c.weights[:] = self.weights
         self.c = c
 
     # ---- operators -------------------------------------------------------------------------

@@ -166,17 +166,60 @@ def prefill_factorize(Q: torch.Tensor, K: torch.Tensor, A_Q: torch.Tensor, A_K: 
     return A_Q, B_Q, A_K, B_K
 
 
+def prefill_factorize_weighted(Q: torch.Tensor, K: torch.Tensor, A_Q: torch.Tensor, A_K: torch.Tensor,
+                               lambda_q: float, lambda_k: float, max_iter: int, tol: float,
+                               return_sweeps: bool = False):
+    """The factorisation with weights lambda_Q, lambda_K on the two reconstruction terms
+    (lrqk_attention.py:218-309), taken whenever either differs from 1 (:790-797).
+
+    One sweep (:252-300) -- unlike the unit-weight form, BOTH left factors are renewed from the
+    factors the sweep started with:
+      B_Q, B_K  <- least squares against the current A factors                           (:256-263)
+      A_Q'      <- Q (K^T A_K + lambda_Q B_Q^T)(A_K^T A_K + lambda_Q B_Q B_Q^T)^-1       (:266-274)
+      A_K'      <- K (Q^T A_Q + lambda_K B_K^T)(A_Q^T A_Q + lambda_K B_K B_K^T)^-1       (:277-288)
+      stop after the sweep if max(mse(A_Q,A_Q'), mse(A_K,A_K')) < tol                    (:291-300)
+    then B_Q, B_K from the final A factors (:303-308).
+    """
+    sweeps = 0
+    for _ in range(max_iter):
+        gram_q = _t(A_Q) @ A_Q
+        gram_k = _t(A_K) @ A_K
+        B_Q = _solve_left(gram_q, _t(A_Q) @ Q)
+        B_K = _solve_left(gram_k, _t(A_K) @ K)
+
+        rhs_q = _t(K) @ A_K + lambda_q * _t(B_Q)
+        new_A_Q = Q @ _solve_right(gram_k + lambda_q * (B_Q @ _t(B_Q)), rhs_q)
+
+        rhs_k = _t(Q) @ A_Q + lambda_k * _t(B_K)
+        new_A_K = K @ _solve_right(gram_q + lambda_k * (B_K @ _t(B_K)), rhs_k)
+
+        delta = max(torch.nn.functional.mse_loss(A_Q, new_A_Q), torch.nn.functional.mse_loss(A_K, new_A_K))
+        A_Q, A_K = new_A_Q, new_A_K
+        sweeps += 1
+        if delta < tol:
+            break
+    B_Q = _ls_right_factor(A_Q, Q)
+    B_K = _ls_right_factor(A_K, K)
+    if return_sweeps:
+        return A_Q, B_Q, A_K, B_K, sweeps
+    return A_Q, B_Q, A_K, B_K
+
+
 def cast_prefill(Q: torch.Tensor, K: torch.Tensor, r: int, max_iter: int, tol: float,
-                 init: str = "randn", init_factors_override=None):
-    """fp32 up-cast, initial factors, factorisation, results rounded to K's dtype:
-    lrqk_attention.py:772-800."""
+                 init: str = "randn", init_factors_override=None, lambda_q: float = 1.0, lambda_k: float = 1.0):
+    """fp32 up-cast, initial factors, factorisation (unit-weight form when both weights are 1,
+    :790), results rounded to K's dtype: lrqk_attention.py:772-800."""
     out_dtype = K.dtype
     Q32, K32 = Q.to(torch.float32), K.to(torch.float32)
     if init_factors_override is not None:
         aq, ak = (t.to(torch.float32) for t in init_factors_override)
     else:
         aq, ak = init_factors(Q32, K32, r, init)
-    return tuple(o.to(out_dtype) for o in prefill_factorize(Q32, K32, aq, ak, max_iter, tol))
+    if lambda_q == 1.0 and lambda_k == 1.0:
+        out = prefill_factorize(Q32, K32, aq, ak, max_iter, tol)
+    else:
+        out = prefill_factorize_weighted(Q32, K32, aq, ak, lambda_q, lambda_k, max_iter, tol)
+    return tuple(o.to(out_dtype) for o in out)
 
 
 # ----------------------------------------------------------------------------
@@ -230,12 +273,54 @@ def decode_project_update(B_Q: torch.Tensor, A_act: torch.Tensor, B_K: torch.Ten
     return B_Q, B_K, q_hat, k_hat
 
 
-def cast_decode(B_Q, A_act, B_K, K_act, q, k, max_iter: int, tol: float):
-    """fp32 up-cast of every operand, update, results rounded to k's dtype:
-    lrqk_attention.py:803-839."""
+def decode_project_update_weighted(B_Q: torch.Tensor, A_act: torch.Tensor, B_K: torch.Tensor,
+                                   K_act: torch.Tensor, q: torch.Tensor, k: torch.Tensor,
+                                   lambda1: float, lambda2: float, max_iter: int, tol: float,
+                                   return_iters: bool = False):
+    """The decode update with weights (lrqk_attention.py:433-519), taken whenever either differs
+    from 1 (:820-837): lambda2 weighs the active set's terms, lambda1 the new token's own
+    q k^T term --
+        q_hat = (q B_Q^T + l2 (q K_act^T) A_act + l1 (q k^T) k_hat)(B_Q B_Q^T + l2 A_act^T A_act + l1 k_hat^T k_hat)^-1
+        k_hat'= (k B_K^T + l1 (q k^T) q_hat)(B_K B_K^T + l1 q_hat^T q_hat)^-1
+    (:462-495); everything else as in the unit-weight form.
+    """
+    max_iter = max(max_iter, 1)
+    k_bk = k @ _t(B_K)
+    gram_bk = B_K @ _t(B_K)
+    q_rhs = q @ _t(B_Q) + lambda2 * ((q @ _t(K_act)) @ A_act)
+    gram_q = B_Q @ _t(B_Q) + lambda2 * (_t(A_act) @ A_act)
+    qk = lambda1 * (q @ _t(k))
+
+    k_hat = _solve_right(gram_bk, k_bk)
+    iters = 0
+    for _ in range(max_iter):
+        q_hat = _solve_right(gram_q + lambda1 * (_t(k_hat) @ k_hat), q_rhs + qk @ k_hat)
+        new_k_hat = _solve_right(gram_bk + lambda1 * (_t(q_hat) @ q_hat), k_bk + qk @ q_hat)
+        delta = torch.nn.functional.mse_loss(k_hat, new_k_hat)
+        k_hat = new_k_hat
+        iters += 1
+        if delta < tol:
+            break
+
+    dBQ = _t(q_hat) @ (q_hat @ B_Q - q)
+    dBK = _t(k_hat) @ (k_hat @ B_K - k)
+    B_Q = B_Q - _line_search_step(dBQ, q_hat) * dBQ
+    B_K = B_K - _line_search_step(dBK, k_hat) * dBK
+    if return_iters:
+        return B_Q, B_K, q_hat, k_hat, iters
+    return B_Q, B_K, q_hat, k_hat
+
+
+def cast_decode(B_Q, A_act, B_K, K_act, q, k, max_iter: int, tol: float,
+                lambda_dec_q: float = 1.0, lambda_dec_k: float = 1.0):
+    """fp32 up-cast of every operand, update (unit-weight form when both weights are 1, :820),
+    results rounded to k's dtype: lrqk_attention.py:803-839."""
     f = torch.float32
-    out = decode_project_update(B_Q.to(f), A_act.to(f), B_K.to(f), K_act.to(f), q.to(f), k.to(f),
-                                max_iter, tol)
+    ops = (B_Q.to(f), A_act.to(f), B_K.to(f), K_act.to(f), q.to(f), k.to(f))
+    if lambda_dec_q == 1.0 and lambda_dec_k == 1.0:
+        out = decode_project_update(*ops, max_iter, tol)
+    else:
+        out = decode_project_update_weighted(*ops, lambda_dec_q, lambda_dec_k, max_iter, tol)
     return tuple(o.to(k.dtype) for o in out)
 
 
@@ -440,8 +525,10 @@ class OracleLayer:
 
     def __init__(self, r: int, k: int, m: int, groups: int, max_iter=(2, 2), tol=(1e-2, 1e-2),
                  capacity: int = 4096, init: str = "randn", scaling_ratio: float = 1.5,
-                 faithful: bool = False):
+                 faithful: bool = False, weights=(1.0, 1.0, 1.0, 1.0)):
         self.r, self.k, self.m, self.groups = r, k, m, groups
+        # (lambda_Q, lambda_K, lambda_dec_q, lambda_dec_k): :1040, :1066-1072, used at :1435-1436, :1535-1536
+        self.weights = (weights,) * 4 if isinstance(weights, float) else tuple(weights)
         self.max_iter = tuple(max_iter) if isinstance(max_iter, (tuple, list)) else (max_iter, max_iter)
         self.tol = tuple(tol) if isinstance(tol, (tuple, list)) else (tol, tol)
         self.capacity, self.init, self.scaling_ratio, self.faithful = capacity, init, scaling_ratio, faithful
@@ -475,7 +562,7 @@ class OracleLayer:
         self.Vres = torch.zeros_like(self.Kres)
         self.current_len = s
         A_Q, B_Q, A_K, B_K = cast_prefill(Q, Krep, self.r, self.max_iter[0], self.tol[0], self.init,
-                                          init_factors_override)
+                                          init_factors_override, self.weights[0], self.weights[1])
         self.B_Q, self.B_K = B_Q, B_K
         cap = self._first_capacity(s)
         self.A_K = torch.zeros((b, hq, cap, self.r), dtype=A_K.dtype)
@@ -544,7 +631,8 @@ class OracleLayer:
             # every token is still resident: project against all earlier rows, no selection
             n = self.current_len - 1
             B_Q, B_K, q_hat, k_hat = cast_decode(self.B_Q, self.A_K[:, :, :self.a_len], self.B_K, self.Kres[:, :, :n],
-                                                 q, expand_kv_heads(k, g), self.max_iter[1], self.tol[1])
+                                                 q, expand_kv_heads(k, g), self.max_iter[1], self.tol[1],
+                                                 self.weights[2], self.weights[3])
             self.B_Q, self.B_K = B_Q, B_K
             self.A_K = self._ensure(self.A_K, self.a_len, 1)
             self.A_K[:, :, self.a_len:self.a_len + 1] = k_hat
@@ -562,7 +650,7 @@ class OracleLayer:
         idx = torch.from_numpy(act.astype(np.int64))[..., None].expand(-1, -1, -1, self.r)
         A_act = torch.gather(self.A_K, 2, idx)
         B_Q, B_K, q_hat, k_hat = cast_decode(self.B_Q, A_act, self.B_K, self.Kres, q, expand_kv_heads(k, g),
-                                             self.max_iter[1], self.tol[1])
+                                             self.max_iter[1], self.tol[1], self.weights[2], self.weights[3])
         self.B_Q, self.B_K = B_Q, B_K
         self.A_K = self._ensure(self.A_K, self.a_len, 1)
         self.A_K[:, :, self.a_len:self.a_len + 1] = k_hat               # :1231

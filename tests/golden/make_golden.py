@@ -57,6 +57,14 @@ CASES = {
     # num_active_tokens (:1928-1958).
     "short_exact_k": dict(seed=43, init_seed=9, bsz=1, hq=4, hkv=1, seq=32, d=128, r=8, k=32, m=4,
                           max_iter=(2, 2), tol=1e-2, init="randn", steps=10),
+    # weights other than 1 on all four terms: the general forms of both solvers (:218-309, :433-519).
+    "weighted": dict(seed=51, init_seed=10, bsz=1, hq=4, hkv=2, seq=384, d=128, r=16, k=48, m=8,
+                     max_iter=(3, 3), tol=1e-4, init="randn", steps=10, weights=(0.5, 2.0, 0.75, 1.5)),
+    # only the prompt's weights differ from 1 / only the decode step's (each solver's dispatch is its own).
+    "weighted_prompt_only": dict(seed=52, init_seed=11, bsz=1, hq=2, hkv=1, seq=256, d=128, r=8, k=32, m=4,
+                                 max_iter=(2, 2), tol=1e-2, init="top", steps=6, weights=(1.0, 3.0, 1.0, 1.0)),
+    "weighted_decode_only": dict(seed=53, init_seed=12, bsz=2, hq=2, hkv=2, seq=200, d=128, r=8, k=32, m=4,
+                                 max_iter=(2, 2), tol=1e-2, init="top", steps=6, weights=(1.0, 1.0, 2.5, 0.4)),
 }
 
 
@@ -112,7 +120,7 @@ def run_case(ref, name: str, c: dict) -> dict:
 
     f = Recorder(num_lite_tokens=c["m"], attn_topk=c["k"], num_key_value_groups=groups, r=c["r"],
                  max_iter=c["max_iter"], tol=c["tol"], capacity=c["seq"] + 64,
-                 init_aq_ak_method=c["init"])
+                 init_aq_ak_method=c["init"], weights=tuple(c.get("weights", (1.0, 1.0, 1.0, 1.0))))
     torch.manual_seed(c["init_seed"])
     f.prefill(Q.clone(), K.clone(), V.clone())
     out = {"config": np.array(json.dumps(c))}

@@ -10,7 +10,7 @@ def state_from_oracle(lay: "orc.OracleLayer", kv_heads: int, max_iter: int = 2) 
     b, hq, a_cap, r = lay.A_K.shape
     d = lay.Kres.shape[-1]
     st = LayerState(b, hq, kv_heads, d, r, lay.k, lay.m, a_capacity=a_cap, host_capacity=lay.host.shape[2],
-                    dtype=lay.A_K.dtype, max_iter=max_iter)
+                    dtype=lay.A_K.dtype, max_iter=max_iter, weights=getattr(lay, "weights", (1.0, 1.0, 1.0, 1.0)))
     sync_state(st, lay)
     return st
 

@@ -293,11 +293,27 @@ def test_flash_decode_matches_oracle(dtype, d, rows, bsz, hq):
     (torch.bfloat16, 64, 4096, 128, 1, 2, 1, 4, 128),  # rank, set size and alternations of the 256K configuration
 ])
 def test_project_update_matches_oracle(dtype, r, k, m, bsz, hq, hkv, max_iter, d):
+    _check_project_update(dtype, r, k, m, bsz, hq, hkv, max_iter, d, (1.0, 1.0))
+
+
+@pytest.mark.parametrize("dtype,r,k,m,bsz,hq,hkv,max_iter,d,lam", [
+    (torch.float32, 16, 256, 16, 1, 4, 2, 2, 128, (0.75, 1.5)),     # lambda_dec_q, lambda_dec_k
+    (torch.bfloat16, 32, 512, 64, 1, 8, 2, 3, 128, (2.5, 0.4)),
+    (torch.float32, 8, 64, 4, 2, 2, 2, 2, 64, (1.0, 0.3)),          # one weight at 1 still takes the general form
+    (torch.bfloat16, 64, 300, 20, 1, 2, 2, 2, 128, (0.0, 2.0)),     # no q k^T term of the new token at all
+    (torch.bfloat16, 16, 1024, 32, 1, 4, 2, 2, 128, (4.0, 1.0)),
+])
+def test_project_update_with_weights_matches_oracle(dtype, r, k, m, bsz, hq, hkv, max_iter, d, lam):
+    _check_project_update(dtype, r, k, m, bsz, hq, hkv, max_iter, d, lam)
+
+
+def _check_project_update(dtype, r, k, m, bsz, hq, hkv, max_iter, d, lam):
     g = torch.Generator().manual_seed(r * k)
     cap = 3000 if k < 2000 else 6000
     grp = hq // hkv
     st = _state(bsz=bsz, q_heads=hq, kv_heads=hkv, head_dim=d, r=r, k=k, m=m, a_capacity=cap,
-                host_capacity=16, dtype=dtype, with_host=False, max_iter=max(1, max_iter))
+                host_capacity=16, dtype=dtype, with_host=False, max_iter=max(1, max_iter),
+                weights=(1.0, 1.0) + tuple(lam))
     A = torch.randn(bsz, hq, cap, r, generator=g).to(dtype)
     append_row = cap - 500
     A[:, :, append_row:] = 0                     # the row being appended still reads as zero
@@ -319,9 +335,12 @@ def test_project_update_matches_oracle(dtype, r, k, m, bsz, hq, hkv, max_iter, d
         A_act = torch.gather(A, 2, act[..., None].expand(-1, -1, -1, r))
         krep = kn.repeat_interleave(grp, dim=1)[:, :, None]
         f = torch.float32
-        eBQ, eBK, eq, ek, iters = orc.decode_project_update(
-            BQ.to(f), A_act.to(f), BK.to(f), Kres.to(f), q[:, :, None].to(f), krep.to(f), max_iter, tol_exit,
-            return_iters=True)
+        ops = (BQ.to(f), A_act.to(f), BK.to(f), Kres.to(f), q[:, :, None].to(f), krep.to(f))
+        if tuple(lam) == (1.0, 1.0):
+            eBQ, eBK, eq, ek, iters = orc.decode_project_update(*ops, max_iter, tol_exit, return_iters=True)
+        else:
+            eBQ, eBK, eq, ek, iters = orc.decode_project_update_weighted(*ops, lam[0], lam[1], max_iter, tol_exit,
+                                                                         return_iters=True)
         assert int(st.counters[2].item()) == iters
         tol = 2e-4                                   # the solves amplify fp32 round-off
         if dtype == torch.float32:
@@ -343,7 +362,7 @@ def _load_case(name):
     return z, json.loads(str(z["config"]))
 
 
-@pytest.mark.parametrize("name", ["cfg0", "wrap_top", "topcol_g1"])
+@pytest.mark.parametrize("name", ["cfg0", "wrap_top", "topcol_g1", "weighted", "weighted_decode_only"])
 def test_layer_step_replay_against_oracle_and_golden(name):
     """Every step starts from the oracle's state, so one stage's round-off cannot cascade:
     integer outputs must then equal the oracle's exactly whenever the device scores rank the
@@ -352,7 +371,7 @@ def test_layer_step_replay_against_oracle_and_golden(name):
     z, c = _load_case(name)
     Q, K, V = orc.make_prompt(c["seed"], c["bsz"], c["hq"], c["hkv"], c["seq"], c["d"])
     lay = orc.OracleLayer(c["r"], c["k"], c["m"], c["hq"] // c["hkv"], c["max_iter"], c["tol"],
-                          capacity=c["seq"] + 64, init=c["init"])
+                          capacity=c["seq"] + 64, init=c["init"], weights=tuple(c.get("weights", (1.0, 1.0, 1.0, 1.0))))
     torch.manual_seed(c["init_seed"])
     lay.prefill(Q, K, V)
     st = state_from_oracle(lay, c["hkv"], max_iter=c["max_iter"][1])

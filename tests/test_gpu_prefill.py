@@ -22,11 +22,12 @@ def _rel(a, b):
     return float((a - b).abs().max() / b.abs().max().clamp_min(1e-30))
 
 
-def _factorize(Q, K, aq, ak, r, sweeps, tol, groups):
+def _factorize(Q, K, aq, ak, r, sweeps, tol, groups, lam=(1.0, 1.0)):
     from lrqk_b200 import _lib
     from lrqk_b200.state import LayerState, _ptr, _stream
     b, hq, s, d = Q.shape
-    st = LayerState(b, hq, K.shape[1], d, r, 16, 4, a_capacity=s + 8, host_capacity=16, dtype=Q.dtype, with_host=False)
+    st = LayerState(b, hq, K.shape[1], d, r, 16, 4, a_capacity=s + 8, host_capacity=16, dtype=Q.dtype, with_host=False,
+                    weights=tuple(lam) + (1.0, 1.0))
     dq, dk = Q.cuda().contiguous(), K.cuda().contiguous()
     daq, dak = aq.float().cuda().contiguous(), ak.float().cuda().contiguous()
     nb = st.lib.lrqk_prefill_factorize_workspace_bytes(C.byref(st.c), s)
@@ -74,6 +75,94 @@ def test_prefill_factorize_matches_reference_algorithm(dtype, r, b, hq, hkv, s, 
     px = (A_K.float() @ last.float()[..., None])[..., 0]
     pr = (eAK @ eAQ[:, :, -1][..., None])[..., 0]
     assert _rel(px, pr) < (2e-3 if dtype == torch.float32 else 3e-2)
+
+
+@pytest.mark.parametrize("dtype,r,b,hq,hkv,s,sweeps,tol,lam", [
+    (torch.float32, 16, 1, 4, 2, 2048, 3, 1e-9, (0.5, 2.0)),       # lambda_Q, lambda_K
+    (torch.float32, 8, 2, 2, 2, 1500, 2, 1e-9, (1.0, 3.0)),        # one weight at 1 still takes the general form
+    (torch.float32, 16, 1, 4, 2, 2048, 4, 50.0, (0.25, 0.25)),     # leaves early
+    (torch.bfloat16, 32, 1, 4, 2, 4096, 2, 1e-9, (2.0, 0.5)),
+    (torch.bfloat16, 64, 1, 2, 1, 3000, 2, 1e-9, (0.0, 1.5)),
+])
+def test_prefill_factorize_with_weights_matches_reference_algorithm(dtype, r, b, hq, hkv, s, sweeps, tol, lam):
+    """The general form (lrqk_attention.py:218-309): both left factors renewed from the factors a sweep
+    started with, weights on the B terms."""
+    Q, K, _ = orc.make_prompt(s + r + 1, b, hq, hkv, s, 128, dtype=dtype)
+    g = torch.Generator().manual_seed(r + 7)
+    aq = torch.randn(b, hq, s, r, generator=g)
+    ak = torch.randn(b, hq, s, r, generator=g)
+    if dtype == torch.bfloat16:
+        aq, ak = aq.bfloat16().float(), ak.bfloat16().float()
+    groups = hq // hkv
+    A_K, B_Q, B_K, last, n_sw = _factorize(Q, K, aq, ak, r, sweeps, tol, groups, lam)
+    Krep = orc.expand_kv_heads(K, groups).float()
+    eAQ, eBQ, eAK, eBK, e_sw = orc.prefill_factorize_weighted(Q.float(), Krep, aq, ak, lam[0], lam[1], sweeps, tol,
+                                                               return_sweeps=True)
+    assert n_sw == e_sw
+    tol_e = 5e-4 if dtype == torch.float32 else 2e-2
+    assert _rel(A_K.float(), eAK) < tol_e
+    assert _rel(B_Q.float(), eBQ) < tol_e and _rel(B_K.float(), eBK) < tol_e
+    assert _rel(last.float(), eAQ[:, :, -1]) < tol_e
+    err = lambda A, B: float((Krep - A.float() @ B.float()).norm() / Krep.norm())
+    ours, ref = err(A_K, B_K), err(eAK.to(dtype), eBK.to(dtype))
+    assert abs(ours - ref) <= 0.01 * ref + 1e-6
+    # and it is not the unit-weight result
+    uAQ, uBQ, uAK, uBK = orc.prefill_factorize(Q.float(), Krep, aq, ak, sweeps, tol)
+    assert _rel(uBK, eBK) > 10 * tol_e or _rel(uBQ, eBQ) > 10 * tol_e
+
+
+@pytest.mark.parametrize("name", ["weighted", "weighted_prompt_only", "weighted_decode_only"])
+def test_factory_with_weights_follows_the_reference_trace(name):
+    """LightAttentionIndicesFactory(weights=...) through prompt and decode steps against the trace the
+    reference recorded with the same weights: factors to fp32 round-off of the r x r solves, and the
+    selection/table/resident rows identical on the steps where the device's scores rank the candidates
+    like the reference's."""
+    import hashlib
+    import json
+    import os
+    from lrqk_b200 import LightAttentionIndicesFactory
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", f"{name}.npz"))
+    c = json.loads(str(z["config"]))
+    groups = c["hq"] // c["hkv"]
+    Q, K, V = orc.make_prompt(c["seed"], c["bsz"], c["hq"], c["hkv"], c["seq"], c["d"])
+    class Factory(LightAttentionIndicesFactory):
+        def _initial_factors(self, Qd, Kd):
+            # the reference drew its starting factors from the CPU generator: hand over the same ones
+            torch.manual_seed(c["init_seed"])
+            aq0, ak0 = orc.init_factors(Q.float(), orc.expand_kv_heads(K, groups).float(), c["r"], c["init"])
+            return aq0.cuda().contiguous(), ak0.cuda().contiguous()
+
+    fac = Factory(num_lite_tokens=c["m"], attn_topk=c["k"], num_key_value_groups=groups, r=c["r"],
+                  max_iter=tuple(c["max_iter"]), tol=c["tol"], capacity=c["seq"] + 64, init_aq_ak_method=c["init"],
+                  weights=tuple(c["weights"]))
+    fac.prefill(Q.cuda(), K.cuda(), V.cuda())
+    torch.cuda.synchronize()
+    st = fac.state
+    assert _rel(st.B_Q.cpu(), torch.from_numpy(z["prefill_B_Q"])) < 5e-4
+    assert _rel(st.B_K.cpu(), torch.from_numpy(z["prefill_B_K"])) < 5e-4
+    assert _rel(st.A_K[:, :, :c["seq"]:8].cpu(), torch.from_numpy(z["prefill_A_K_every8"])) < 5e-4
+    sha = lambda t: hashlib.sha256(np.ascontiguousarray(t.cpu().numpy()).tobytes()).hexdigest()
+    exact = int(np.array_equal(fac.hit_indices[..., 0].cpu().numpy(), z["prefill_table"]))
+    agree = exact
+    for s in range(c["steps"]):
+        q, k, v = orc.make_step(c["seed"], s, c["bsz"], c["hq"], c["hkv"], c["d"])
+        a_row = fac.current_len
+        Kres, Vres = fac.decode(q.cuda(), k.cuda(), v.cuda())
+        torch.cuda.synchronize()
+        assert _rel(st.A_K[:, :, a_row:a_row + 1].cpu(), torch.from_numpy(z[f"s{s}_k_hat"])) < 2e-3
+        lite = z[f"s{s}_lite"]
+        assert list(lite[:c["m"]]) == fac.lite_indices
+        assert (int(lite[-3]), int(lite[-2]), int(lite[-1])) == (fac.lite_len, fac.current_len, len(fac.KVcpu))
+        same = np.array_equal(st.wanted.cpu().numpy(), z[f"s{s}_wanted"])
+        if same and agree == s + 1 and np.array_equal(fac.hit_indices[..., 0].cpu().numpy(), z[f"s{s}_table"]):
+            agree += 1
+            assert sha(Kres) == str(z[f"s{s}_Kres_sha256"]) and sha(Vres) == str(z[f"s{s}_Vres_sha256"])
+        overlap = np.mean([len(np.intersect1d(st.wanted.cpu().numpy()[b, h], z[f"s{s}_wanted"][b, h])) / c["k"]
+                           for b in range(c["bsz"]) for h in range(c["hq"])])
+        assert overlap > 0.97
+    assert agree >= 1            # the selection after the prompt, at least, is the reference's
+    assert _rel(st.B_Q.cpu(), torch.from_numpy(z["final_B_Q"])) < 5e-3
+    fac.close()
 
 
 @pytest.mark.parametrize("init", ["top", "topcol", "randn"])

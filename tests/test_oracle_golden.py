@@ -11,7 +11,8 @@ import torch
 import lrqk_oracle as orc
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
-CASES = ["cfg0", "wrap_top", "topcol_g1", "short_k3", "short_exact_k"]
+CASES = ["cfg0", "wrap_top", "topcol_g1", "short_k3", "short_exact_k", "weighted", "weighted_prompt_only",
+         "weighted_decode_only"]
 
 
 def _sha(t):
@@ -27,7 +28,8 @@ def _load(name):
 def _run(c, faithful):
     Q, K, V = orc.make_prompt(c["seed"], c["bsz"], c["hq"], c["hkv"], c["seq"], c["d"])
     lay = orc.OracleLayer(c["r"], c["k"], c["m"], c["hq"] // c["hkv"], c["max_iter"], c["tol"],
-                          capacity=c["seq"] + 64, init=c["init"], faithful=faithful)
+                          capacity=c["seq"] + 64, init=c["init"], faithful=faithful,
+                          weights=tuple(c.get("weights", (1.0, 1.0, 1.0, 1.0))))
     torch.manual_seed(c["init_seed"])
     lay.prefill(Q, K, V)
     return lay
