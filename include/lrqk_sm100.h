@@ -256,6 +256,15 @@ int lrqk_peer_buffer_destroy(void *dev_ptr);
  * `out` may be NULL when only the exchange buffer is wanted. */
 int lrqk_flash_decode_push(const lrqk_layer *L, const void *q, void *out, int32_t rows, float scale,
                            void *workspace, const lrqk_peer_group *g, int32_t seq, lrqk_stream_t stream);
+/* Miss fetch and attention in ONE kernel: lrqk_miss_gather (driven by `mask`, the byte per slot that
+ * lrqk_slot_diff or the step's scoring kernel wrote, and the slot table it updated) followed by
+ * lrqk_flash_decode over all k + m rows (or lrqk_flash_decode_push when `g` is not NULL; `out` may
+ * then be NULL) -- with the same results bit for bit: the thread that attends to a refilled slot
+ * reads that row from the host store itself (take_along_dim_with_mask + index_put_ + the attention
+ * call of the reference, lrqk_attention.py:1570-1613, in one pass), and stores it into K_res/V_res
+ * on the side.  lrqk_layer_step uses it whenever the step ends in attention. */
+int lrqk_fetch_attend(const lrqk_layer *L, const uint8_t *mask, const void *q, void *out, float scale,
+                      void *workspace, const struct lrqk_peer_group *g, int32_t seq, lrqk_stream_t stream);
 /* Wait (bounded) until push `seq` of every rank has arrived in this rank's buffer, then copy the
  * gathered rows [world][heads_per_rank][d] to gathered_out if it is not NULL.  If the wait runs
  * out, *status (device int32) is set to LRQK_ETIMEOUT and the copy is skipped; the kernel always

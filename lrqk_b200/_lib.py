@@ -102,6 +102,8 @@ _SIGNATURES = {
     "lrqk_peer_buffer_destroy": (C.c_int, [C.c_void_p]),
     "lrqk_flash_decode_push": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_void_p, C.c_int32, C.c_float, C.c_void_p,
                                          C.POINTER(PeerGroup), C.c_int32, C.c_void_p]),
+    "lrqk_fetch_attend": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_void_p,
+                                    C.POINTER(PeerGroup), C.c_int32, C.c_void_p]),
     "lrqk_peer_set_wait_polls": (C.c_int, [C.c_uint32]),
     "lrqk_allgather_wait": (C.c_int, [C.POINTER(PeerGroup), C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
     "lrqk_layer_step": (C.c_int, [C.POINTER(Layer), C.POINTER(StepArgs), C.c_void_p]),

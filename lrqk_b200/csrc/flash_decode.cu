@@ -14,6 +14,14 @@
 //
 // The wait on the mbarrier is bounded: if it runs out, the CTA records it in the status word,
 // contributes an empty partial and still takes its ticket, so nothing is left waiting.
+//
+// Miss fetch fused in (FETCH): a slot whose mask byte is set is refilled from the page-locked host
+// store by the very thread that attends to it -- its 16-byte piece of the value row comes over the
+// host link straight into the register the weighted sum reads, its piece of the key row by an
+// asynchronous 16-byte copy into the staging buffer (this variant stages every key piece that way
+// instead of one bulk copy), and both pieces are stored into the resident rows on the side.  Same threads, same pieces, same order
+// of operations as the fetch kernel followed by this kernel without FETCH: bit-identical results,
+// one launch and one pass over the missed rows fewer.
 #include <math.h>
 #include <stdio.h>
 
@@ -39,9 +47,20 @@ struct AttnParams {
   int32_t splits, chunk;
   float scale_log2;   // softmax scale * log2(e)
   PushTargets push;   // world == 0: no exchange with other ranks
+  // FETCH only: slots [0, k) with a set mask byte are refilled from host row table[slot]
+  const uint8_t *mask;      // [N][k]
+  const int32_t *table;     // [N][k]
+  const char *host_kv;      // [B][Hkv][host_capacity][K row | V row]
+  void *K_res_w, *V_res_w;
+  int64_t host_capacity;
+  int32_t k, q_heads, groups, kv_heads;
 };
 
-template <typename T, int D>
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void *src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+
+template <typename T, int D, bool FETCH>
 __global__ void __launch_bounds__(kAThreads, 4) flash_decode_kernel(AttnParams p) {
   constexpr int EPV = Elt<T>::kPerVec;            // elements per 16-byte vector
   constexpr int LPR = D / EPV;                    // lanes per row
@@ -64,6 +83,19 @@ __global__ void __launch_bounds__(kAThreads, 4) flash_decode_kernel(AttnParams p
   const int r_end = min(p.rows, r_begin + p.chunk);
   const char *Kg = reinterpret_cast<const char *>(p.K_res) + ((int64_t)n * p.slots) * ROW_BYTES;
   const char *Vg = reinterpret_cast<const char *>(p.V_res) + ((int64_t)n * p.slots) * ROW_BYTES + lir * 16;
+  // FETCH: this head's mask and slot table, this thread's 16-byte piece of its KV head's host rows
+  const uint8_t *mk = nullptr;
+  const int32_t *tb = nullptr;
+  const char *hrow = nullptr;
+  char *Kw = nullptr, *Vw = nullptr;
+  if constexpr (FETCH) {
+    mk = p.mask + (int64_t)n * p.k;
+    tb = p.table + (int64_t)n * p.k;
+    const int b_idx = n / p.q_heads, h = n % p.q_heads;
+    hrow = p.host_kv + ((int64_t)b_idx * p.kv_heads + h / p.groups) * p.host_capacity * (2 * ROW_BYTES) + lir * 16;
+    Kw = reinterpret_cast<char *>(p.K_res_w) + ((int64_t)n * p.slots) * ROW_BYTES + lir * 16;
+    Vw = reinterpret_cast<char *>(p.V_res_w) + ((int64_t)n * p.slots) * ROW_BYTES + lir * 16;
+  }
 
   pdl_launch_dependents();
   if (tid == 0) {
@@ -84,11 +116,13 @@ __global__ void __launch_bounds__(kAThreads, 4) flash_decode_kernel(AttnParams p
     const int nrows = min(STAGE_ROWS, r_end - base);
     // everything this round reads is requested before anything is waited for: the keys by one bulk
     // copy into shared memory, the values straight into registers
-    if (tid == 0) {
-      const uint32_t bytes = (uint32_t)nrows * ROW_BYTES;
-      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
-      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                   ::"r"(smem_addr(sK)), "l"(Kg + (int64_t)base * ROW_BYTES), "r"(bytes), "r"(smem_addr(bar)) : "memory");
+    if constexpr (!FETCH) {
+      if (tid == 0) {
+        const uint32_t bytes = (uint32_t)nrows * ROW_BYTES;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(smem_addr(sK)), "l"(Kg + (int64_t)base * ROW_BYTES), "r"(bytes), "r"(smem_addr(bar)) : "memory");
+      }
     }
     if (base == r_begin) {
       float raw[EPV];
@@ -97,13 +131,42 @@ __global__ void __launch_bounds__(kAThreads, 4) flash_decode_kernel(AttnParams p
       for (int e = 0; e < EPV / 2; ++e) qf[e] = make_float2(raw[2 * e] * p.scale_log2, raw[2 * e + 1] * p.scale_log2);
     }
     uint4 vv[RPT];
+    uint32_t fetch_bits = 0;  // which of this thread's rows come from the host store
+    if constexpr (FETCH) {
+      // No bulk copy here: every thread brings its own 16-byte piece of each of its key rows into the
+      // staging buffer with an asynchronous copy -- from the host store for a slot that is being refilled,
+      // from the resident rows otherwise -- so that key and value of a missed row are requested together.
 #pragma unroll
-    for (int i = 0; i < RPT; ++i) {
-      const int j = grp + i * GROUPS;
-      vv[i] = j < nrows ? ld_stream16(Vg + (int64_t)(base + j) * ROW_BYTES) : make_uint4(0u, 0u, 0u, 0u);
+      for (int i = 0; i < RPT; ++i) {
+        const int j = grp + i * GROUPS;
+        const int slot = base + j;
+        if (j < nrows) {
+          int64_t pos = -1;
+          if (slot < p.k && mk[slot] != 0) pos = tb[slot];
+          if (pos >= 0 && pos < p.host_capacity) {  // (a malformed entry is skipped, never dereferenced)
+            const char *src = hrow + pos * (2 * ROW_BYTES);
+            cp_async16(smem_addr(sK + (size_t)j * D + lir * EPV), src);
+            vv[i] = ld16(src + ROW_BYTES);
+            fetch_bits |= 1u << i;
+          } else {
+            cp_async16(smem_addr(sK + (size_t)j * D + lir * EPV), Kg + (int64_t)slot * ROW_BYTES + lir * 16);
+            vv[i] = ld_stream16(Vg + (int64_t)slot * ROW_BYTES);
+          }
+        } else {
+          vv[i] = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    } else {
+#pragma unroll
+      for (int i = 0; i < RPT; ++i) {
+        const int j = grp + i * GROUPS;
+        vv[i] = j < nrows ? ld_stream16(Vg + (int64_t)(base + j) * ROW_BYTES) : make_uint4(0u, 0u, 0u, 0u);
+      }
+      // ---- scores of this round -------------------------------------------------------------
+      if (!mbar_wait_bounded(bar, parity)) timed_out = true;
     }
-    // ---- scores of this round -------------------------------------------------------------
-    if (!mbar_wait_bounded(bar, parity)) timed_out = true;
     float sc[RPT];
 #pragma unroll
     for (int i = 0; i < RPT; ++i) {
@@ -137,6 +200,19 @@ __global__ void __launch_bounds__(kAThreads, 4) flash_decode_kernel(AttnParams p
       }
 #pragma unroll
       for (; o >= 1; o >>= 1) sc[0] += __shfl_xor_sync(0xFFFFFFFFu, sc[0], o);
+    }
+    if constexpr (FETCH) {
+      // ... and into the resident rows, for the steps to come
+      if (fetch_bits) {
+#pragma unroll
+        for (int i = 0; i < RPT; ++i) {
+          if (fetch_bits >> i & 1u) {
+            const int j = grp + i * GROUPS;
+            st16(Kw + (int64_t)(base + j) * ROW_BYTES, *reinterpret_cast<const uint4 *>(sK + (size_t)j * D + lir * EPV));
+            st16(Vw + (int64_t)(base + j) * ROW_BYTES, vv[i]);
+          }
+        }
+      }
     }
     float mx = -INFINITY;
     {
@@ -268,10 +344,15 @@ constexpr size_t kAttnSmem = (size_t)kStageBytes + (kStageBytes / 128) * sizeof(
 size_t ticket_region_bytes(int n_heads) { return ((size_t)(n_heads + 1) * sizeof(int32_t) + 255) / 256 * 256; }
 
 int launch_flash_decode(const lrqk_layer *L, const void *q, void *out, int32_t rows, float scale, void *scratch,
-                        cudaStream_t s, const lrqk_peer_group *g = nullptr, int32_t seq = 0) {
+                        cudaStream_t s, const lrqk_peer_group *g = nullptr, int32_t seq = 0,
+                        const uint8_t *fetch_mask = nullptr) {
   const int n_heads = L->bsz * L->q_heads;
   AttnParams p;
   p.push.world = 0;
+  p.mask = fetch_mask; p.table = L->table; p.host_kv = reinterpret_cast<const char *>(L->host_kv);
+  p.K_res_w = L->K_res; p.V_res_w = L->V_res;
+  p.host_capacity = L->host_capacity;
+  p.k = L->k; p.q_heads = L->q_heads; p.kv_heads = L->kv_heads; p.groups = L->q_heads / L->kv_heads;
   if (g) {
     const size_t esz = elt_size(L->dtype);
     const size_t half = peer_data_bytes(g->world, g->heads_per_rank, g->head_dim, g->dtype) / 2;
@@ -298,10 +379,17 @@ int launch_flash_decode(const lrqk_layer *L, const void *q, void *out, int32_t r
   dim3 grid(p.splits, n_heads, 1);
 #define LRQK_ATTN_LAUNCH(T, D)                                                                              \
   do {                                                                                                      \
-    auto kern = flash_decode_kernel<T, D>;                                                                  \
-    static SmemOptIn opt_in;                                                                                \
-    LRQK_CUDA_TRY(opt_in.ensure(kern, kAttnSmem));                                                          \
-    LRQK_CUDA_TRY(launch_dependent(kern, grid, dim3(kAThreads), kAttnSmem, s, 0, p));                       \
+    if (fetch_mask) {                                                                                       \
+      auto kern = flash_decode_kernel<T, D, true>;                                                          \
+      static SmemOptIn opt_in;                                                                              \
+      LRQK_CUDA_TRY(opt_in.ensure(kern, kAttnSmem));                                                        \
+      LRQK_CUDA_TRY(launch_dependent(kern, grid, dim3(kAThreads), kAttnSmem, s, 0, p));                     \
+    } else {                                                                                                \
+      auto kern = flash_decode_kernel<T, D, false>;                                                         \
+      static SmemOptIn opt_in;                                                                              \
+      LRQK_CUDA_TRY(opt_in.ensure(kern, kAttnSmem));                                                        \
+      LRQK_CUDA_TRY(launch_dependent(kern, grid, dim3(kAThreads), kAttnSmem, s, 0, p));                     \
+    }                                                                                                       \
   } while (0)
   if (L->head_dim == 128) {
     LRQK_DISPATCH_DTYPE(L->dtype, T, LRQK_ATTN_LAUNCH(T, 128));
@@ -356,6 +444,25 @@ extern "C" int lrqk_flash_decode_push(const lrqk_layer *L, const void *q, void *
   if (rc != LRQK_OK) return rc;
   if (g->heads_per_rank != L->bsz * L->q_heads || g->head_dim != L->head_dim || g->dtype != L->dtype) return LRQK_EINVAL;
   return launch_flash_decode(L, q, out, rows, scale, workspace, as_stream(stream), g, seq);
+}
+
+extern "C" int lrqk_fetch_attend(const lrqk_layer *L, const uint8_t *mask, const void *q, void *out, float scale,
+                                 void *workspace, const lrqk_peer_group *g, int32_t seq, lrqk_stream_t stream) {
+  using namespace lrqk;
+  if (!L) return LRQK_EINVAL;
+  const int32_t rows = L->k + L->m;
+  int rc = check_attn_args(L, q, out, rows);
+  if (rc != LRQK_OK) return rc;
+  if (!workspace || !mask || !L->table || !L->host_kv || L->host_capacity <= 0) return LRQK_EINVAL;
+  if (g) {
+    if (seq < 1) return LRQK_EINVAL;
+    rc = check_peer_group(g);
+    if (rc != LRQK_OK) return rc;
+    if (g->heads_per_rank != L->bsz * L->q_heads || g->head_dim != L->head_dim || g->dtype != L->dtype) return LRQK_EINVAL;
+  } else if (!out) {
+    return LRQK_EINVAL;
+  }
+  return launch_flash_decode(L, q, out, rows, scale, workspace, as_stream(stream), g, seq, mask);
 }
 
 // ---------------------------------------------------------------------------------------------

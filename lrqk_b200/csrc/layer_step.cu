@@ -14,7 +14,7 @@ extern "C" int lrqk_layer_step(const lrqk_layer *L, const lrqk_step_args *a, lrq
   // The ring write is done by the projection kernel (its solver CTAs store the step's key/value, the
   // streaming CTAs take that row from k_new); a ring-write kernel only runs on the steps that flush
   // the ring to the host store.  The miss-list length is cleared by the projection's second kernel,
-  // the hit/miss difference runs as the tail of the scoring kernel: five launches per step.
+  // the hit/miss difference runs as the tail of the scoring kernel, the miss fetch inside the attention kernel.
   if (a->lite_slot < 0 || a->lite_slot >= L->m) return LRQK_ECAPACITY;
   if (a->flush_rows != 0 && a->flush_rows != L->m) return LRQK_EINVAL;
   // Where the scoring stage is one kernel, that kernel also applies the projection's update (early-exit
@@ -35,21 +35,14 @@ extern "C" int lrqk_layer_step(const lrqk_layer *L, const lrqk_step_args *a, lrq
   rc = score_topk_enqueue(L, a->q_hat, a->candidates, a->wanted, nullptr, 0, nullptr, as_stream(stream), &diff,
                           a->score_workspace, a->score_workspace_bytes, fold ? &deferred : nullptr);
   if (rc != LRQK_OK) return rc;
-  rc = lrqk_miss_gather(L, a->miss_list, a->counters, stream);
+  if (!a->peers && !a->attn_out)  // no attention asked for: only refill the missed slots
+    return lrqk_miss_gather(L, a->miss_list, a->counters, stream);
+  // the attention kernel fetches the missed rows itself
+  rc = lrqk_fetch_attend(L, a->mask, a->q, a->attn_out, a->scale, a->attn_workspace, a->peers, a->push_seq, stream);
   if (rc != LRQK_OK) return rc;
-  if (a->peers) {
-    rc = lrqk_flash_decode_push(L, a->q, a->attn_out, L->k + L->m, a->scale, a->attn_workspace, a->peers, a->push_seq,
-                                stream);
-    if (rc != LRQK_OK) return rc;
-    if (a->wait_status) {  // ... and the wait for every rank's rows of this push, in the same call
-      rc = lrqk_allgather_wait(a->peers, a->push_seq, a->gathered_out, a->wait_status, stream);
-      if (rc != LRQK_OK) return rc;
-    }
-  } else if (a->attn_out) {
-    rc = lrqk_flash_decode(L, a->q, a->attn_out, L->k + L->m, a->scale, a->attn_workspace, stream);
-    if (rc != LRQK_OK) return rc;
-  }
-  return LRQK_OK;
+  if (a->peers && a->wait_status)  // ... and the wait for every rank's rows of this push, in the same call
+    rc = lrqk_allgather_wait(a->peers, a->push_seq, a->gathered_out, a->wait_status, stream);
+  return rc;
 }
 
 // How many kernels lrqk_layer_step enqueues for these arguments (for launch accounting).
@@ -58,9 +51,8 @@ extern "C" int lrqk_layer_step_launches(const lrqk_layer *L, const lrqk_step_arg
   if (!L || !a) return LRQK_EINVAL;
   const bool fold = score_topk_can_fold_update(L, a->candidates, a->score_workspace, a->score_workspace_bytes);
   int n = 1 /* projection */ + (fold ? 0 : 1) /* update */ + 1 /* scoring + difference */ + (fold ? 0 : 1) /* key pass */ +
-          1 /* miss fetch */;
+          1 /* miss fetch, with the attention when the step ends in one */;
   if (a->flush_rows) n += 1;
-  if (a->peers) n += 1 + (a->wait_status ? 1 : 0);
-  else if (a->attn_out) n += 1;
+  if (a->peers && a->wait_status) n += 1;
   return n;
 }

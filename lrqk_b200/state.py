@@ -247,6 +247,17 @@ class LayerState:
                                               _ptr(self.attn_ws), _stream()), "lrqk_flash_decode")
         return self.attn_out
 
+    def fetch_attend(self, q, scale: Optional[float] = None, exchange=None):
+        """``miss_gather()`` followed by ``flash_decode(q)`` as ONE kernel: the threads that attend to a slot
+        whose mask byte is set read that row from the host store themselves (and refill the slot on the
+        side).  Same results bit for bit."""
+        self._chk(q, (self.bsz, self.q_heads, self.head_dim), "q")
+        scale = self.head_dim ** -0.5 if scale is None else scale
+        peers, seq = (None, 0) if exchange is None else (C.byref(exchange.c), exchange.seq.next_push())
+        _lib.check(self.lib.lrqk_fetch_attend(C.byref(self.c), _ptr(self.mask), _ptr(q), _ptr(self.attn_out), scale,
+                                              _ptr(self.attn_ws), peers, seq, _stream()), "lrqk_fetch_attend")
+        return self.attn_out
+
     def make_step_args(self, q, k_new, v_new, lite_slot: int, position: int, flush_rows: int, host_row: int,
                        candidates: int, max_iter: int, tol: float, scale: Optional[float] = None,
                        attention: bool = True) -> _lib.StepArgs:

@@ -354,6 +354,62 @@ def _check_project_update(dtype, r, k, m, bsz, hq, hkv, max_iter, d, lam):
         assert torch.equal(st.A_K[:, :, :append_row].cpu(), A[:, :, :append_row])
 
 
+@pytest.mark.parametrize("dtype,d,k,m,bsz,hq,hkv,miss", [
+    (torch.bfloat16, 128, 512, 64, 1, 8, 2, 0.9), (torch.bfloat16, 128, 2048, 64, 1, 4, 2, 0.1),
+    (torch.float32, 128, 300, 20, 2, 4, 4, 0.5), (torch.bfloat16, 64, 257, 8, 1, 6, 3, 1.0),
+    (torch.float32, 64, 64, 4, 1, 2, 1, 0.0),
+])
+def test_fetch_attend_equals_miss_gather_then_attention(dtype, d, k, m, bsz, hq, hkv, miss):
+    """One kernel that refills the missed slots from the host store while it attends to them, against the two
+    kernels it replaces in the fused step: resident rows and attention output identical bit for bit; a slot
+    whose table entry points outside the host store is left alone by both."""
+    ctx = 5000
+    g = torch.Generator().manual_seed(k + d)
+    st = _state(bsz=bsz, q_heads=hq, kv_heads=hkv, head_dim=d, r=16, k=k, m=m, a_capacity=ctx + 64,
+                host_capacity=ctx + 64, dtype=dtype)
+    st.host.data[:, :, :ctx].copy_(torch.randn(bsz, hkv, ctx, 2 * d, generator=g).to(dtype))
+    st.K_res.copy_(torch.randn(bsz, hq, k + m, d, generator=g).to(dtype))
+    st.V_res.copy_(torch.randn(bsz, hq, k + m, d, generator=g).to(dtype))
+    table = torch.stack([torch.randperm(ctx, generator=g)[:k] for _ in range(bsz * hq)]).view(bsz, hq, k).int()
+    mask = (torch.rand(bsz, hq, k, generator=g) < miss).to(torch.uint8)
+    if miss > 0:
+        table[0, 0, 3] = ctx + 64 + 7          # malformed: outside the store
+        table[0, 1, 5] = -2
+        mask[0, 0, 3] = mask[0, 1, 5] = 1
+    st.table.copy_(table)
+    st.mask.copy_(mask)
+    # the miss list the stand-alone fetch kernel takes: (head, slot, position) of every set mask byte
+    hh, ss = np.nonzero(mask.view(bsz * hq, k).numpy())
+    entries = np.stack([hh, ss, table.view(bsz * hq, k).numpy()[hh, ss]], axis=1).astype(np.int32)
+    st.miss_list[:len(entries)].copy_(torch.from_numpy(entries))
+    st.counters.zero_()
+    st.counters[0] = len(entries)
+    q = torch.randn(bsz, hq, d, generator=g).to(dtype).cuda()
+    K0, V0 = st.K_res.clone(), st.V_res.clone()
+    st.miss_gather()
+    out_a = st.flash_decode(q).clone()
+    Ka, Va = st.K_res.clone(), st.V_res.clone()
+    st.K_res.copy_(K0)
+    st.V_res.copy_(V0)
+    out_b = st.fetch_attend(q).clone()
+    torch.cuda.synchronize()
+    assert torch.equal(st.K_res, Ka) and torch.equal(st.V_res, Va)
+    assert torch.equal(out_a.view(torch.uint8), out_b.view(torch.uint8))
+    # and the refilled slots hold the host rows
+    grp = hq // hkv
+    ok = (table >= 0) & (table < ctx + 64) & (mask != 0)
+    for b in range(bsz):
+        for h in range(hq):
+            sel = ok[b, h].nonzero()[:, 0]
+            rows = st.host.data[b, h // grp][table[b, h][sel].long()]
+            assert torch.equal(st.K_res[b, h, sel.cuda()].cpu(), rows[:, :d])
+            assert torch.equal(st.V_res[b, h, sel.cuda()].cpu(), rows[:, d:])
+    untouched = ~ok
+    assert torch.equal(st.K_res[:, :, :k][untouched.cuda()], K0[:, :, :k][untouched.cuda()])
+    st.check_status()
+    st.close()
+
+
 # --------------------------------------------------------------------------------------------
 # whole decode steps against the oracle and against the reference's recorded trace
 # --------------------------------------------------------------------------------------------
