@@ -199,6 +199,9 @@ def stage_bytes(w, hq, hkv, cand, misses, e=2):
         "slot_diff": 3 * n * k * 4 + n * k,
         "miss_gather": misses * 2 * d * e,
         "flash_decode": n * (k + m) * 2 * d * e + 2 * n * d * e,
+        # the fused step's last kernel does both: the missed rows over the host link (its bound; the figure
+        # here), the rows that stayed resident out of HBM
+        "fetch_attend": misses * 2 * d * e,
     }
 
 
@@ -292,7 +295,11 @@ def run_ours(args):
     h2d = (dq.numel() + dk.numel() + dv.numel()) * dq.element_size()
     d2h = out_pin.numel() * out_pin.element_size()
     # ---- per-kernel timing: the same step issued stage by stage with events in between ----
-    names = ["lite_append", "project_update", "score_topk", "slot_diff", "miss_gather", "flash_decode"]
+    # (the last entry is the kernel the fused step runs instead of the two before it: it fetches the same rows
+    # again -- the mask still marks them -- and leaves the same state)
+    names = ["lite_append", "project_update", "score_topk", "slot_diff", "miss_gather", "flash_decode", "fetch_attend"]
+    floor_names = names[:6]            # the step's floor: each byte once
+    LINK_BOUND = ("miss_gather", "fetch_attend")
     evs, miss_total, cand_seen = [], 0, 0
     miss_acc = torch.zeros((), dtype=torch.int64, device=device)
     for _ in range(args.steps):
@@ -302,7 +309,7 @@ def run_ours(args):
             q, k, v = q_all[tcur, li], k_all[tcur, li], v_all[tcur, li]
             slot, position, flush_rows, host_row, cand = fac._step_counters()
             cand_seen = cand
-            marks = [torch.cuda.Event(enable_timing=True) for _ in range(7)]
+            marks = [torch.cuda.Event(enable_timing=True) for _ in range(8)]
             torch.cuda._sleep(400_000)   # ~0.2 ms of GPU idle spin: the host queues the six launches behind it,
             marks[0].record()            # so the event deltas are device time, not host launch time
             st.lite_append(k, v, slot, position, flush_rows, host_row); marks[1].record()
@@ -311,6 +318,7 @@ def run_ours(args):
             st.slot_diff(); marks[4].record()
             st.miss_gather(); marks[5].record()
             st.flash_decode(q); marks[6].record()
+            st.fetch_attend(q); marks[7].record()
             miss_acc += st.miss_count.sum()
             evs.append(marks)
         tcur += 1
@@ -323,7 +331,7 @@ def run_ours(args):
     # queries (rho = 0) miss nearly every selected row; a model's consecutive queries are correlated ----
     def floor_us(misses):
         b = stage_bytes(w, hq_l, hkv_l, cand_seen, misses, e=2 if dtype == torch.bfloat16 else 4)
-        return sum(b[n] / ((link_peak if n == "miss_gather" else hbm_peak) * 1e9) for n in names) * 1e6
+        return sum(b[n] / ((link_peak if n in LINK_BOUND else hbm_peak) * 1e9) for n in floor_names) * 1e6
 
     hbm_peak, peak_kind = measured_hbm_peak()
     link_peak = host_link_peak_gbs(device)
@@ -403,27 +411,29 @@ def run_ours(args):
     per_kernel = {}
     for n in names:
         gbs = bytes_[n] / (stage_us[n] * 1e-6) / 1e9 if stage_us[n] > 0 else 0.0
-        bound = "host_link" if n == "miss_gather" else "hbm"
-        peak = link_peak if n == "miss_gather" else hbm_peak
+        bound = "host_link" if n in LINK_BOUND else "hbm"
+        peak = link_peak if n in LINK_BOUND else hbm_peak
         per_kernel[n] = {"us": round(stage_us[n], 2), "bytes": int(bytes_[n]), "bound": bound,
                          "achieved": round(gbs, 1), "peak": round(peak, 1), "unit": "GB/s", "frac": round(gbs / peak, 4),
                          # DRAM traffic of one launch (ncu) where a capture exists; the miss fetch moves its bytes over
                          # the host link, not out of DRAM, so it has none
                          "traffic": (round(bytes_[n] * NCU_TRAFFIC_RATIO[n]) if n in NCU_TRAFFIC_RATIO else None)}
-        if n == "miss_gather":
+        if n in LINK_BOUND:
             per_kernel[n]["host_link_bytes"] = int(bytes_[n])
+        if n == "fetch_attend":
+            per_kernel[n]["hbm_bytes"] = int(bytes_["flash_decode"])  # resident rows read + refilled rows written
     dominant = max(names, key=lambda n: stage_us[n])
     roof = dict(per_kernel[dominant])
     roof.update({"kernel": dominant,
                  "peak_source": ("MEASURED_PEAKS.json hbm_gbs" if peak_kind == "measured" else "fallback 6650 GB/s")
-                 if dominant != "miss_gather" else "pinned host->device cudaMemcpy measured in this run"})
-    hbm_kernel = max((n for n in names if n != "miss_gather"), key=lambda n: stage_us[n])
+                 if dominant not in LINK_BOUND else "pinned host->device cudaMemcpy measured in this run"})
+    hbm_kernel = max((n for n in names if n not in LINK_BOUND), key=lambda n: stage_us[n])
     roof_hbm = dict(per_kernel[hbm_kernel]); roof_hbm["kernel"] = hbm_kernel
     roof_hbm["peak_source"] = "MEASURED_PEAKS.json hbm_gbs" if peak_kind == "measured" else "fallback 6650 GB/s"
 
     # the stages of a step depend on one another, so the step's roofline is the SUM of the stages'
     # algorithmic bytes over their peaks (HBM for all but the miss fetch, the host link for that)
-    step_floor_us = sum(bytes_[n] / ((link_peak if n == "miss_gather" else hbm_peak) * 1e9) for n in names) * 1e6
+    step_floor_us = sum(bytes_[n] / ((link_peak if n in LINK_BOUND else hbm_peak) * 1e9) for n in floor_names) * 1e6
     roof_step = {"us_at_roofline": round(step_floor_us, 1), "us_measured": round(us_per_layer, 2),
                  "frac": round(step_floor_us / us_per_layer, 4), "miss_rate": round(miss_rate, 4),
                  "note": "sum over the six stages of algorithmic bytes / measured peak"}

@@ -314,8 +314,9 @@ typedef struct lrqk_step_args {
 } lrqk_step_args;
 
 int lrqk_layer_step(const lrqk_layer *L, const lrqk_step_args *a, lrqk_stream_t stream);
-/* Number of kernels that call enqueues for these arguments (4 to 8: projection, [update], [key pass], scoring +
- * difference, miss fetch, [ring flush], [attention], [exchange wait]); negative LRQK_E* on bad arguments. */
+/* Number of kernels that call enqueues for these arguments (3 to 7: projection, [update], [key pass], scoring +
+ * difference, miss fetch -- inside the attention kernel when the step ends in attention --, [ring flush],
+ * [exchange wait]); negative LRQK_E* on bad arguments. */
 int lrqk_layer_step_launches(const lrqk_layer *L, const lrqk_step_args *a);
 
 /* ------------------------------------------------------------------------------------
