@@ -146,20 +146,37 @@ def measured_hbm_peak():
         return FALLBACK_HBM_GBS, "fallback"
 
 
-def host_link_peak_gbs(device) -> float:
-    """Pinned host -> device copy bandwidth, best of 5, 256 MiB."""
+def host_link_peak_gbs(device, world: int = 1, rank: int = 0, sync=None):
+    """Pinned host -> device copy bandwidth (256 MiB, best of 5) of this rank: with every rank copying at the
+    same moment -- the condition of the timed loop, where the exchange keeps the ranks in step and they all
+    fetch at once; this is the roofline's peak -- and with the ranks taking turns.  Returns (together, alone)."""
     n = 256 << 20
     h = torch.empty(n, dtype=torch.uint8, pin_memory=True)
     dv = torch.empty(n, dtype=torch.uint8, device=device)
-    best = 0.0
-    for _ in range(6):
+
+    def once():
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         dv.copy_(h, non_blocking=True)
         e1.record()
         e1.synchronize()
-        best = max(best, n / (e0.elapsed_time(e1) * 1e-3) / 1e9)
-    return best
+        return n / (e0.elapsed_time(e1) * 1e-3) / 1e9
+
+    once()
+    together = 0.0
+    for _ in range(5):
+        if sync is not None:
+            sync()
+        together = max(together, once())
+    alone = together
+    if world > 1 and sync is not None:
+        alone = 0.0
+        for r in range(world):
+            sync()
+            if r == rank:
+                alone = max(once() for _ in range(3))
+        sync()
+    return together, alone
 
 
 def build_layers(w, layers, hq_local, hkv_local, head_offset, device, dtype, seed, n_tokens):
@@ -334,7 +351,7 @@ def run_ours(args):
         return sum(b[n] / ((link_peak if n in LINK_BOUND else hbm_peak) * 1e9) for n in floor_names) * 1e6
 
     hbm_peak, peak_kind = measured_hbm_peak()
-    link_peak = host_link_peak_gbs(device)
+    link_peak, link_peak_alone = host_link_peak_gbs(device, world, rank, barrier)
     by_rho = {}
     for rho in sweep_rhos:
         n_sw = sweep_warm + args.steps + sweep_probe
@@ -440,7 +457,8 @@ def run_ours(args):
     by_rho[str(args.rho)] = {k2: roof_step[k2] for k2 in ("us_measured", "us_at_roofline", "frac", "miss_rate")}
     # every rank's own figures (the value above is the slowest rank's): unequal host links show up here
     mine = {"rank": rank, "us_per_layer_step": round(ms_dev_own * 1e3 / (args.steps * layers), 2),
-            "host_link_peak_gbs": round(link_peak, 1), "host_issue_us_per_layer_step": round(host_issue_us, 1),
+            "host_link_peak_gbs": round(link_peak, 1), "host_link_peak_alone_gbs": round(link_peak_alone, 1),
+            "host_issue_us_per_layer_step": round(host_issue_us, 1),
             "stage_us": {n: round(stage_us[n], 2) for n in names}}
     per_rank = [mine]
     if world > 1:
