@@ -358,12 +358,14 @@ def _check_project_update(dtype, r, k, m, bsz, hq, hkv, max_iter, d, lam):
     (torch.bfloat16, 128, 512, 64, 1, 8, 2, 0.9), (torch.bfloat16, 128, 2048, 64, 1, 4, 2, 0.1),
     (torch.float32, 128, 300, 20, 2, 4, 4, 0.5), (torch.bfloat16, 64, 257, 8, 1, 6, 3, 1.0),
     (torch.float32, 64, 64, 4, 1, 2, 1, 0.0),
+    (torch.bfloat16, 128, 9000, 16, 1, 2, 1, 0.6),   # more rows than 64 splits of one staging round: two rounds per CTA
+    (torch.float32, 128, 4990, 10, 1, 1, 1, 0.3),
 ])
 def test_fetch_attend_equals_miss_gather_then_attention(dtype, d, k, m, bsz, hq, hkv, miss):
     """One kernel that refills the missed slots from the host store while it attends to them, against the two
     kernels it replaces in the fused step: resident rows and attention output identical bit for bit; a slot
     whose table entry points outside the host store is left alone by both."""
-    ctx = 5000
+    ctx = max(5000, 2 * k)
     g = torch.Generator().manual_seed(k + d)
     st = _state(bsz=bsz, q_heads=hq, kv_heads=hkv, head_dim=d, r=16, k=k, m=m, a_capacity=ctx + 64,
                 host_capacity=ctx + 64, dtype=dtype)
@@ -374,8 +376,8 @@ def test_fetch_attend_equals_miss_gather_then_attention(dtype, d, k, m, bsz, hq,
     mask = (torch.rand(bsz, hq, k, generator=g) < miss).to(torch.uint8)
     if miss > 0:
         table[0, 0, 3] = ctx + 64 + 7          # malformed: outside the store
-        table[0, 1, 5] = -2
-        mask[0, 0, 3] = mask[0, 1, 5] = 1
+        table[0, hq - 1, 5] = -2
+        mask[0, 0, 3] = mask[0, hq - 1, 5] = 1
     st.table.copy_(table)
     st.mask.copy_(mask)
     # the miss list the stand-alone fetch kernel takes: (head, slot, position) of every set mask byte
