@@ -512,6 +512,10 @@ __global__ void __launch_bounds__(kThreads, 1) score_topk_kernel(ScoreTopkParams
     }
   }
   const uint32_t T_key = prefix;  // the k-th largest key
+  // the CTA that will run the hit/miss difference asks for its slot-table entries now: they do not depend on
+  // the selection, and the load has returned by the time the compaction and the cluster barrier are through
+  DiffPre tab_pre = DiffPre{0, 0, 0, 0, false};
+  if (p.table != nullptr && rank == 0 && p.k <= kDiffPre * kDThreads) tab_pre = slot_diff_preload(n, p.table, p.k);
 
   // ---- ordered compaction: every thread owns 4*V consecutive rows -----------------------------
   // The undecided keys (a handful per cluster by now) are settled against the threshold; the
@@ -557,7 +561,7 @@ __global__ void __launch_bounds__(kThreads, 1) score_topk_kernel(ScoreTopkParams
     cluster.sync();
     if (rank == 0)
       slot_diff_head(n, p.table, p.wanted, p.mask, p.miss_count, p.miss_list, p.list_len, p.diff_status, p.k,
-                     reinterpret_cast<unsigned char *>(smem));
+                     reinterpret_cast<unsigned char *>(smem), tab_pre);
   }
   if (p.fold_update && rank == csize - 1) {
     // the head's update of B_Q, B_K, q_hat and the new A_K row: by the cluster's last CTA, which is idle
