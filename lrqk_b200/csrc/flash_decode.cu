@@ -142,7 +142,11 @@ __global__ void __launch_bounds__(kAThreads, 4) flash_decode_kernel(AttnParams p
         const int slot = base + j;
         if (j < nrows) {
           int64_t pos = -1;
-          if (slot < p.k && mk[slot] != 0) pos = tb[slot];
+          if (slot < p.k) {  // mask byte and table entry are asked for together, not one after the other
+            const uint8_t refill = mk[slot];
+            const int32_t at = tb[slot];
+            if (refill != 0) pos = at;
+          }
           if (pos >= 0 && pos < p.host_capacity) {  // (a malformed entry is skipped, never dereferenced)
             const char *src = hrow + pos * (2 * ROW_BYTES);
             cp_async16(smem_addr(sK + (size_t)j * D + lir * EPV), src);
