@@ -797,7 +797,7 @@ __global__ void __launch_bounds__(kPThreads, 2) project_kernel(ProjectParams p) 
       partw[gw * R + cw] = wacc;
       if (nstages > 0 && !mbar_wait_bounded(acc_bar, 0u)) timed_out = true;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      timed_out = __syncthreads_or(timed_out ? 1 : 0) != 0;  // one verdict for the CTA: the loads below are warp-wide
+      timed_out = __syncthreads_or(timed_out ? 1 : 0) != 0;  // one decision for the CTA: the loads below are warp-wide
       if (nstages > 0 && !timed_out) {
         gram_from_tmem<R>(tmem_base, 0, slot_dst, R);
       } else {
