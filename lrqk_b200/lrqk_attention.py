@@ -316,6 +316,7 @@ class LightAttentionIndicesFactory:
 
     @property
     def KVcpu(self):
+        self._await_host_store(on_host=True)
         return _HostKVView(self.state.host)
 
     @property
@@ -432,7 +433,22 @@ class LightAttentionIndicesFactory:
         st.fill_resident(k, v)
         self.lite_indices = list(range(seq_len - self.num_lite_tokens, seq_len))
         self.lite_len = 0
-        main.wait_stream(side)                                         # the host store is complete from here on
+        # The copy to the host store may still be running when this returns: nothing on the main stream reads the
+        # store before the layer's first decode step, which waits for this event (as does any host-side look at
+        # KVcpu), so the copy also overlaps whatever the caller enqueues next -- the next layer's prompt pass.
+        self._host_ready = torch.cuda.Event()
+        self._host_ready.record(side)
+
+    def _await_host_store(self, on_host: bool):
+        """Order what follows after the prompt's copy into the host store: the current stream waits
+        (``on_host=False``), or the calling thread does."""
+        ev = getattr(self, "_host_ready", None)
+        if ev is not None:
+            if on_host:
+                ev.synchronize()
+            else:
+                torch.cuda.current_stream().wait_event(ev)
+            self._host_ready = None
 
     def _factorize(self, st: LayerState, q, k, seq_len: int) -> torch.Tensor:
         """Prompt factorisation into st.A_K[:seq_len], st.B_Q, st.B_K; returns the last row of A_Q."""
@@ -556,6 +572,7 @@ class LightAttentionIndicesFactory:
 
     def _decode_on_device(self, query_states, key_states, value_states, attention: bool, exchange=None):
         st = self.state
+        self._await_host_store(on_host=False)
         self._reserve()
         q = self._flat(query_states.to(st.dtype), st.q_heads)
         k = self._flat(key_states.to(st.dtype), st.kv_heads)
@@ -637,6 +654,7 @@ class LightAttentionIndicesFactory:
 
     def close(self):
         if self.state is not None:
+            self._await_host_store(on_host=True)
             self.state.close()
             self.state = None
 
