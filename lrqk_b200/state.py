@@ -25,7 +25,15 @@ def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else C.c_void_p(t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream():
+    """The current CUDA stream of the current device as a cudaStream_t.  (torch.cuda.current_stream() costs
+    ~15 us of Python per call -- a third of a decode step's host time; the raw accessor, where this torch has
+    it, a fraction of a microsecond.)"""
+    if _raw_stream is not None:
+        return C.c_void_p(_raw_stream(torch.cuda.current_device()))
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
