@@ -20,6 +20,7 @@ set-up / baseline traffic, not part of the per-step selection path.
 from __future__ import annotations
 
 import json
+import os
 from typing import Callable, Dict, Optional
 
 import torch
@@ -309,9 +310,14 @@ def tps_estimate(model, past_key_values_factory: Optional[Callable] = None, prom
 
 def run_task(name: str, model, *, r: int = 16, num_active_tokens: int = 1024, lite_tokens: int = 16, prompt_lens=(4096,),
              max_new_tokens: int = 32, out_path: Optional[str] = None) -> dict:
-    """One row of the reference's throughput table (tps_estimate.py:126-142): ``name`` in ``task_dict``."""
+    """One row of the reference's throughput table (tps_estimate.py:126-142): ``name`` in ``task_dict``.
+    Like the reference's driver (:127-130), a row whose ``out_path`` already exists is not measured again: the
+    file's records are returned."""
     if name not in task_dict:
         raise ValueError(f"Unknown task {name}")
+    if out_path and os.path.exists(out_path):
+        with open(out_path) as f:
+            return json.load(f)
     groups = model.config.num_attention_heads // model.config.num_key_value_heads
     if name == "cpu_offload":
         factory = FullOffloadCache

@@ -514,6 +514,62 @@ class LightAttentionIndicesFactory:
         self.lite_indices = list(range(seq_len - self.num_lite_tokens, seq_len))
         self.lite_len = 0
 
+    # ---- save / resume ----------------------------------------------------------------------------
+    # (The reference keeps no cache state across runs; this is the dump a serving host needs to park a long
+    # context and pick it up again.)
+    def state_dict(self) -> dict:
+        """Everything ``load_state_dict`` needs to go on decoding bit for bit: the rank-r key factors of all
+        tokens so far, the right factors, the resident rows, slot table and ring positions, the filled rows of
+        the host store, and the host-side counters.  Tensors are CPU copies (this call synchronises)."""
+        st = self.state
+        if st is None:
+            raise RuntimeError("nothing to save before prefill")
+        self._await_host_store(on_host=True)
+        with on_device(st.device):
+            torch.cuda.synchronize()
+        rows = st.host.current_len
+        return {
+            "format": 1,
+            "shape": dict(bsz=st.bsz, q_heads=st.q_heads, kv_heads=st.kv_heads, head_dim=st.head_dim, r=st.r,
+                          k=st.k, m=st.m, a_capacity=st.A_K.shape[2], host_capacity=st.host.capacity,
+                          dtype=str(st.dtype).replace("torch.", ""), weights=list(st.weights)),
+            "counters": dict(current_len=self.current_len, prefill_length=self.prefill_length, lite_len=self.lite_len,
+                             lite_indices=list(self.lite_indices), resident_rows=self.resident_rows, host_len=rows),
+            "A_K": st.A_K[:, :, :self.current_len].cpu(), "B_Q": st.B_Q.cpu(), "B_K": st.B_K.cpu(),
+            "K_res": st.K_res.cpu(), "V_res": st.V_res.cpu(), "table": st.table.cpu(), "lite_pos": st.lite_pos.cpu(),
+            "host": st.host.data[:, :, :rows].clone(),
+        }
+
+    def load_state_dict(self, sd: dict, device=None) -> None:
+        """Rebuild the layer from ``state_dict()`` output on ``device`` (default: this factory's, else the
+        current CUDA device).  The factory must have been built with the same ``attn_topk``, ``num_lite_tokens``,
+        ``r`` and ``num_key_value_groups``."""
+        if sd.get("format") != 1:
+            raise ValueError("not a state this version wrote")
+        sh, c = sd["shape"], sd["counters"]
+        if (sh["k"], sh["m"], sh["r"]) != (self.attn_topk, self.num_lite_tokens, self.r) or \
+                sh["q_heads"] != sh["kv_heads"] * self.num_key_value_groups:
+            raise ValueError("the saved state was produced with other settings (attn_topk, num_lite_tokens, r, groups)")
+        if tuple(float(w) for w in sh["weights"]) != tuple(self.weights):
+            raise ValueError("the saved state was produced with other weights")
+        dtype = getattr(torch, sh["dtype"])
+        device = torch.device(device if device is not None else (self.device if self.device is not None else "cuda"))
+        if self.state is not None:
+            self.close()
+        with on_device(device if device.index is not None else torch.device("cuda", torch.cuda.current_device())):
+            st = self.state = LayerState(sh["bsz"], sh["q_heads"], sh["kv_heads"], sh["head_dim"], sh["r"], sh["k"], sh["m"],
+                                         a_capacity=sh["a_capacity"], host_capacity=sh["host_capacity"], dtype=dtype,
+                                         device=device, max_iter=self.max_iter[1], zero_host=True, weights=self.weights)
+            st.A_K[:, :, :c["current_len"]].copy_(sd["A_K"])
+            for name in ("B_Q", "B_K", "K_res", "V_res", "table", "lite_pos"):
+                getattr(st, name).copy_(sd[name])
+            st.host.data[:, :, :c["host_len"]].copy_(sd["host"])
+            st.host.current_len = c["host_len"]
+            torch.cuda.synchronize()
+        self.current_len, self.prefill_length = c["current_len"], c["prefill_length"]
+        self.lite_len, self.lite_indices = c["lite_len"], list(c["lite_indices"])
+        self.resident_rows = c["resident_rows"]
+
     # ---- decode ---------------------------------------------------------------------------------
     def _reserve(self):
         st = self.state
@@ -807,6 +863,45 @@ class DynamicLRQKCache(_CacheBase):
         exchange = self.sharding.exchange(q.shape[0] * q.shape[1], q.shape[-1], fac.state.dtype)
         fac.decode_attend_push(q, k, v, exchange)
         return self.sharding.gather_step(bsz, kv_heads, q_heads).unsqueeze(2)
+
+    def state_dict(self) -> dict:
+        """The whole cache for ``load_state_dict``: every decoding layer's ``state_dict()`` and the prompt rows of
+        layers that are still collecting a short prompt."""
+        layers = {}
+        for idx, state in self.sequence_state.items():
+            if state == DynamicLRQKCache.State.decoding:
+                layers[idx] = {"state": "decoding", "layer": self.lwattn[idx].state_dict()}
+            elif state == DynamicLRQKCache.State.collecting:
+                buf = self.temp_buff_cache_qkv[idx]
+                layers[idx] = {"state": "collecting", "Q": buf.Q.tensor().cpu(), "K": buf.K.tensor().cpu(), "V": buf.V.tensor().cpu()}
+        return {"format": 1, "layers": layers,
+                "settings": dict(r=self.r, num_active_tokens=self.num_active_tokens, lite_tokens=self.lite_tokens,
+                                 num_key_value_groups=self.num_key_value_groups)}
+
+    def load_state_dict(self, sd: dict, device=None) -> None:
+        """Restore what ``state_dict()`` wrote into this (fresh, identically configured) cache."""
+        if sd.get("format") != 1:
+            raise ValueError("not a state this version wrote")
+        mine = dict(r=self.r, num_active_tokens=self.num_active_tokens, lite_tokens=self.lite_tokens,
+                    num_key_value_groups=self.num_key_value_groups)
+        if sd["settings"] != mine:
+            raise ValueError(f"the saved cache was configured as {sd['settings']}, this one as {mine}")
+        for idx, entry in sd["layers"].items():
+            idx = int(idx)
+            if entry["state"] == "decoding":
+                self.lwattn[idx].load_state_dict(entry["layer"], device=device)
+                self.sequence_state[idx] = DynamicLRQKCache.State.decoding
+            else:
+                dev = torch.device(device if device is not None else "cuda")
+                self.temp_buff_cache_qkv[idx].append(entry["Q"].to(dev), entry["K"].to(dev), entry["V"].to(dev))
+                self.sequence_state[idx] = DynamicLRQKCache.State.collecting
+
+    def save(self, path: str) -> None:
+        """``torch.save`` of ``state_dict()``."""
+        torch.save(self.state_dict(), path)
+
+    def load(self, path: str, device=None) -> None:
+        self.load_state_dict(torch.load(path, map_location="cpu", weights_only=False), device=device)
 
     def check_status(self) -> None:
         """Synchronising check of every layer's device-side status words (the hit/miss difference's mismatch flag,
