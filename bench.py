@@ -212,7 +212,8 @@ def stage_bytes(w, hq, hkv, cand, misses, e=2):
     k, m, r, d = w["k"], w["m"], w["r"], w["d"]
     return {
         "lite_append": n * 2 * d * e + w["bsz"] * hkv * 2 * d * e,
-        "project_update": n * (k + m) * (d + r) * e + 4 * n * r * d * e,
+        "project": n * (k + m) * (d + r) * e + 2 * n * r * d * e,
+        "update": 2 * n * r * d * e,          # the right factors written back (its reads of them are re-reads)
         "score_topk": n * cand * r * e + n * k * 4,
         "slot_diff": 3 * n * k * 4 + n * k,
         "miss_gather": misses * 2 * d * e,
@@ -317,8 +318,8 @@ def run_ours(args):
     # ---- per-kernel timing: the same step issued stage by stage with events in between ----
     # (the last entry is the kernel the fused step runs instead of the two before it: it fetches the same rows
     # again -- the mask still marks them -- and leaves the same state)
-    names = ["lite_append", "project_update", "score_topk", "slot_diff", "miss_gather", "flash_decode", "fetch_attend"]
-    floor_names = names[:6]            # the step's floor: each byte once
+    names = ["lite_append", "project", "update", "score_topk", "slot_diff", "miss_gather", "flash_decode", "fetch_attend"]
+    floor_names = names[:7]            # the step's floor: each byte once
     LINK_BOUND = ("miss_gather", "fetch_attend")
     evs, miss_total, cand_seen = [], 0, 0
     miss_acc = torch.zeros((), dtype=torch.int64, device=device)
@@ -329,16 +330,17 @@ def run_ours(args):
             q, k, v = q_all[tcur, li], k_all[tcur, li], v_all[tcur, li]
             slot, position, flush_rows, host_row, cand = fac._step_counters()
             cand_seen = cand
-            marks = [torch.cuda.Event(enable_timing=True) for _ in range(8)]
+            marks = [torch.cuda.Event(enable_timing=True) for _ in range(9)]
             torch.cuda._sleep(400_000)   # ~0.2 ms of GPU idle spin: the host queues the six launches behind it,
             marks[0].record()            # so the event deltas are device time, not host launch time
             st.lite_append(k, v, slot, position, flush_rows, host_row); marks[1].record()
-            st.project_update(q, k, w["max_iter"][1], w["tol"], position); marks[2].record()
-            st.score_topk(st.q_hat, cand); marks[3].record()
-            st.slot_diff(); marks[4].record()
-            st.miss_gather(); marks[5].record()
-            st.flash_decode(q); marks[6].record()
-            st.fetch_attend(q); marks[7].record()
+            st.project(q, k, w["max_iter"][1], position); marks[2].record()     # the fused step's first kernel
+            st.update(q, k, w["max_iter"][1], w["tol"], position); marks[3].record()   # (inside its scoring kernel)
+            st.score_topk(st.q_hat, cand); marks[4].record()
+            st.slot_diff(); marks[5].record()
+            st.miss_gather(); marks[6].record()
+            st.flash_decode(q); marks[7].record()
+            st.fetch_attend(q); marks[8].record()
             miss_acc += st.miss_count.sum()
             evs.append(marks)
         tcur += 1

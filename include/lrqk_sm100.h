@@ -128,6 +128,16 @@ int lrqk_lite_append(const lrqk_layer *L, const void *k_new, const void *v_new, 
  * 16 bytes of the workspace); zero-fill the workspace before its first use.
  * ---------------------------------------------------------------------------------- */
 size_t lrqk_decode_project_update_workspace_bytes(const lrqk_layer *L, int32_t max_iter);
+/* The two halves of lrqk_decode_project_update as separate calls, for callers that want to place (or time) them
+ * separately -- lrqk_layer_step runs the first as its own kernel and the second inside the scoring kernel.
+ * lrqk_decode_project: the alternating solves (:555-609); leaves every alternation's (q_hat, k_hat, squared
+ * change) in `workspace` and touches nothing else.  lrqk_decode_update: the early-exit decision over all heads
+ * (:603-609) from those, then B_Q, B_K (:612-626), q_hat and the new row of A_K.  Same workspace, same max_iter. */
+int lrqk_decode_project(const lrqk_layer *L, const void *q, const void *k_new, int32_t max_iter,
+                        int64_t append_row, void *q_hat, void *workspace, lrqk_stream_t stream);
+int lrqk_decode_update(const lrqk_layer *L, const void *q, const void *k_new, int32_t max_iter, float tol,
+                       int64_t append_row, void *q_hat, int32_t *iters_out, void *workspace,
+                       lrqk_stream_t stream);
 int32_t *lrqk_decode_project_update_status_word(const lrqk_layer *L, int32_t max_iter, void *workspace);
 int lrqk_decode_project_update(const lrqk_layer *L, const void *q, const void *k_new, int32_t max_iter,
                                float tol, int64_t append_row, void *q_hat, int32_t *iters_out,

@@ -80,6 +80,10 @@ _SIGNATURES = {
     "lrqk_decode_project_update_workspace_bytes": (C.c_size_t, [C.POINTER(Layer), C.c_int32]),
     "lrqk_decode_project_update": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_void_p, C.c_int32, C.c_float,
                                              C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "lrqk_decode_project": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_void_p,
+                                      C.c_void_p, C.c_void_p]),
+    "lrqk_decode_update": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_void_p, C.c_int32, C.c_float,
+                                     C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "lrqk_score_topk_workspace_bytes": (C.c_size_t, [C.POINTER(Layer), C.c_int64]),
     "lrqk_score_topk": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64,
                                   C.c_void_p, C.c_size_t, C.c_void_p]),

@@ -201,7 +201,8 @@ int plan_score_topk(const lrqk_layer *L, int64_t candidates, int n_heads, int *c
 // rank-1 step on B_Q / B_K, q_hat, the new A_K row) are handed back for the scoring kernel to apply.
 int project_update_enqueue(const lrqk_layer *L, const void *q, const void *k_new, int32_t max_iter, float tol,
                            int64_t append_row, void *q_hat, int32_t *iters_out, void *workspace, int32_t *clear_word,
-                           cudaStream_t stream, const void *v_new, int32_t lite_slot, UpdateArgs *deferred = nullptr);
+                           cudaStream_t stream, const void *v_new, int32_t lite_slot, UpdateArgs *deferred = nullptr,
+                           bool update_only = false);
 // The flush half of lrqk_lite_append alone: the ring of every KV head to host rows [host_row, host_row + m).
 int lite_flush_enqueue(const lrqk_layer *L, int64_t host_row, cudaStream_t stream);
 

@@ -937,7 +937,8 @@ int plan_cluster(int n_heads, int n_act) {
 }
 
 template <typename T, int R, int D>
-int launch(const lrqk_layer *L, ProjectParams pp, const UpdateParams &up, cudaStream_t stream, bool with_update) {
+int launch(const lrqk_layer *L, ProjectParams pp, const UpdateParams &up, cudaStream_t stream, bool with_update,
+           bool with_project) {
   const int n_heads = L->bsz * L->q_heads;
   const int n_act = L->k + L->m;
   const int csize = plan_cluster<T, R, D>(n_heads, n_act);
@@ -945,10 +946,12 @@ int launch(const lrqk_layer *L, ProjectParams pp, const UpdateParams &up, cudaSt
   const int share = (n_act + n_streamers - 1) / n_streamers;
   const size_t smem = project_smem_bytes<T, R, D>(csize, share);
   if (smem > 227 * 1024) return LRQK_EUNSUPPORTED;
-  auto kern = project_kernel<T, R, D>;
-  static SmemOptIn opt_in;
-  LRQK_CUDA_TRY(opt_in.ensure(kern, smem));
-  LRQK_CUDA_TRY(launch_dependent(kern, dim3(csize, n_heads, 1), dim3(kPThreads), smem, stream, csize, pp));
+  if (with_project) {
+    auto kern = project_kernel<T, R, D>;
+    static SmemOptIn opt_in;
+    LRQK_CUDA_TRY(opt_in.ensure(kern, smem));
+    LRQK_CUDA_TRY(launch_dependent(kern, dim3(csize, n_heads, 1), dim3(kPThreads), smem, stream, csize, pp));
+  }
   if (with_update) {
     constexpr size_t usmem = sizeof(float) * (size_t)update_head_smem_floats(R, D);
     static SmemOptIn opt_in_u;
@@ -960,12 +963,13 @@ int launch(const lrqk_layer *L, ProjectParams pp, const UpdateParams &up, cudaSt
 }
 
 template <typename T, int D>
-int dispatch_r(const lrqk_layer *L, const ProjectParams &pp, const UpdateParams &up, cudaStream_t stream, bool with_update) {
+int dispatch_r(const lrqk_layer *L, const ProjectParams &pp, const UpdateParams &up, cudaStream_t stream, bool with_update,
+               bool with_project) {
   switch (L->r) {
-    case 8: return launch<T, 8, D>(L, pp, up, stream, with_update);
-    case 16: return launch<T, 16, D>(L, pp, up, stream, with_update);
-    case 32: return launch<T, 32, D>(L, pp, up, stream, with_update);
-    case 64: return launch<T, 64, D>(L, pp, up, stream, with_update);
+    case 8: return launch<T, 8, D>(L, pp, up, stream, with_update, with_project);
+    case 16: return launch<T, 16, D>(L, pp, up, stream, with_update, with_project);
+    case 32: return launch<T, 32, D>(L, pp, up, stream, with_update, with_project);
+    case 64: return launch<T, 64, D>(L, pp, up, stream, with_update, with_project);
     default: return LRQK_EUNSUPPORTED;
   }
 }
@@ -989,6 +993,22 @@ extern "C" int32_t *lrqk_decode_project_update_status_word(const lrqk_layer *L, 
   return reinterpret_cast<int32_t *>(reinterpret_cast<char *>(workspace) + project_iterates_bytes(L, max_iter < 1 ? 1 : max_iter));
 }
 
+// The two halves as separate calls.  (The fused step runs the first as its own kernel and applies the second
+// inside the scoring kernel.)
+extern "C" int lrqk_decode_project(const lrqk_layer *L, const void *q, const void *k_new, int32_t max_iter,
+                                   int64_t append_row, void *q_hat, void *workspace, lrqk_stream_t stream) {
+  lrqk::UpdateArgs unused;
+  return lrqk::project_update_enqueue(L, q, k_new, max_iter, 0.0f, append_row, q_hat, nullptr, workspace, nullptr,
+                                      lrqk::as_stream(stream), nullptr, -1, &unused);
+}
+
+extern "C" int lrqk_decode_update(const lrqk_layer *L, const void *q, const void *k_new, int32_t max_iter, float tol,
+                                  int64_t append_row, void *q_hat, int32_t *iters_out, void *workspace,
+                                  lrqk_stream_t stream) {
+  return lrqk::project_update_enqueue(L, q, k_new, max_iter, tol, append_row, q_hat, iters_out, workspace, nullptr,
+                                      lrqk::as_stream(stream), nullptr, -1, nullptr, true);
+}
+
 extern "C" int lrqk_decode_project_update(const lrqk_layer *L, const void *q, const void *k_new, int32_t max_iter,
                                           float tol, int64_t append_row, void *q_hat, int32_t *iters_out,
                                           void *workspace, lrqk_stream_t stream) {
@@ -999,7 +1019,7 @@ extern "C" int lrqk_decode_project_update(const lrqk_layer *L, const void *q, co
 int lrqk::project_update_enqueue(const lrqk_layer *L, const void *q, const void *k_new, int32_t max_iter, float tol,
                                  int64_t append_row, void *q_hat, int32_t *iters_out, void *workspace,
                                  int32_t *clear_word, cudaStream_t s, const void *v_new, int32_t lite_slot,
-                                 UpdateArgs *deferred) {
+                                 UpdateArgs *deferred, bool update_only) {
   int rc = check_device();
   if (rc != LRQK_OK) return rc;
   rc = check_layer(L);
@@ -1039,9 +1059,9 @@ int lrqk::project_update_enqueue(const lrqk_layer *L, const void *q, const void 
     pp.clear_word = clear_word;
   }
   if (L->head_dim == 128) {
-    LRQK_DISPATCH_DTYPE(L->dtype, T, return (dispatch_r<T, 128>(L, pp, up, s, with_update)));
+    LRQK_DISPATCH_DTYPE(L->dtype, T, return (dispatch_r<T, 128>(L, pp, up, s, with_update, !update_only)));
   } else if (L->head_dim == 64) {
-    LRQK_DISPATCH_DTYPE(L->dtype, T, return (dispatch_r<T, 64>(L, pp, up, s, with_update)));
+    LRQK_DISPATCH_DTYPE(L->dtype, T, return (dispatch_r<T, 64>(L, pp, up, s, with_update, !update_only)));
   }
   return LRQK_EUNSUPPORTED;
 }

@@ -61,6 +61,13 @@ __device__ __forceinline__ void update_head(const UpdateArgs &u, int n, int chos
   float *red = hat + 2 * R;            // [2][2][4]
   const float *w = u.ws + ((int64_t)n * u.max_iter + chosen) * W;
   T *Bg[2] = {reinterpret_cast<T *>(u.B_Q) + (int64_t)n * R * D, reinterpret_cast<T *>(u.B_K) + (int64_t)n * R * D};
+  const T *xg[2] = {reinterpret_cast<const T *>(u.q) + (int64_t)n * D,
+                    reinterpret_cast<const T *>(u.k_new) + ((int64_t)b_idx * kv_heads + kvh) * D};
+  // everything this head needs from global memory is asked for in one go: the chosen iterate, this thread's
+  // elements of q and k, then the right factors
+  const float hat_in = tid < 2 * R ? w[tid] : 0.0f;
+  float x_in[2] = {0.0f, 0.0f};
+  if (tid < D) { x_in[0] = Elt<T>::to_float(xg[0][tid]); x_in[1] = Elt<T>::to_float(xg[1][tid]); }
   {
     // every load of a thread is requested before the first is stored (up to eight per trip)
     const int per = R * D / EPV, total = 2 * per;
@@ -84,10 +91,9 @@ __device__ __forceinline__ void update_head(const UpdateArgs &u, int n, int chos
       }
     }
   }
-  for (int i = tid; i < 2 * R; i += blockDim.x) hat[i] = w[i];
+  if (tid < 2 * R) hat[tid] = hat_in;
+  for (int i = tid + blockDim.x; i < 2 * R; i += blockDim.x) hat[i] = w[i];  // (blockDim.x < 2R: head_dim 64 at rank 64)
   __syncthreads();
-  const T *xg[2] = {reinterpret_cast<const T *>(u.q) + (int64_t)n * D,
-                    reinterpret_cast<const T *>(u.k_new) + ((int64_t)b_idx * kv_heads + kvh) * D};
   const bool active = tid < D;
   const int e = tid;
   float t[2] = {0.0f, 0.0f};
@@ -97,7 +103,7 @@ __device__ __forceinline__ void update_head(const UpdateArgs &u, int n, int chos
       float acc = 0.0f;
 #pragma unroll 8
       for (int a = 0; a < R; ++a) acc = __fmaf_rn(hat[s * R + a], Bs[(s * R + a) * D + e], acc);
-      t[s] = __fsub_rn(acc, Elt<T>::to_float(xg[s][e]));  // (x_hat B - x)[e]
+      t[s] = __fsub_rn(acc, x_in[s]);  // (x_hat B - x)[e]
     }
   }
   // |dB|^2 = sum_{a,e} (x_hat[a] t[e])^2 ;  |x_hat dB|^2 = sum_e (sum_a x_hat[a]^2 t[e])^2

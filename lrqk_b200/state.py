@@ -216,6 +216,26 @@ class LayerState:
             "lrqk_decode_project_update")
         return self.q_hat
 
+    def project(self, q, k_new, max_iter: int, append_row: int):
+        """First half of ``project_update``: the alternating solves; every alternation's iterates stay in the
+        projection workspace (nothing else is written)."""
+        self._chk(q, (self.bsz, self.q_heads, self.head_dim), "q")
+        self._chk(k_new, (self.bsz, self.kv_heads, self.head_dim), "k_new")
+        if max(1, max_iter) > self.max_iter_ws:
+            raise ValueError("max_iter exceeds the workspace this state was sized for")
+        _lib.check(self.lib.lrqk_decode_project(C.byref(self.c), _ptr(q), _ptr(k_new), max_iter, append_row,
+                                                _ptr(self.q_hat), _ptr(self.project_ws), _stream()), "lrqk_decode_project")
+
+    def update(self, q, k_new, max_iter: int, tol: float, append_row: int):
+        """Second half: early-exit decision, ``B_Q``/``B_K``, ``q_hat`` and the new row of ``A_K`` from the iterates
+        ``project`` left."""
+        self._chk(q, (self.bsz, self.q_heads, self.head_dim), "q")
+        self._chk(k_new, (self.bsz, self.kv_heads, self.head_dim), "k_new")
+        _lib.check(self.lib.lrqk_decode_update(
+            C.byref(self.c), _ptr(q), _ptr(k_new), max_iter, tol, append_row, _ptr(self.q_hat),
+            C.c_void_p(self.counters.data_ptr() + 8), _ptr(self.project_ws), _stream()), "lrqk_decode_update")
+        return self.q_hat
+
     def score_topk(self, q_hat, candidates: int, scores_out: Optional[torch.Tensor] = None):
         self._chk(q_hat, (self.bsz, self.q_heads, self.r), "q_hat")
         stride = 0

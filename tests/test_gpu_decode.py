@@ -307,6 +307,28 @@ def test_project_update_with_weights_matches_oracle(dtype, r, k, m, bsz, hq, hkv
     _check_project_update(dtype, r, k, m, bsz, hq, hkv, max_iter, d, lam)
 
 
+def test_project_then_update_equals_project_update():
+    """lrqk_decode_project followed by lrqk_decode_update (how the fused step splits the stage) against the one call."""
+    from gpu_util import synthetic_state
+    st = synthetic_state(1, 8, 2, 128, 32, 512, 64, 9000, seed=4)
+    g = torch.Generator(device="cuda").manual_seed(2)
+    q = torch.randn(1, 8, 128, generator=g, device="cuda").to(torch.bfloat16)
+    kn = torch.randn(1, 2, 128, generator=g, device="cuda").to(torch.bfloat16)
+    BQ, BK, A = st.B_Q.clone(), st.B_K.clone(), st.A_K.clone()
+    qa = st.project_update(q, kn, 2, 1e-2, 9000).clone()
+    one = (st.B_Q.clone(), st.B_K.clone(), st.A_K[:, :, 9000].clone(), int(st.counters[2]))
+    st.B_Q.copy_(BQ); st.B_K.copy_(BK); st.A_K.copy_(A)
+    st.project(q, kn, 2, 9000)
+    torch.cuda.synchronize()
+    assert torch.equal(st.B_Q, BQ) and torch.equal(st.A_K, A)          # the first half writes only its workspace
+    qb = st.update(q, kn, 2, 1e-2, 9000).clone()
+    torch.cuda.synchronize()
+    assert torch.equal(qa, qb) and torch.equal(st.B_Q, one[0]) and torch.equal(st.B_K, one[1])
+    assert torch.equal(st.A_K[:, :, 9000], one[2]) and int(st.counters[2]) == one[3]
+    st.check_status()
+    st.close()
+
+
 def _check_project_update(dtype, r, k, m, bsz, hq, hkv, max_iter, d, lam):
     g = torch.Generator().manual_seed(r * k)
     cap = 3000 if k < 2000 else 6000
