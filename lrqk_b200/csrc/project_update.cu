@@ -32,6 +32,8 @@
 // A_K row in the storage dtype.
 #include <cooperative_groups.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "smallmat.cuh"
 #include "tc_common.cuh"
@@ -923,16 +925,73 @@ size_t project_smem_bytes(int csize, int share_rows) {
   return sizeof(float) * floats + PL::tile_bytes + 1024 + 128;  // slack for the 1024-byte alignment of the tiles
 }
 
+// A lower bound of how many clusters of `csize` CTAs of the projection kernel the current device keeps resident at
+// once (a cluster must fit inside one GPC, so this is not simply CTA slots / csize).  Asked of the runtime once per
+// (kernel, cluster size, shared-memory size, device); 0 when it cannot be told.
+template <typename T, int R, int D>
+SmemOptIn &project_opt_in() {
+  static SmemOptIn o;  // one record of the kernel's shared-memory attribute per device, shared by launch and query
+  return o;
+}
+
+template <typename T, int R, int D>
+int project_resident_clusters(int csize, size_t smem) {
+  struct Entry { size_t smem; int n; };  // the answer for the last shared-memory size asked about
+  static std::mutex mu;
+  static Entry cache[kMaxDevices][9] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices || csize < 1 || csize > 8) { cudaGetLastError(); return 0; }
+  std::lock_guard<std::mutex> lock(mu);
+  Entry &c = cache[dev][csize];
+  if (c.n == 0 || c.smem != smem) {
+    auto kern = project_kernel<T, R, D>;
+    int n = 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(csize, 1, 1);
+    cfg.blockDim = dim3(kPThreads);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)csize; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    cudaError_t e = project_opt_in<T, R, D>().ensure(kern, smem);
+    if (e == cudaSuccess) e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+    // The runtime's figure is for one CTA of the cluster per SM (15 clusters of 8 on a 148-SM part).  Where an SM
+    // holds two CTAs of this kernel it says nothing useful (32 clusters of 8 are resident at once there): -2.
+    // (two CTAs: by shared memory -- the kernel's register bound is set for two)
+    if (e == cudaSuccess && 2 * (smem + 1024) <= 227 * 1024) n = -2;
+    if (e != cudaSuccess) { cudaGetLastError(); n = -1; }
+    c.smem = smem;
+    c.n = n > 0 ? n : (n == -2 ? -2 : -1);
+  }
+  return c.n > 0 ? c.n : 0;  // 0: not known
+}
+
 // Clusters: one solver CTA plus streaming CTAs.  The cluster grows (2, 4, 8 CTAs) while every streaming
 // CTA keeps at least two ring stages of rows and the grid stays within the CTAs that are resident at
 // once (two per SM); rank 64 keeps to clusters of 2..4 (its solver holds 16 KiB of partial sums per
-// streaming CTA, and solver and streaming buffers together exceed one CTA's shared memory).
+// streaming CTA, and solver and streaming buffers together exceed one CTA's shared memory).  Where only one
+// CTA fits an SM (rank 64) the runtime knows how many clusters are resident at once, and the cluster shrinks
+// until every head's is: a cluster that has to wait for a place starts when the first streaming CTAs leave
+// and ends long after all the others (40 heads: clusters of 3, all resident, instead of 33 of 40 clusters of 4).
+template <typename T, int R, int D>
+size_t project_smem_for(int csize, int n_act) {
+  const int n_streamers = csize == 1 ? 1 : csize - 1;
+  return project_smem_bytes<T, R, D>(csize, (n_act + n_streamers - 1) / n_streamers);
+}
+
 template <typename T, int R, int D>
 int plan_cluster(int n_heads, int n_act) {
   constexpr int SR = Plan<T, R, D>::SR;
   const int max_c = R >= 64 ? 4 : 8;
-  int csize = R >= 64 ? 2 : 1;
+  const int min_c = R >= 64 ? 2 : 1;
+  int csize = min_c;
   while (csize < max_c && n_heads * csize * 2 <= 2 * kNumSMs && n_act / (csize * 2 - 1) >= 2 * SR) csize *= 2;
+  while (csize > min_c) {
+    const int resident = project_resident_clusters<T, R, D>(csize, project_smem_for<T, R, D>(csize, n_act));
+    if (resident <= 0 || n_heads <= resident) break;
+    --csize;
+  }
   return csize;
 }
 
@@ -948,8 +1007,7 @@ int launch(const lrqk_layer *L, ProjectParams pp, const UpdateParams &up, cudaSt
   if (smem > 227 * 1024) return LRQK_EUNSUPPORTED;
   if (with_project) {
     auto kern = project_kernel<T, R, D>;
-    static SmemOptIn opt_in;
-    LRQK_CUDA_TRY(opt_in.ensure(kern, smem));
+    LRQK_CUDA_TRY((project_opt_in<T, R, D>().ensure(kern, smem)));
     LRQK_CUDA_TRY(launch_dependent(kern, dim3(csize, n_heads, 1), dim3(kPThreads), smem, stream, csize, pp));
   }
   if (with_update) {
