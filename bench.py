@@ -458,7 +458,7 @@ def run_ours(args):
     step_floor_us = sum(bytes_[n] / ((link_peak if n in LINK_BOUND else hbm_peak) * 1e9) for n in floor_names) * 1e6
     roof_step = {"us_at_roofline": round(step_floor_us, 1), "us_measured": round(us_per_layer, 2),
                  "frac": round(step_floor_us / us_per_layer, 4), "miss_rate": round(miss_rate, 4),
-                 "note": "sum over the six stages of algorithmic bytes / measured peak"}
+                 "note": "sum over the stages (ring, projection, update, scoring, difference, miss fetch, attention) of algorithmic bytes / measured peak"}
     by_rho[str(args.rho)] = {k2: roof_step[k2] for k2 in ("us_measured", "us_at_roofline", "frac", "miss_rate")}
     # every rank's own figures (the value above is the slowest rank's): unequal host links show up here
     mine = {"rank": rank, "us_per_layer_step": round(ms_dev_own * 1e3 / (args.steps * layers), 2),
