@@ -12,6 +12,7 @@ from .lrqk_attention import (  # noqa: F401
     LightAttentionIndicesFactory,
     LightAttentionIndicesNoHitMiss,
     PreAllocatedTensor,
+    cast_lrqk_decode,
     repeat_kv,
 )
 
@@ -39,5 +40,5 @@ __all__ = [
     "tps_estimate",
     "load_lrqk_model", "load_model", "load_model_hack", "load_tokenizer", "lrqk_attention_forward", "lrqk_decoder_layer_forward", "patch_model",
     "AutoIncreaseTensor", "AutoIncreaseTensorSharedKV", "DynamicLRQKCache", "InitAQAK",
-    "LightAttentionIndicesFactory", "LightAttentionIndicesNoHitMiss", "PreAllocatedTensor", "repeat_kv",
+    "LightAttentionIndicesFactory", "LightAttentionIndicesNoHitMiss", "PreAllocatedTensor", "cast_lrqk_decode", "repeat_kv",
 ]

@@ -715,6 +715,42 @@ class LightAttentionIndicesFactory:
             self.state = None
 
 
+def cast_lrqk_decode(B_Q: torch.Tensor, A_K: torch.Tensor, B_K: torch.Tensor, K__: torch.Tensor, q: torch.Tensor,
+                     k: torch.Tensor, lambda_dec_q: float = 1.0, lambda_dec_k: float = 1.0, max_iter: int = 8,
+                     tol: float = 1e-5):
+    """The reference's functional form of the decode projection (lrqk_attention.py:803-839) on the projection
+    kernel: ``B_Q, B_K`` [B,H,r,d]; ``A_K`` [B,H,n,r] and ``K__`` [B,H,n,d], the rank-r rows and the keys of the
+    active set; ``q, k`` [B,H,1,d] (``k`` already repeated to the query heads).  Returns ``(B_Q', B_K', q_hat,
+    k_hat)`` with ``q_hat, k_hat`` [B,H,1,r], everything in ``k``'s dtype.  A convenience for code written
+    against the reference's functions: it builds a scratch layer state per call; the cache objects above are the
+    fast path."""
+    bsz, heads, n, r = A_K.shape
+    d = K__.shape[-1]
+    if n < 2:
+        raise ValueError("the active set needs at least two rows")
+    if max_iter > 8:
+        raise ValueError("at most 8 alternations")
+    dtype = k.dtype
+    with on_device(k.device):
+        st = LayerState(bsz, heads, heads, d, r, n - 1, 1, a_capacity=n + 1, host_capacity=1, dtype=dtype,
+                        device=k.device, max_iter=max(1, max_iter), with_host=False,
+                        weights=(1.0, 1.0, float(lambda_dec_q), float(lambda_dec_k)))
+        try:
+            st.A_K[:, :, :n].copy_(A_K)
+            st.B_Q.copy_(B_Q)
+            st.B_K.copy_(B_K)
+            st.K_res.copy_(K__)
+            st.table.copy_(torch.arange(n - 1, dtype=torch.int32, device=k.device).expand(bsz, heads, n - 1))
+            st.lite_pos.fill_(n - 1)
+            q_hat = st.project_update(q.reshape(bsz, heads, d).to(dtype).contiguous(),
+                                      k.reshape(bsz, heads, d).to(dtype).contiguous(), max_iter, tol, n)
+            out = (st.B_Q.clone(), st.B_K.clone(), q_hat.clone().unsqueeze(2), st.A_K[:, :, n:n + 1].clone())
+            st.check_status()
+        finally:
+            st.close()
+    return out
+
+
 class LightAttentionIndicesNoHitMiss(LightAttentionIndicesFactory):
     """Comparison mode without the hit/miss table (lrqk_attention.py:1683-1775): every selected
     row is fetched from the host store on every step."""

@@ -307,6 +307,32 @@ def test_project_update_with_weights_matches_oracle(dtype, r, k, m, bsz, hq, hkv
     _check_project_update(dtype, r, k, m, bsz, hq, hkv, max_iter, d, lam)
 
 
+@pytest.mark.parametrize("dtype,lam", [(torch.float32, (1.0, 1.0)), (torch.bfloat16, (1.0, 1.0)), (torch.float32, (0.5, 2.0))])
+def test_cast_lrqk_decode_functional_form(dtype, lam):
+    """The reference's function signature (lrqk_attention.py:803-839) on the projection kernel, against the oracle."""
+    from lrqk_b200 import cast_lrqk_decode
+    g = torch.Generator().manual_seed(17)
+    b, h, n, r, d = 2, 4, 300, 16, 128
+    A = (torch.randn(b, h, n, r, generator=g) * 0.5).to(dtype)
+    K = torch.randn(b, h, n, d, generator=g).to(dtype)
+    BQ = (torch.randn(b, h, r, d, generator=g) * 0.3).to(dtype)
+    BK = (torch.randn(b, h, r, d, generator=g) * 0.3).to(dtype)
+    q = torch.randn(b, h, 1, d, generator=g).to(dtype)
+    k = torch.randn(b, h, 1, d, generator=g).to(dtype)
+    oBQ, oBK, oq, ok = cast_lrqk_decode(BQ.cuda(), A.cuda(), BK.cuda(), K.cuda(), q.cuda(), k.cuda(),
+                                        lambda_dec_q=lam[0], lambda_dec_k=lam[1], max_iter=3, tol=1e-12)
+    assert oq.shape == (b, h, 1, r) and ok.shape == (b, h, 1, r) and oBQ.dtype == dtype
+    eBQ, eBK, eq, ek = orc.cast_decode(BQ, A, BK, K, q, k, 3, 1e-12, lam[0], lam[1])
+    if dtype == torch.float32:
+        for x, y in ((oBQ, eBQ), (oBK, eBK), (oq, eq), (ok, ek)):
+            assert _rel(x.float().cpu(), y.float()) < 2e-4
+    else:
+        f = torch.float32
+        rBQ, rBK, rq, rk = orc.decode_project_update(BQ.to(f), A.to(f), BK.to(f), K.to(f), q.to(f), k.to(f), 3, 1e-12)
+        for x, y in ((oBQ, rBQ), (oBK, rBK), (oq, rq), (ok, rk)):
+            assert bf16_excess(x, y, 2e-4) <= 1.0
+
+
 def test_project_then_update_equals_project_update():
     """lrqk_decode_project followed by lrqk_decode_update (how the fused step splits the stage) against the one call."""
     from gpu_util import synthetic_state
