@@ -411,6 +411,14 @@ int lrqk_prefill_factorize(const lrqk_layer *L, const void *Q, const void *K, fl
                            void *a_q_last, int32_t *sweeps_out, void *workspace,
                            lrqk_stream_t stream);
 
+/* After lrqk_prefill_factorize (same L, seq_len, sweeps and workspace; sweeps_out as that call wrote it): copies
+ * the d x r maps of the stopping sweep out of the workspace -- in fp32, A_Q = Q X_Q and A_K = K X_K -- to
+ * x_q_out / x_k_out, fp32 [B,Hq,d,r]; either may be NULL.  For callers that want the full left factor of the
+ * queries, which the reference's cast_lrqk_prefill returns (lrqk_attention.py:772-800) and the decode path never
+ * needs beyond its last row. */
+int lrqk_prefill_factor_maps(const lrqk_layer *L, int64_t seq_len, int32_t sweeps, const int32_t *sweeps_out,
+                             const void *workspace, float *x_q_out, float *x_k_out, lrqk_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -13,6 +13,7 @@ from .lrqk_attention import (  # noqa: F401
     LightAttentionIndicesNoHitMiss,
     PreAllocatedTensor,
     cast_lrqk_decode,
+    cast_lrqk_prefill,
     repeat_kv,
 )
 
@@ -40,5 +41,5 @@ __all__ = [
     "tps_estimate",
     "load_lrqk_model", "load_model", "load_model_hack", "load_tokenizer", "lrqk_attention_forward", "lrqk_decoder_layer_forward", "patch_model",
     "AutoIncreaseTensor", "AutoIncreaseTensorSharedKV", "DynamicLRQKCache", "InitAQAK",
-    "LightAttentionIndicesFactory", "LightAttentionIndicesNoHitMiss", "PreAllocatedTensor", "cast_lrqk_decode", "repeat_kv",
+    "LightAttentionIndicesFactory", "LightAttentionIndicesNoHitMiss", "PreAllocatedTensor", "cast_lrqk_decode", "cast_lrqk_prefill", "repeat_kv",
 ]

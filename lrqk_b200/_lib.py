@@ -127,6 +127,8 @@ _SIGNATURES = {
     "lrqk_kv_pack_host": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
     "lrqk_prefill_fill_resident": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "lrqk_prefill_factorize_workspace_bytes": (C.c_size_t, [C.POINTER(Layer), C.c_int64]),
+    "lrqk_prefill_factor_maps": (C.c_int, [C.POINTER(Layer), C.c_int64, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
+                                           C.c_void_p, C.c_void_p]),
     "lrqk_prefill_factorize": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                          C.c_int64, C.c_int32, C.c_float, C.c_void_p, C.c_void_p, C.c_void_p,
                                          C.c_void_p]),

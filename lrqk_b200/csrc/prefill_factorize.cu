@@ -445,8 +445,40 @@ int dispatch_r(const lrqk_layer *L, const void *Q, const void *K, float *A_Q, fl
   }
 }
 
+// The d x r maps of the stopping sweep, copied out of the workspace: A_Q = Q X_Q, A_K = K X_K.
+__global__ void factor_maps_kernel(const float *ws, FactorWs lay, int sweeps, const int32_t *sweeps_out, int dr,
+                                   float *x_q_out, float *x_k_out) {
+  const int n = blockIdx.x;
+  int chosen = *sweeps_out - 1;
+  if (chosen < 0) chosen = 0;
+  if (chosen >= sweeps) chosen = sweeps - 1;
+  const float *res = ws + lay.sweep + ((int64_t)n * sweeps + chosen) * lay.sweep_stride;  // X_Q, X_K, B_Q, B_K, ...
+  for (int i = threadIdx.x; i < dr; i += blockDim.x) {
+    if (x_q_out) x_q_out[(int64_t)n * dr + i] = res[i];
+    if (x_k_out) x_k_out[(int64_t)n * dr + i] = res[dr + i];
+  }
+}
+
 }  // namespace
 }  // namespace lrqk
+
+extern "C" int lrqk_prefill_factor_maps(const lrqk_layer *L, int64_t seq_len, int32_t sweeps, const int32_t *sweeps_out,
+                                        const void *workspace, float *x_q_out, float *x_k_out, lrqk_stream_t stream) {
+  using namespace lrqk;
+  int rc = check_device();
+  if (rc != LRQK_OK) return rc;
+  rc = check_layer(L);
+  if (rc != LRQK_OK) return rc;
+  if (!workspace || !sweeps_out || seq_len <= 0 || (!x_q_out && !x_k_out)) return LRQK_EINVAL;
+  if (sweeps < 1) sweeps = 1;
+  if (sweeps > kMaxSweeps) return LRQK_EUNSUPPORTED;
+  const int n_heads = L->bsz * L->q_heads;
+  const FactorWs lay = factor_ws_layout(n_heads, L->r, L->head_dim, sweeps, plan_gram_splits(n_heads, seq_len));
+  factor_maps_kernel<<<n_heads, 256, 0, as_stream(stream)>>>(reinterpret_cast<const float *>(workspace), lay, sweeps,
+                                                             sweeps_out, L->head_dim * L->r, x_q_out, x_k_out);
+  LRQK_LAUNCH_CHECK();
+  return LRQK_OK;
+}
 
 extern "C" size_t lrqk_prefill_factorize_workspace_bytes(const lrqk_layer *L, int64_t seq_len) {
   using namespace lrqk;

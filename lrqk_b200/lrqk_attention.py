@@ -715,6 +715,40 @@ class LightAttentionIndicesFactory:
             self.state = None
 
 
+def cast_lrqk_prefill(Q: torch.Tensor, K: torch.Tensor, r: int, lambda_Q: float = 1.0, lambda_K: float = 1.0,
+                      max_iter: int = 8, tol: float = 1e-5, init_method: Union[InitAQAK, str] = InitAQAK.randn):
+    """The reference's functional form of the prompt factorisation (lrqk_attention.py:772-800) on the prompt
+    kernels: ``Q, K`` [B,H,S,d] (``K`` already repeated to the query heads, as the reference passes it).  Returns
+    ``(A_Q, B_Q, A_K, B_K)`` in ``K``'s dtype; the full ``A_Q``, which the kernels never materialise, is one
+    library product ``Q X_Q`` with the d x r map the factorisation leaves.  A convenience (scratch state per call)."""
+    bsz, heads, seq_len, d = Q.shape
+    dtype = K.dtype
+    if max_iter > 8:
+        raise ValueError("at most 8 sweeps")
+    with on_device(K.device):
+        st = LayerState(bsz, heads, heads, d, r, 1, 1, a_capacity=seq_len, host_capacity=1, dtype=dtype, device=K.device,
+                        with_host=False, weights=(float(lambda_Q), float(lambda_K), 1.0, 1.0))
+        try:
+            fac = LightAttentionIndicesFactory(r=r, init_aq_ak_method=init_method, num_key_value_groups=1)
+            q, k = Q.to(dtype).contiguous(), K.to(dtype).contiguous()
+            aq, ak = fac._initial_factors(q, k)
+            nb = st.lib.lrqk_prefill_factorize_workspace_bytes(C.byref(st.c), seq_len)
+            ws = torch.empty((max(nb, 16),), dtype=torch.uint8, device=K.device)
+            last = torch.empty((bsz, heads, r), dtype=dtype, device=K.device)
+            n_sw = torch.zeros(1, dtype=torch.int32, device=K.device)
+            sweeps = max(1, max_iter)
+            _lib.check(st.lib.lrqk_prefill_factorize(C.byref(st.c), _ptr(q), _ptr(k), _ptr(aq), _ptr(ak), seq_len, sweeps,
+                                                     tol, _ptr(last), _ptr(n_sw), _ptr(ws), _stream()), "lrqk_prefill_factorize")
+            x_q = torch.empty((bsz, heads, d, r), dtype=torch.float32, device=K.device)
+            _lib.check(st.lib.lrqk_prefill_factor_maps(C.byref(st.c), seq_len, sweeps, _ptr(n_sw), _ptr(ws), _ptr(x_q), None,
+                                                       _stream()), "lrqk_prefill_factor_maps")
+            A_Q = (q.float() @ x_q).to(dtype)
+            out = (A_Q, st.B_Q.clone(), st.A_K[:, :, :seq_len].clone(), st.B_K.clone())
+        finally:
+            st.close()
+    return out
+
+
 def cast_lrqk_decode(B_Q: torch.Tensor, A_K: torch.Tensor, B_K: torch.Tensor, K__: torch.Tensor, q: torch.Tensor,
                      k: torch.Tensor, lambda_dec_q: float = 1.0, lambda_dec_k: float = 1.0, max_iter: int = 8,
                      tol: float = 1e-5):

@@ -69,5 +69,5 @@ def test_throughput_table_rows_and_exports():
     assert issubclass(LightAttentionIndicesNoHitMiss, LightAttentionIndicesFactory)
     for name in ("AutoIncreaseTensor", "AutoIncreaseTensorSharedKV", "PreAllocatedTensor", "repeat_kv", "FullOffloadCache",
                  "HitRateCounter", "LightAttentionIndicesOffloadPrefill", "WrapForwardTimer", "load_model", "load_model_hack",
-                 "load_lrqk_model", "load_tokenizer", "cast_lrqk_decode", "tps_estimate", "run_task"):
+                 "load_lrqk_model", "load_tokenizer", "cast_lrqk_decode", "cast_lrqk_prefill", "tps_estimate", "run_task"):
         assert hasattr(lrqk_b200, name), name

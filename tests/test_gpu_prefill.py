@@ -169,6 +169,26 @@ def test_factory_with_weights_follows_the_reference_trace(name):
     fac.close()
 
 
+@pytest.mark.parametrize("lam", [(1.0, 1.0), (0.5, 2.0)])
+def test_cast_lrqk_prefill_functional_form(lam):
+    """The reference's function signature (lrqk_attention.py:772-800), full A_Q included, against the oracle."""
+    from lrqk_b200 import cast_lrqk_prefill
+    b, hq, hkv, s, d, r = 1, 4, 2, 1500, 128, 16
+    Q, K, _ = orc.make_prompt(61, b, hq, hkv, s, d, latent=64)
+    Krep = orc.expand_kv_heads(K, hq // hkv)
+    A_Q, B_Q, A_K, B_K = cast_lrqk_prefill(Q.cuda(), Krep.cuda(), r, lambda_Q=lam[0], lambda_K=lam[1], max_iter=2, tol=1e-9,
+                                            init_method="top")
+    assert A_Q.shape == (b, hq, s, r) and A_K.shape == (b, hq, s, r) and B_Q.shape == (b, hq, r, d)
+    eAQ, eBQ, eAK, eBK = orc.cast_prefill(Q, Krep, r, 2, 1e-9, "top", None, lam[0], lam[1])
+    for x, y in ((A_Q, eAQ), (B_Q, eBQ), (A_K, eAK), (B_K, eBK)):
+        assert _rel(x.float().cpu(), y.float()) < 5e-4
+    # the joint objective the factors serve: A_Q A_K^T against Q K^T on a slice of the prompt
+    qk = Q[:, :, -64:].float() @ Krep.float().transpose(-1, -2)
+    approx = A_Q[:, :, -64:].float().cpu() @ A_K.float().cpu().transpose(-1, -2)
+    ref = eAQ[:, :, -64:] @ eAK.transpose(-1, -2)
+    assert abs(float((qk - approx).norm() / qk.norm()) - float((qk - ref).norm() / qk.norm())) < 1e-3
+
+
 @pytest.mark.parametrize("init", ["top", "topcol", "randn"])
 def test_factory_prefill_then_decode_matches_oracle(init):
     from lrqk_b200 import LightAttentionIndicesFactory
